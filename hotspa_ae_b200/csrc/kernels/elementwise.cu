@@ -1,0 +1,420 @@
+// Bandwidth-bound fused kernels of the Llama training step (sm_100a, 128-bit accesses):
+//   RoPE on the packed qkv tensor, SwiGLU, (vocab-parallel) softmax cross-entropy, embedding
+//   gather / scatter-add, fused Adam with bf16 emit and gradient clearing, casts and axpy helpers.
+//
+// Reference counterparts: hetu/impl/kernel/rotary.cu, SwiGLU.cu, VocabParallelCrossEntropyLoss.cu,
+// SoftmaxCrossEntropySparse.cu, EmbeddingLookup.cu, Optimizers.cu, DataTransfer.cu, BinaryElewise.cu.
+#include "common.cuh"
+#include "ew_api.h"
+#include <float.h>
+
+namespace hsb {
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE, non-interleaved (rotate-half), in place on q and k inside the packed qkv tensor
+// [T, heads, 3, hd] (per head: q | k | v).  Positions come per token (restart at every packed
+// document).  sign = +1 forward, -1 backward (the conjugate rotation).
+// ---------------------------------------------------------------------------------------------
+__global__ void rope_qkv_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
+                                const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int heads,
+                                int hd, float sign) {
+  const int half = hd >> 1;
+  const int vec_per_half = half >> 3;                 // 8 bf16 per vector
+  const int per_tok = heads * 2 * vec_per_half;       // q and k
+  const long total = static_cast<long>(T) * per_tok;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / per_tok);
+    int r = static_cast<int>(idx - static_cast<long>(t) * per_tok);
+    const int h = r / (2 * vec_per_half);
+    r -= h * 2 * vec_per_half;
+    const int which = r / vec_per_half;               // 0 = q, 1 = k
+    const int v = r - which * vec_per_half;
+    __nv_bfloat16* p = qkv + (static_cast<size_t>(t) * heads + h) * 3 * hd + which * hd + v * 8;
+    const int ps = pos[t];
+    const float* c = cos_t + static_cast<size_t>(ps) * half + v * 8;
+    const float* s = sin_t + static_cast<size_t>(ps) * half + v * 8;
+    float x1[8], x2[8], o1[8], o2[8];
+    ld8(p, x1);
+    ld8(p + half, x2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float cs = c[j], sn = sign * s[j];
+      o1[j] = x1[j] * cs - x2[j] * sn;
+      o2[j] = x1[j] * sn + x2[j] * cs;
+    }
+    st8(p, o1);
+    st8(p + half, o2);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU:  in [rows, 2d] (gate = first half, up = second half of the local shard) -> out [rows, d]
+// ---------------------------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long rows,
+                                  int d) {
+  const int vec = d >> 3;
+  const long total = rows * vec;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = idx / vec;
+    const int v = static_cast<int>(idx - r * vec);
+    float g[8], u[8], o[8];
+    ld8(in + r * 2 * d + v * 8, g);
+    ld8(in + r * 2 * d + d + v * 8, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    st8(out + r * d + v * 8, o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
+                                  __nv_bfloat16* __restrict__ din, long rows, int d) {
+  const int vec = d >> 3;
+  const long total = rows * vec;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = idx / vec;
+    const int v = static_cast<int>(idx - r * vec);
+    float g[8], u[8], dy[8], dg[8], du[8];
+    ld8(in + r * 2 * d + v * 8, g);
+    ld8(in + r * 2 * d + d + v * 8, u);
+    ld8(dout + r * d + v * 8, dy);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * sg;
+      du[j] = dy[j] * silu;
+      dg[j] = dy[j] * u[j] * (sg + silu * (1.f - sg));
+    }
+    st8(din + r * 2 * d + v * 8, dg);
+    st8(din + r * 2 * d + d + v * 8, du);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Softmax cross-entropy over a vocabulary shard.
+//  stats pass : per row (max, sum exp(l - max), target logit if the label falls in this shard)
+//  grad pass  : logits <- (softmax - onehot) * scale[row]   in place, bf16
+// For tensor-parallel vocab the three per-row scalars are combined across ranks between the two
+// passes (host side all-gather of [rows,3] or the fused peer-exchange kernel).
+// ---------------------------------------------------------------------------------------------
+constexpr int CE_THREADS = 256;
+
+__global__ void __launch_bounds__(CE_THREADS)
+ce_stats_kernel(const __nv_bfloat16* __restrict__ logits, const long* __restrict__ labels, float* __restrict__ stats,
+                int rows, int V, int ld, int vocab_start) {
+  __shared__ float sm[32], ss[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* l = logits + static_cast<size_t>(row) * ld;
+    float m = -FLT_MAX, s = 0.f;
+    const int nvec = V >> 3;
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+      float f[8];
+      ld8(l + i * 8, f);
+      float cm = f[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) cm = fmaxf(cm, f[j]);
+      const float nm = fmaxf(m, cm);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
+      s = s * __expf(m - nm) + acc;
+      m = nm;
+    }
+    for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) {
+      const float f = __bfloat162float(l[i]);
+      const float nm = fmaxf(m, f);
+      s = s * __expf(m - nm) + __expf(f - nm);
+      m = nm;
+    }
+    // block combine of (m, s)
+    float wm = warp_max(m);
+    s *= __expf(m - wm);
+    s = warp_sum(s);
+    const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+    __syncthreads();
+    if (ln == 0) { sm[w] = wm; ss[w] = s; }
+    __syncthreads();
+    if (w == 0) {
+      float m2 = ln < CE_THREADS / 32 ? sm[ln] : -FLT_MAX;
+      float s2 = ln < CE_THREADS / 32 ? ss[ln] : 0.f;
+      const float gm = warp_max(m2);
+      s2 *= __expf(m2 - gm);
+      s2 = warp_sum(s2);
+      if (ln == 0) {
+        const long lab = labels[row] - vocab_start;
+        float tgt = 0.f;
+        if (lab >= 0 && lab < V) tgt = __bfloat162float(l[lab]);
+        stats[row * 3 + 0] = gm;
+        stats[row * 3 + 1] = s2;
+        stats[row * 3 + 2] = tgt;
+      }
+    }
+  }
+}
+
+// gstats: per row (global max, global sum-exp); scale: per row multiplier (0 for ignored rows).
+__global__ void __launch_bounds__(CE_THREADS)
+ce_grad_kernel(__nv_bfloat16* __restrict__ logits, const long* __restrict__ labels, const float* __restrict__ gstats,
+               const float* __restrict__ scale, int rows, int V, int ld, int vocab_start) {
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    __nv_bfloat16* l = logits + static_cast<size_t>(row) * ld;
+    const float gm = gstats[row * 2 + 0];
+    const float inv = 1.f / gstats[row * 2 + 1];
+    const float sc = scale[row];
+    const long lab = labels[row] - vocab_start;
+    const int nvec = V >> 3;
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+      float f[8];
+      ld8(l + i * 8, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float p = __expf(f[j] - gm) * inv;
+        if (static_cast<long>(i) * 8 + j == lab) p -= 1.f;
+        f[j] = p * sc;
+      }
+      st8(l + i * 8, f);
+    }
+    for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) {
+      float p = __expf(__bfloat162float(l[i]) - gm) * inv;
+      if (i == lab) p -= 1.f;
+      l[i] = __float2bfloat16(p * sc);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Embedding gather (ids outside [vocab_start, vocab_start + Vloc) give a zero row -> partial sum
+// over tensor-parallel ranks) and scatter-add of the gradient into the fp32 gradient table.
+// ---------------------------------------------------------------------------------------------
+__global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const long* __restrict__ ids,
+                                 __nv_bfloat16* __restrict__ out, int T, int H, int Vloc, int vocab_start) {
+  const int vec = H >> 3;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long id = ids[t] - vocab_start;
+    const bool in = id >= 0 && id < Vloc;
+    for (int i = threadIdx.x; i < vec; i += blockDim.x) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (in) v = *reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * H + i * 8);
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i * 8) = v;
+    }
+  }
+}
+__global__ void embed_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const long* __restrict__ ids,
+                                 float* __restrict__ dtable, int T, int H, int Vloc, int vocab_start) {
+  const int vec = H >> 3;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long id = ids[t] - vocab_start;
+    if (id < 0 || id >= Vloc) continue;
+    for (int i = threadIdx.x; i < vec; i += blockDim.x) {
+      float f[8];
+      ld8(dout + static_cast<size_t>(t) * H + i * 8, f);
+      float* d = dtable + static_cast<size_t>(id) * H + i * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(d + j, f[j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused Adam over flat fp32 arrays: reads the fp32 gradient, updates m, v and the fp32 master
+// parameter, emits the bf16 compute copy and clears the gradient, all in one pass.
+// ---------------------------------------------------------------------------------------------
+__global__ void adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                            float* __restrict__ g, __nv_bfloat16* __restrict__ p_bf16, long n, float lr, float b1,
+                            float b2, float eps, float wd, float bc1, float bc2, float gscale, int zero_grad) {
+  const long nvec = n >> 2;
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = tid; i < nvec; i += stride) {
+    float4 pv = reinterpret_cast<float4*>(p)[i];
+    float4 mv = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float4 gv = reinterpret_cast<float4*>(g)[i];
+    float* pp = reinterpret_cast<float*>(&pv);
+    float* mp = reinterpret_cast<float*>(&mv);
+    float* vp = reinterpret_cast<float*>(&vv);
+    float* gp = reinterpret_cast<float*>(&gv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gr = gp[j] * gscale;
+      mp[j] = b1 * mp[j] + (1.f - b1) * gr;
+      vp[j] = b2 * vp[j] + (1.f - b2) * gr * gr;
+      const float mh = mp[j] / bc1, vh = vp[j] / bc2;
+      pp[j] = pp[j] - lr * (mh / (sqrtf(vh) + eps) + wd * pp[j]);
+    }
+    reinterpret_cast<float4*>(p)[i] = pv;
+    reinterpret_cast<float4*>(m)[i] = mv;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p_bf16) {
+      uint2 o;
+      o.x = pack_bf16x2(pp[0], pp[1]);
+      o.y = pack_bf16x2(pp[2], pp[3]);
+      reinterpret_cast<uint2*>(p_bf16)[i] = o;
+    }
+  }
+  for (long i = (nvec << 2) + tid; i < n; i += stride) {
+    const float gr = g[i] * gscale;
+    const float mm = b1 * m[i] + (1.f - b1) * gr;
+    const float vv2 = b2 * v[i] + (1.f - b2) * gr * gr;
+    const float pn = p[i] - lr * ((mm / bc1) / (sqrtf(vv2 / bc2) + eps) + wd * p[i]);
+    m[i] = mm; v[i] = vv2; p[i] = pn;
+    if (zero_grad) g[i] = 0.f;
+    if (p_bf16) p_bf16[i] = __float2bfloat16(pn);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Casts and accumulate helpers on flat arrays.
+// ---------------------------------------------------------------------------------------------
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
+  const long nvec = n >> 2;
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = tid; i < nvec; i += stride) {
+    const float4 f = reinterpret_cast<const float4*>(in)[i];
+    uint2 o;
+    o.x = pack_bf16x2(f.x, f.y);
+    o.y = pack_bf16x2(f.z, f.w);
+    reinterpret_cast<uint2*>(out)[i] = o;
+  }
+  for (long i = (nvec << 2) + tid; i < n; i += stride) out[i] = __float2bfloat16(in[i]);
+}
+// acc (fp32) += alpha * x (bf16)
+__global__ void axpy_bf16_f32_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ acc, long n,
+                                     float alpha) {
+  const long nvec = n >> 3;
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = tid; i < nvec; i += stride) {
+    float f[8];
+    ld8(x + i * 8, f);
+    float4 a = reinterpret_cast<float4*>(acc)[2 * i], b = reinterpret_cast<float4*>(acc)[2 * i + 1];
+    a.x += alpha * f[0]; a.y += alpha * f[1]; a.z += alpha * f[2]; a.w += alpha * f[3];
+    b.x += alpha * f[4]; b.y += alpha * f[5]; b.z += alpha * f[6]; b.w += alpha * f[7];
+    reinterpret_cast<float4*>(acc)[2 * i] = a;
+    reinterpret_cast<float4*>(acc)[2 * i + 1] = b;
+  }
+  for (long i = (nvec << 3) + tid; i < n; i += stride) acc[i] += alpha * __bfloat162float(x[i]);
+}
+// out (bf16) = a (bf16) + b (bf16)
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, long n) {
+  const long nvec = n >> 3;
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = tid; i < nvec; i += stride) {
+    float x[8], y[8];
+    ld8(a + i * 8, x);
+    ld8(b + i * 8, y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += y[j];
+    st8(out + i * 8, x);
+  }
+  for (long i = (nvec << 3) + tid; i < n; i += stride)
+    out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+}
+
+static inline int ew_grid(long work_items, int threads) {
+  long g = (work_items + threads - 1) / threads;
+  const long cap = 148L * 16;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace hsb
+
+using namespace hsb;
+#define BF(p) reinterpret_cast<__nv_bfloat16*>(p)
+#define CBF(p) reinterpret_cast<const __nv_bfloat16*>(p)
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -4)
+
+extern "C" int hsb_rope_qkv(void* qkv, const int* pos, const float* cos_t, const float* sin_t, int T, int heads,
+                            int hd, int backward, void* stream) {
+  if (hd % 16 != 0 || T <= 0) return -10;
+  const long total = static_cast<long>(T) * heads * 2 * (hd / 16);
+  rope_qkv_kernel<<<ew_grid(total, 256), 256, 0, ST(stream)>>>(BF(qkv), pos, cos_t, sin_t, T, heads, hd,
+                                                                backward ? -1.f : 1.f);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_swiglu_fwd(const void* in, void* out, long rows, int d, void* stream) {
+  if (d % 8 != 0 || rows <= 0) return -10;
+  swiglu_fwd_kernel<<<ew_grid(rows * (d / 8), 256), 256, 0, ST(stream)>>>(CBF(in), BF(out), rows, d);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_swiglu_bwd(const void* in, const void* dout, void* din, long rows, int d, void* stream) {
+  if (d % 8 != 0 || rows <= 0) return -10;
+  swiglu_bwd_kernel<<<ew_grid(rows * (d / 8), 256), 256, 0, ST(stream)>>>(CBF(in), CBF(dout), BF(din), rows, d);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_ce_stats(const void* logits, const long* labels, float* stats, int rows, int V, int ld,
+                            int vocab_start, void* stream) {
+  if (rows <= 0 || ld % 8 != 0) return -10;
+  ce_stats_kernel<<<rows < 148 * 8 ? rows : 148 * 8, CE_THREADS, 0, ST(stream)>>>(CBF(logits), labels, stats, rows,
+                                                                                    V, ld, vocab_start);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_ce_grad(void* logits, const long* labels, const float* gstats, const float* scale, int rows,
+                           int V, int ld, int vocab_start, void* stream) {
+  if (rows <= 0 || ld % 8 != 0) return -10;
+  ce_grad_kernel<<<rows < 148 * 8 ? rows : 148 * 8, CE_THREADS, 0, ST(stream)>>>(BF(logits), labels, gstats, scale,
+                                                                                   rows, V, ld, vocab_start);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_embed_fwd(const void* table, const long* ids, void* out, int T, int H, int Vloc, int vocab_start,
+                             void* stream) {
+  if (H % 8 != 0 || T <= 0) return -10;
+  embed_fwd_kernel<<<T < 148 * 16 ? T : 148 * 16, 128, 0, ST(stream)>>>(CBF(table), ids, BF(out), T, H, Vloc,
+                                                                          vocab_start);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_embed_bwd(const void* dout, const long* ids, float* dtable, int T, int H, int Vloc,
+                             int vocab_start, void* stream) {
+  if (H % 8 != 0 || T <= 0) return -10;
+  embed_bwd_kernel<<<T < 148 * 16 ? T : 148 * 16, 128, 0, ST(stream)>>>(CBF(dout), ids, dtable, T, H, Vloc,
+                                                                          vocab_start);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_adam(float* p, float* m, float* v, float* g, void* p_bf16, long n, float lr, float b1, float b2,
+                        float eps, float wd, float bc1, float bc2, float gscale, int zero_grad, void* stream) {
+  if (n <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(g)) & 15)
+    return -11;
+  if (p_bf16 && (reinterpret_cast<uintptr_t>(p_bf16) & 7)) return -11;
+  adam_kernel<<<ew_grid(n / 4 + 1, 256), 256, 0, ST(stream)>>>(p, m, v, g, BF(p_bf16), n, lr, b1, b2, eps, wd, bc1,
+                                                                bc2, gscale, zero_grad);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_cast_f32_bf16(const float* in, void* out, long n, void* stream) {
+  if (n <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 7)) return -11;
+  cast_f32_bf16_kernel<<<ew_grid(n / 4 + 1, 256), 256, 0, ST(stream)>>>(in, BF(out), n);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_axpy_bf16_f32(const void* x, float* acc, long n, float alpha, void* stream) {
+  if (n <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(acc) & 15)) return -11;
+  axpy_bf16_f32_kernel<<<ew_grid(n / 8 + 1, 256), 256, 0, ST(stream)>>>(CBF(x), acc, n, alpha);
+  return LAUNCH_OK();
+}
+extern "C" int hsb_add_bf16(const void* a, const void* b, void* out, long n, void* stream) {
+  if (n <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return -11;
+  add_bf16_kernel<<<ew_grid(n / 8 + 1, 256), 256, 0, ST(stream)>>>(CBF(a), CBF(b), BF(out), n);
+  return LAUNCH_OK();
+}

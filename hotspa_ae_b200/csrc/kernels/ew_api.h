@@ -1,0 +1,34 @@
+// C entry points of the bandwidth-bound fused kernels (norm.cu, elementwise.cu).
+// All pointers are device pointers; bf16 tensors are passed as void*.  Every function returns 0
+// when the launch was accepted, -10/-11 for a rejected shape/alignment and -4 for a launch error.
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+int hsb_norm_bwd_parts(int rows, int num_sms);
+int hsb_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* hsum, float* mean,
+                 float* rstd, int rows, int H, float eps, int is_rms, void* stream);
+int hsb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                 const void* dres, void* dx, float* dw, float* db, float* scratch, int rows, int H, int is_rms,
+                 int accumulate, int num_sms, void* stream);
+int hsb_rope_qkv(void* qkv, const int* pos, const float* cos_t, const float* sin_t, int T, int heads, int hd,
+                 int backward, void* stream);
+int hsb_swiglu_fwd(const void* in, void* out, long rows, int d, void* stream);
+int hsb_swiglu_bwd(const void* in, const void* dout, void* din, long rows, int d, void* stream);
+int hsb_ce_stats(const void* logits, const long* labels, float* stats, int rows, int V, int ld, int vocab_start,
+                 void* stream);
+int hsb_ce_grad(void* logits, const long* labels, const float* gstats, const float* scale, int rows, int V, int ld,
+                int vocab_start, void* stream);
+int hsb_embed_fwd(const void* table, const long* ids, void* out, int T, int H, int Vloc, int vocab_start,
+                  void* stream);
+int hsb_embed_bwd(const void* dout, const long* ids, float* dtable, int T, int H, int Vloc, int vocab_start,
+                  void* stream);
+int hsb_adam(float* p, float* m, float* v, float* g, void* p_bf16, long n, float lr, float b1, float b2, float eps,
+             float wd, float bc1, float bc2, float gscale, int zero_grad, void* stream);
+int hsb_cast_f32_bf16(const float* in, void* out, long n, void* stream);
+int hsb_axpy_bf16_f32(const void* x, float* acc, long n, float alpha, void* stream);
+int hsb_add_bf16(const void* a, const void* b, void* out, long n, void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,115 @@
+"""ctypes binding of the sm_100a kernel library (``_hsb_kernels.so``).
+
+The library exports plain C launchers that take raw device pointers and a CUDA stream, so the
+Python side only passes ``tensor.data_ptr()`` and ``torch.cuda.current_stream().cuda_stream``.
+On a machine with a GPU the library MUST load: a missing or stale build raises instead of
+silently falling back to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_LIB_PATH = os.path.join(_PKG, "_hsb_kernels.so")
+_lib = None
+_lock = threading.Lock()
+_status: dict[int, torch.Tensor] = {}
+_launches = 0
+
+c_void_p, c_int, c_long, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+_SIGNATURES = {
+    "hsb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_void_p, c_void_p, c_int],
+    "hsb_norm_bwd_parts": [c_int, c_int],
+    "hsb_norm_fwd": [c_void_p] * 8 + [c_int, c_int, c_float, c_int, c_void_p],
+    "hsb_norm_bwd": [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hsb_rope_qkv": [c_void_p] * 4 + [c_int, c_int, c_int, c_int, c_void_p],
+    "hsb_swiglu_fwd": [c_void_p, c_void_p, c_long, c_int, c_void_p],
+    "hsb_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
+    "hsb_ce_stats": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hsb_ce_grad": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hsb_embed_fwd": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hsb_embed_bwd": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hsb_adam": [c_void_p] * 5 + [c_long] + [c_float] * 8 + [c_int, c_void_p],
+    "hsb_cast_f32_bf16": [c_void_p, c_void_p, c_long, c_void_p],
+    "hsb_axpy_bf16_f32": [c_void_p, c_void_p, c_long, c_float, c_void_p],
+    "hsb_add_bf16": [c_void_p, c_void_p, c_void_p, c_long, c_void_p],
+}
+
+
+def available() -> bool:
+    """True when the CUDA kernels can run here (GPU present)."""
+    return torch.cuda.is_available()
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(_LIB_PATH):
+                from .. import build
+                build.build_kernels()
+            handle = ctypes.CDLL(_LIB_PATH)
+            for name, argtypes in _SIGNATURES.items():
+                fn = getattr(handle, name, None)
+                if fn is None:
+                    continue  # optional entry points are declared by their own modules
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            _lib = handle
+    return _lib
+
+
+def declare(name: str, argtypes: list, restype=c_int):
+    fn = getattr(lib(), name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_tensor(device=None) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits set when a wait ran out."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    t = _status.get(dev)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        _status[dev] = t
+    return t
+
+
+_STATUS_NAMES = {1: "TMA producer wait timed out", 2: "MMA issuer wait timed out", 3: "epilogue wait timed out",
+                 4: "peer flag wait timed out", 5: "bad kernel argument"}
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises if any kernel reported a timed-out wait since the last check."""
+    code = int(status_tensor(device).item())
+    if code != 0:
+        status_tensor(device).zero_()
+        raise RuntimeError(f"hotspa_ae_b200 kernel error {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+
+
+def count_launch(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def launches() -> int:
+    """Number of kernels of this library launched by this process so far."""
+    return _launches
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what}: launcher returned {rc}")

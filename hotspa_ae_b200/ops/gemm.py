@@ -1,0 +1,138 @@
+"""tcgen05 GEMM wrappers and the Linear autograd function built on them.
+
+Operand conventions follow ``csrc/kernels/gemm_tcgen05.cu``:
+``gemm(a, b, a_mn=False, b_mn=False)`` computes ``op(a) @ op(b).T`` where a K-major operand is
+stored ``[rows, K]`` and an MN-major operand ``[K, rows]`` (both row-major).  A Linear layer
+``y = x @ W.T`` with ``W`` stored ``[out, in]`` therefore needs no transposed copies in any of
+its three GEMMs.  Replaces the cuBLAS path of the reference's Linear op
+(hetu/graph/ops/Linear.cc, hetu/impl/kernel/Linear.cu).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+EPI_BF16, EPI_F32, EPI_F32_ACC = 0, 1, 2
+
+
+def _use_cuda(*ts: torch.Tensor) -> bool:
+    return all(t.is_cuda for t in ts)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, tile_n: int = 0) -> torch.Tensor:
+    """``out (=|+=) op(a) @ op(b).T`` with fp32 accumulation.
+
+    a: [M, K] (or [K, M] when ``a_mn``), b: [N, K] (or [K, N] when ``b_mn``), bf16, last dim contiguous.
+    ``accumulate`` requires an fp32 ``out`` and adds into it.
+    """
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    if accumulate:
+        assert out is not None and out.dtype == torch.float32
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(-1) == 1
+
+    if not _use_cuda(a, b):
+        # CPU reference path (unit tests of the layers above run here)
+        A = a.float().t() if a_mn else a.float()
+        B = b.float() if b_mn else b.float().t()
+        res = A @ B
+        if accumulate:
+            out.add_(res)
+        else:
+            out.copy_(res.to(out.dtype))
+        return out
+
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    if a.stride(0) % 8 or b.stride(0) % 8 or a.data_ptr() % 16 or b.data_ptr() % 16:
+        a, b = a.contiguous(), b.contiguous()
+        if a.stride(0) % 8 or b.stride(0) % 8:
+            # rows that are not 16-byte multiples cannot be described to TMA: pad K
+            raise ValueError("gemm: leading dimensions must be multiples of 8 elements")
+    if out.dtype == torch.bfloat16:
+        epi = EPI_BF16
+    else:
+        epi = EPI_F32_ACC if accumulate else EPI_F32
+    rc = _lib.lib().hsb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                  out.stride(0), int(a_mn), int(b_mn), epi, tile_n,
+                                  _lib.status_tensor(a.device).data_ptr(), _lib.stream_ptr(), 0)
+    _lib.check(rc, "hsb_gemm_bf16")
+    _lib.count_launch()
+    return out
+
+
+class LinearFn(torch.autograd.Function):
+    """y = x @ W.T  (W stored [out, in]); weight gradient optionally accumulated into an fp32 main-grad."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad):
+        ctx.save_for_backward(x, w)
+        ctx.main_grad = main_grad
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w)
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx[T, in] = dy[T, out] @ W[out, in]  -> b operand is W as [K=out, N=in] (MN-major)
+            dx = gemm(dy2, w, b_mn=True).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            # dW[out, in] = dy^T x : a = dy as [K=T, M=out] (MN-major), b = x as [K=T, N=in] (MN-major)
+            if ctx.main_grad is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+                dw = None  # accumulated in place; the optimizer reads main_grad
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype if w.dtype != torch.bfloat16 else torch.bfloat16)
+        return dx, dw, None
+
+
+class LinearKNFn(torch.autograd.Function):
+    """y = x @ W  with W stored [in, out] (the reference's row-parallel weight layout)."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad):
+        ctx.save_for_backward(x, w)
+        ctx.main_grad = main_grad
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, b_mn=True)           # b = W as [K=in, N=out]
+        return y.reshape(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w).reshape(x.shape)   # dx[T,in] = dy[T,out] @ W[in,out]^T -> b = W [N=in, K=out] K-major
+        if ctx.needs_input_grad[1]:
+            # dW[in, out] = x^T dy : a = x as [K=T, M=in], b = dy as [K=T, N=out]
+            if ctx.main_grad is not None:
+                gemm(x2, dy2, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+            else:
+                dw = gemm(x2, dy2, a_mn=True, b_mn=True)
+        return dx, dw, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, main_grad: torch.Tensor | None = None, trans_b: bool = True):
+    """Linear layer on the tcgen05 GEMM.  ``trans_b=True``: w is [out, in]; else w is [in, out]."""
+    return (LinearFn if trans_b else LinearKNFn).apply(x, w, main_grad)

@@ -1,0 +1,495 @@
+"""Per-rank runtime of the define-and-run graph.
+
+For every strategy an :class:`ExecPlan` is derived once: the pipeline stages (from the device groups of
+the ops), the ops this rank executes, the stage-boundary transfers, the collective behind every ``comm``
+op and the process groups they need.  A run interprets the plan micro-batch by micro-batch under the
+1F1B schedule; differentiation is torch autograd over the custom Functions of ``hotspa_ae_b200.ops``
+and ``parallel.comm``; parameters, gradients and optimizer state live in :class:`ParamStore` arenas.
+
+Reference counterparts: hetu/graph/executable_graph.cc (Instantiate, SubstituteCommOp, ComputeFunc,
+pipedream-flush schedule, run levels) and define_and_run_graph.cc (plan cache, hot-switch trigger).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+import torch.utils.checkpoint as ckpt
+
+from .. import core as C
+from ..ops import _lib
+from ..ops.gemm import linear as gemm_linear
+from ..parallel import comm as PC
+from ..parallel import mesh as M
+from ..parallel.param_store import ParamStore
+from . import ops as O
+from .graph import ALLOC, GRAD, TOPO, UPDATE
+from .tensor import Tensor
+
+
+@dataclass
+class CommInfo:
+    kind: int
+    name: str
+    group_ranks: tuple = ()
+    dim: int = 0
+    index: int = 0
+    count: int = 1
+    src_peer: int = -1      # for P2P: the rank we receive from
+    dst_peer: int = -1      # for P2P: the rank we send to
+
+
+@dataclass
+class Segment:
+    ops: list
+    recompute: bool = False
+    ext_inputs: list = field(default_factory=list)    # tensors read from outside (recompute segments)
+    outputs: list = field(default_factory=list)       # tensors needed after the segment
+
+
+@dataclass
+class ExecPlan:
+    sid: int
+    stages: list
+    my_stage: int
+    my_ops: list
+    segments: list
+    recv_ops: list
+    send_ops: list
+    comm: dict
+    dp: int
+    loss_local: bool = False
+
+
+class Runtime:
+    """What op implementations see while they compute."""
+
+    def __init__(self, ex: "Executor", plan: ExecPlan):
+        self.ex, self.plan = ex, plan
+        self.strategy_id = plan.sid
+        self.training = True
+        self.mesh = ex.mesh
+
+    def device_index_of(self, t: Tensor) -> int:
+        for g in t.dg_hierarchy[self.strategy_id]:
+            if g.contains(self.mesh.rank):
+                return g.get_index(self.mesh.rank)
+        raise RuntimeError(f"rank {self.mesh.rank} does not hold {t}")
+
+    def group_ranks_by_dim(self, t: Tensor, dim: int) -> tuple:
+        ds = t.ds(self.strategy_id)
+        for g in t.dg_hierarchy[self.strategy_id]:
+            if g.contains(self.mesh.rank):
+                return tuple(ds.get_devices_by_dim(dim, g.get_index(self.mesh.rank), g.ranks()))
+        raise RuntimeError(f"rank {self.mesh.rank} does not hold {t}")
+
+    def group_by_dim(self, t: Tensor, dim: int):
+        return self.mesh.group(self.group_ranks_by_dim(t, dim))
+
+    combine_ce_stats = staticmethod(PC.combine_ce_stats)
+
+    def linear(self, op, x, w, trans_b: bool):
+        a, b = op.inputs[0], op.inputs[1]
+        a_ds, b_ds = a.ds(self.strategy_id), b.ds(self.strategy_id)
+        b_col = b_ds.get_dim(0 if trans_b else 1)
+        # a duplicated activation multiplied by column-sharded weights: its gradient is partial over
+        # those shards -> all-reduce in backward (tensor parallel without sequence parallel)
+        if b_col > 1 and a_ds.get_dim(-1) > 1 and x.requires_grad:
+            ranks = self.group_ranks_by_dim(a, -1)
+            if len(ranks) > 1 and not self.mesh.virtual:
+                x = PC.CopyToGroup.apply(x, self.mesh.group(ranks))
+        return gemm_linear(x, w, getattr(w, "main_grad", None), trans_b=trans_b)
+
+    def comm(self, op, x):
+        info: CommInfo = self.plan.comm[op.id]
+        k = info.kind
+        if k == C._C.COMM_UNUSED:
+            return x
+        group = self.mesh.group(info.group_ranks) if len(info.group_ranks) > 1 else None
+        if k == C._C.COMM_ALL_GATHER:
+            return PC.AllGather.apply(x, group, info.dim)
+        if k == C._C.COMM_REDUCE_SCATTER:
+            return PC.ReduceScatter.apply(x, group, info.dim)
+        if k == C._C.COMM_ALL_REDUCE:
+            return PC.AllReduce.apply(x, group)
+        if k in (C._C.COMM_SPLIT, C._C.COMM_SCATTER):
+            return PC.SplitLocal.apply(x, group, info.dim, info.index, info.count)
+        raise NotImplementedError(f"comm type {info.name} inside a stage is not implemented")
+
+
+class Executor:
+    def __init__(self, graph):
+        self.graph = graph
+        self.mesh = M.mesh()
+        self.store = ParamStore(graph)
+        self.plans: dict[int, ExecPlan] = {}
+        self.const_cache: dict = {}
+        self.stats: dict = {"runs": 0}
+        self.pipeline_schedule = "1f1b"
+
+    def on_strategies_added(self):
+        self.plans.clear()
+        return self
+
+    # ---- planning ---------------------------------------------------------------------------------------
+    def _placement(self, op, sid):
+        return op.outputs[0].dg_hierarchy[sid]
+
+    def _on_me(self, groups) -> bool:
+        return any(g.contains(self.mesh.rank) for g in groups)
+
+    def plan(self, sid: int) -> ExecPlan:
+        if sid in self.plans:
+            return self.plans[sid]
+        g, rank = self.graph, self.mesh.rank
+        stages: list[tuple] = []
+
+        def note(groups):
+            for grp in groups:
+                r = tuple(grp.ranks())
+                if r not in stages:
+                    stages.append(r)
+
+        for op in g.ops:
+            if op.type == "comm":
+                note(op.inputs[0].dg_hierarchy[sid])
+            for t in op.inputs:
+                if t.is_parameter:
+                    note(t.dg_hierarchy[sid])
+            note(self._placement(op, sid))
+        my_stage = next((i for i, r in enumerate(stages) if rank in r), -1)
+
+        my_ops, recv_ops, send_ops, comm, needed = [], [], [], {}, []
+        for op in g.ops:
+            if getattr(op.outputs[0], "is_train_op", False):
+                continue
+            if op.type == "comm":
+                x, y = op.inputs[0], op.outputs[0]
+                sg, dg = x.dg_hierarchy[sid], y.dg_hierarchy[sid]
+                s_ranks, d_ranks = sg[0].ranks(), dg[0].ranks()
+                kind = C.classify_comm(x.ds_hierarchy[sid], s_ranks, y.ds_hierarchy[sid], d_ranks, 0)
+                name = C.comm_type_name(kind)
+                if kind == C._C.COMM_UNSUPPORTED:
+                    raise RuntimeError(f"{op}: no collective realises {x.ds(sid)} -> {y.ds(sid)}")
+                if kind == C._C.COMM_P2P:
+                    info = CommInfo(kind, name)
+                    if rank in s_ranks:
+                        info.dst_peer = d_ranks[s_ranks.index(rank)]
+                        send_ops.append(op)
+                    if rank in d_ranks:
+                        info.src_peer = s_ranks[d_ranks.index(rank)]
+                        recv_ops.append(op)
+                    comm[op.id] = info
+                    continue
+                if kind == C._C.COMM_BATCHED_SEND_RECV:
+                    raise NotImplementedError(f"{op}: activation repartition between different layouts/groups")
+                # every rank computes every rank's collective group so that groups are created collectively
+                sds, dds = x.ds(sid), y.ds(sid)
+                for idx in range(len(s_ranks)):
+                    ranks_i, dim, index, count = self._collective_group(kind, sds, dds, idx, s_ranks)
+                    needed.append(ranks_i)
+                    if s_ranks[idx] == rank:
+                        comm[op.id] = CommInfo(kind, name, ranks_i, dim, index, count)
+                if rank in s_ranks:
+                    my_ops.append(op)
+                continue
+            if self._on_me(self._placement(op, sid)):
+                my_ops.append(op)
+            if op.type == "vocab_parallel_cross_entropy":
+                lt = op.inputs[0]
+                lds = lt.ds(sid)
+                if lds.get_dim(1) > 1:
+                    for grp in lt.dg_hierarchy[sid]:
+                        for idx in range(grp.num_devices):
+                            needed.append(tuple(lds.get_devices_by_dim(1, idx, grp.ranks())))
+            if op.type == "linear":
+                a = op.inputs[0]
+                ads = a.ds(sid)
+                if ads.get_dim(-1) > 1:
+                    for grp in a.dg_hierarchy[sid]:
+                        for idx in range(grp.num_devices):
+                            needed.append(tuple(ads.get_devices_by_dim(-1, idx, grp.ranks())))
+        # gradient reduce classes of every rank
+        for r in range(self.mesh.world_size):
+            for c in self.store.layout(sid, r).classes:
+                needed.append(tuple(c.ranks))
+        self.mesh.ensure_groups(needed)
+
+        dp = 1
+        for ph in g.placeholders:
+            dp = max(dp, ph.ds(sid).get_dim(0))
+            break
+        segments = self._segments(my_ops, sid, send_ops)
+        loss_local = False
+        plan = ExecPlan(sid, stages, my_stage, my_ops, segments, recv_ops, send_ops, comm, dp, loss_local)
+        self.plans[sid] = plan
+        return plan
+
+    def _collective_group(self, kind, sds, dds, idx, ranks):
+        if kind == C._C.COMM_ALL_GATHER:
+            # gathered dim: the split dim of src that became duplicate in dst
+            dim = next((d for d, n in sds.states.items() if d >= 0 and n > dds.get_dim(d)), 0)
+            return tuple(dds.get_devices_by_dim(-1, idx, ranks)), dim, 0, 1
+        if kind == C._C.COMM_REDUCE_SCATTER:
+            dim = next((d for d, n in dds.states.items() if d >= 0 and n > sds.get_dim(d)), 0)
+            return tuple(sds.get_devices_by_dim(-2, idx, ranks)), dim, 0, 1
+        if kind == C._C.COMM_ALL_REDUCE:
+            return tuple(sds.get_devices_by_dim(-2, idx, ranks)), 0, 0, 1
+        # dup -> split: local slice, all-gather in backward
+        dim = next((d for d, n in dds.states.items() if d >= 0 and n > sds.get_dim(d)), 0)
+        count = dds.get_dim(dim) // sds.get_dim(dim)
+        grp = tuple(sds.get_devices_by_dim(-1, idx, ranks))
+        index = dds.map_device_to_state_index(idx).get(dim, 0) % count
+        # the slice each rank keeps must follow its position inside the duplicate group
+        if len(grp) == count:
+            index = grp.index(ranks[idx])
+        return grp, dim, index, count
+
+    def _segments(self, my_ops, sid, send_ops):
+        segs: list[Segment] = []
+        for op in my_ops:
+            scope = op.recompute_scope
+            if segs and scope is not None and segs[-1].recompute and segs[-1].ops[-1].recompute_scope == scope:
+                segs[-1].ops.append(op)
+            else:
+                segs.append(Segment([op], scope is not None))
+        produced_in = {}
+        for si, s in enumerate(segs):
+            for op in s.ops:
+                for t in op.outputs:
+                    produced_in[t.id] = si
+        keep = {t.inputs[0].id for t in send_ops}
+        consumers: dict[int, set] = {}
+        for si, s in enumerate(segs):
+            for op in s.ops:
+                for t in op.inputs:
+                    consumers.setdefault(t.id, set()).add(si)
+        for si, s in enumerate(segs):
+            if not s.recompute:
+                continue
+            seen_in, seen_out = set(), set()
+            for op in s.ops:
+                for t in op.inputs:
+                    if produced_in.get(t.id) != si and t.id not in seen_in:
+                        seen_in.add(t.id)
+                        s.ext_inputs.append(t)
+                for t in op.outputs:
+                    used_later = any(c != si for c in consumers.get(t.id, ())) or t.id in keep
+                    if used_later and t.id not in seen_out:
+                        seen_out.add(t.id)
+                        s.outputs.append(t)
+            if not s.outputs:
+                s.outputs = list(s.ops[-1].outputs)
+        return segs
+
+    # ---- values -----------------------------------------------------------------------------------------
+    def _const_value(self, t: Tensor, sid: int):
+        key = (t.id, sid)
+        if key not in self.const_cache:
+            arr = self.graph.constants[t.id]
+            idx = None
+            for grp in t.dg_hierarchy[sid]:
+                if grp.contains(self.mesh.rank):
+                    idx = grp.get_index(self.mesh.rank)
+            ds = t.ds(sid)
+            if idx is not None and not ds.is_pure_duplicate:
+                sl = ds.local_slice(list(arr.shape), idx)
+                arr = arr[tuple(slice(o, o + n) for o, n in sl)]
+            v = torch.from_numpy(np.ascontiguousarray(arr)).to(self.mesh.torch_device)
+            if v.is_floating_point() and self.graph.autocast_dtype is not None:
+                v = v.to(self.graph.autocast_dtype)
+            self.const_cache[key] = v
+        return self.const_cache[key]
+
+    def _value(self, t: Tensor, values: dict, feeds: dict, params: dict, sid: int):
+        if t.id in values:
+            return values[t.id]
+        if t.is_parameter:
+            return params[t.id]
+        if t.is_placeholder:
+            if t.id not in feeds:
+                raise KeyError(f"placeholder {t.name} was not fed")
+            return feeds[t.id]
+        if t.id in self.graph.constants:
+            return self._const_value(t, sid)
+        raise RuntimeError(f"{t} has no value on rank {self.mesh.rank} (strategy {sid})")
+
+    def _run_ops(self, rt, ops, values, feeds, params, sid):
+        for op in ops:
+            ins = [self._value(t, values, feeds, params, sid) for t in op.inputs]
+            outs = O.REGISTRY[op.type].compute(rt, op, ins)
+            for t, v in zip(op.outputs, outs):
+                values[t.id] = v
+
+    def _forward(self, rt, plan, feeds, params, recv_vals):
+        sid = plan.sid
+        values = dict(recv_vals)
+        for seg in plan.segments:
+            if not seg.recompute or not torch.is_grad_enabled():
+                self._run_ops(rt, seg.ops, values, feeds, params, sid)
+                continue
+            ext = [self._value(t, values, feeds, params, sid) for t in seg.ext_inputs]
+            ext_ids = [t.id for t in seg.ext_inputs]
+            out_ids = [t.id for t in seg.outputs]
+
+            def body(*args, _seg=seg, _ext_ids=ext_ids, _out_ids=out_ids):
+                local = dict(zip(_ext_ids, args))
+                self._run_ops(rt, _seg.ops, local, feeds, params, sid)
+                return tuple(local[i] for i in _out_ids)
+
+            outs = ckpt.checkpoint(body, *ext, use_reentrant=False, preserve_rng_state=False)
+            for i, v in zip(out_ids, outs):
+                values[i] = v
+        return values
+
+    # ---- run ----------------------------------------------------------------------------------------------
+    def _split_feeds(self, feed_dict, nmb):
+        per_mb = [dict() for _ in range(nmb)]
+        dev = self.mesh.torch_device
+        for t, arr in feed_dict.items():
+            if isinstance(arr, (list, tuple)) and len(arr) == nmb and not isinstance(arr[0], (int, float)):
+                chunks = [torch.as_tensor(np.asarray(a)) if not torch.is_tensor(a) else a for a in arr]
+            else:
+                v = arr if torch.is_tensor(arr) else torch.as_tensor(np.asarray(arr))
+                if v.shape[0] % nmb != 0:
+                    raise ValueError(f"feed for {t.name}: leading dim {v.shape[0]} not divisible by "
+                                     f"num_micro_batches {nmb}")
+                chunks = list(v.chunk(nmb, dim=0))
+            for i, c in enumerate(chunks):
+                c = c.to(dev, non_blocking=True)
+                if c.is_floating_point() and self.graph.autocast_dtype is not None:
+                    c = c.to(self.graph.autocast_dtype)
+                per_mb[i][t.id] = c
+        return per_mb
+
+    def run(self, loss, fetches, feed_dict, nmb, sid, run_level, grad_scale):
+        plan = self.plan(sid)
+        self.stats["runs"] += 1
+        if run_level == TOPO:
+            return []
+        self.store.ensure_compute(sid)
+        if run_level == ALLOC:
+            return []
+        rt = Runtime(self, plan)
+        params = self.store.param_views(sid)
+        feeds = self._split_feeds(feed_dict, nmb)
+        wants_train = any(getattr(f, "is_train_op", False) for f in fetches) or loss is not None
+        loss_t = loss if loss is not None else next((f for f in fetches if not getattr(f, "is_train_op", False)), None)
+        n_stage = len(plan.stages)
+        stage = plan.my_stage
+        if stage < 0:
+            return []
+        seed = grad_scale / (nmb * plan.dp)
+        tasks = (C.schedule_1f1b if self.pipeline_schedule == "1f1b" else C.schedule_gpipe)(n_stage, stage, nmb)
+        live: dict[int, dict] = {}
+        losses: dict[int, torch.Tensor] = {}
+        fetched: dict[int, list] = {f.id: [None] * nmb for f in fetches if not getattr(f, "is_train_op", False)}
+        pending_sends: list = []
+        dev = self.mesh.torch_device
+
+        def recv_specs_fwd():
+            out = []
+            for op in plan.recv_ops:
+                t = op.outputs[0]
+                out.append((t.local_shape(sid), self._act_dtype(t), dev, plan.comm[op.id].src_peer))
+            return out
+
+        def recv_specs_bwd():
+            out = []
+            for op in plan.send_ops:
+                t = op.inputs[0]
+                out.append((t.local_shape(sid), self._act_dtype(t), dev, plan.comm[op.id].dst_peer))
+            return out
+
+        for is_fwd, mb in tasks:
+            if is_fwd:
+                recvd = PC.p2p_exchange(pending_sends, recv_specs_fwd()) if (pending_sends or plan.recv_ops) else []
+                pending_sends = []
+                recv_vals = {}
+                for op, v in zip(plan.recv_ops, recvd):
+                    v.requires_grad_(wants_train and v.is_floating_point())
+                    recv_vals[op.outputs[0].id] = v
+                with torch.set_grad_enabled(wants_train):
+                    values = self._forward(rt, plan, feeds[mb], params, recv_vals)
+                live[mb] = {"recv": recv_vals, "send": [values[op.inputs[0].id] for op in plan.send_ops]}
+                for op, v in zip(plan.send_ops, live[mb]["send"]):
+                    pending_sends.append((v.detach(), plan.comm[op.id].dst_peer))
+                if loss_t is not None and loss_t.id in values:
+                    losses[mb] = values[loss_t.id]
+                for fid in fetched:
+                    if fid in values:
+                        fetched[fid][mb] = values[fid].detach()
+                if not wants_train:
+                    live.pop(mb)
+            else:
+                if not wants_train:
+                    continue
+                grads_in = PC.p2p_exchange(pending_sends, recv_specs_bwd()) if (pending_sends or plan.send_ops) else []
+                pending_sends = []
+                st = live.pop(mb)
+                roots, root_grads = [], []
+                if mb in losses and losses[mb].requires_grad:
+                    roots.append(losses[mb])
+                    root_grads.append(torch.full_like(losses[mb], seed))
+                for v, gin in zip(st["send"], grads_in):
+                    if v.requires_grad:
+                        roots.append(v)
+                        root_grads.append(gin.to(v.dtype))
+                if roots:
+                    torch.autograd.backward(roots, root_grads)
+                for op in plan.recv_ops:
+                    v = st["recv"][op.outputs[0].id]
+                    gsend = v.grad if v.grad is not None else torch.zeros_like(v)
+                    pending_sends.append((gsend, plan.comm[op.id].src_peer))
+                self._fold_autograd_grads(params)
+        if pending_sends:
+            PC.p2p_exchange(pending_sends, [])
+
+        if wants_train and run_level == GRAD:
+            self.store.hand_grads_home(sid)
+        if wants_train and run_level == UPDATE:
+            if self.store.home != sid:
+                raise RuntimeError("UPDATE must run under the home strategy (the one that was allocated first)")
+            self.store.reduce_and_step(self.graph.optimizer, 1.0)
+
+        out = []
+        for f in fetches:
+            if getattr(f, "is_train_op", False):
+                out.append(None)
+                continue
+            vals = [v for v in fetched.get(f.id, []) if v is not None]
+            if not vals:
+                out.append(None)
+            else:
+                out.append(torch.cat([v.reshape(-1) if v.dim() == 0 else v for v in vals], dim=0))
+        return out
+
+    def _act_dtype(self, t: Tensor):
+        if t.dtype.is_floating_point and self.graph.autocast_dtype is not None:
+            return self.graph.autocast_dtype
+        return t.dtype
+
+    def _fold_autograd_grads(self, params):
+        """Gradients that reached a parameter through plain autograd (ops without a fused main-grad path)."""
+        for v in params.values():
+            if v.grad is not None:
+                v.main_grad.add_(v.grad.to(torch.float32))
+                v.grad = None
+
+    # ---- parameter access -----------------------------------------------------------------------------------
+    def get_local_data(self, t: Tensor):
+        if t.is_parameter:
+            if self.store.home is None:
+                self.store.ensure_compute(0)
+            v = self.store.local_value(t)
+            return None if v is None else v.detach().float().cpu().numpy()
+        if t.id in self.graph.constants:
+            return self._const_value(t, self.graph.cur_strategy_id).float().cpu().numpy()
+        raise ValueError(f"{t} holds no persistent data")
+
+    def reset_param_data(self, t: Tensor, array):
+        if self.store.home is None:
+            self.store.ensure_compute(0)
+        self.store.load_global(t, torch.as_tensor(np.asarray(array)))

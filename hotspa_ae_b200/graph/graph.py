@@ -1,0 +1,349 @@
+"""Define-and-run graph with N parallel strategies over one set of ops.
+
+``with ht.graph("define_and_run", num_strategy=N):`` records ops; every tensor gets one
+DistributedStatesUnion per strategy (deduced op by op at definition time).  ``graph.run`` executes
+the recorded program for one strategy on this rank through :class:`Executor`, hot-switching
+parameters and gradients between strategies as needed.
+
+Reference counterparts: hetu/graph/graph.{h,cc} (Graph, MakeOp), hetu/graph/define_and_run_graph.cc
+(multi-strategy planner, Run), python_refactor/hetu/__init__.py (context managers).
+"""
+from __future__ import annotations
+
+import contextlib
+import itertools
+from typing import Any
+
+import numpy as np
+import torch
+
+from ..core import DistributedStates, DistributedStatesUnion, IntSymbol, classify_comm, sym_value
+from ..parallel import mesh as M
+from . import ops as O
+from .tensor import Op, Tensor, as_symbol
+
+RUN_LEVELS = {"update": 0, "grad": 1, "alloc": 2, "topo": 3}
+UPDATE, GRAD, ALLOC, TOPO = 0, 1, 2, 3
+
+_graph_stack: list["Graph"] = []
+_autocast_stack: list[Any] = []
+_default_graph: "Graph | None" = None
+
+
+def run_level(name: str) -> int:
+    return RUN_LEVELS[name]
+
+
+def current_graph() -> "Graph":
+    global _default_graph
+    if _graph_stack:
+        return _graph_stack[-1]
+    if _default_graph is None:
+        _default_graph = Graph("define_and_run", 1, name="default")
+    return _default_graph
+
+
+@contextlib.contextmanager
+def graph(kind: str = "define_and_run", num_strategy: int = 1, create_new: bool = True, name: str | None = None):
+    g = Graph(kind, num_strategy, name=name) if (create_new or not _graph_stack) else _graph_stack[-1]
+    _graph_stack.append(g)
+    try:
+        yield g
+    finally:
+        _graph_stack.pop()
+
+
+@contextlib.contextmanager
+def autocast(dtype=torch.bfloat16):
+    _autocast_stack.append(dtype)
+    g = current_graph()
+    prev = g.autocast_dtype
+    g.autocast_dtype = dtype
+    try:
+        yield
+    finally:
+        _autocast_stack.pop()
+        g.autocast_dtype = prev if _autocast_stack else g.autocast_dtype
+
+
+@contextlib.contextmanager
+def recompute():
+    """Ops created inside are re-executed during backward instead of keeping their activations."""
+    g = current_graph()
+    g._recompute_stack.append(next(g._recompute_ids))
+    try:
+        yield
+    finally:
+        g._recompute_stack.pop()
+
+
+@contextlib.contextmanager
+def merge_strategy(target_graph: "Graph | None" = None, num_strategy: int = 1):
+    """Append `num_strategy` new strategies to an existing graph: ops re-created inside this context with the
+    same names extend the DS hierarchies of the existing tensors instead of adding new ops
+    (reference: hetu.merge_strategy / DefineAndRunGraph::MergeGraph)."""
+    g = target_graph or current_graph()
+    g.begin_merge(num_strategy)
+    _graph_stack.append(g)
+    try:
+        yield g
+    finally:
+        _graph_stack.pop()
+        g.end_merge()
+
+
+class Graph:
+    def __init__(self, kind: str = "define_and_run", num_strategy: int = 1, name: str | None = None):
+        if kind not in ("define_and_run", "eager", "define_by_run"):
+            raise ValueError(f"unknown graph kind {kind}")
+        self.kind = kind
+        self.name = name or kind
+        self.num_strategy = num_strategy
+        self.ops: list[Op] = []
+        self.parameters: list[Tensor] = []
+        self.placeholders: list[Tensor] = []
+        self.constants: dict[int, np.ndarray] = {}
+        self.param_inits: dict[int, Any] = {}
+        self.cur_strategy_id = 0
+        self.autocast_dtype = None
+        self.optimizer = None
+        self._recompute_stack: list[int] = []
+        self._recompute_ids = itertools.count()
+        self._executor = None
+        self._merge = None
+        self._by_name: dict[str, Tensor] = {}
+
+    # ---- definition -------------------------------------------------------------------------
+    def current_recompute_scope(self):
+        return self._recompute_stack[-1] if self._recompute_stack else None
+
+    def _register(self, t: Tensor) -> Tensor:
+        self._by_name.setdefault(t.name, t)
+        return t
+
+    def _check_hierarchy(self, ds_hierarchy, what: str):
+        n_expected = self._merge["count"] if self._merge else self.num_strategy
+        if len(ds_hierarchy) != n_expected:
+            raise ValueError(f"{what}: got {len(ds_hierarchy)} strategies, graph expects {n_expected}")
+
+    def parallel_placeholder(self, dtype, global_shape, ds_hierarchy, device_group_hierarchy=None, name=None):
+        self._check_hierarchy(ds_hierarchy, "parallel_placeholder")
+        if self._merge is not None:
+            t = self._by_name[name]
+            t.ds_hierarchy.extend(ds_hierarchy)
+            t.dg_hierarchy.extend(self._norm_dgh(device_group_hierarchy, ds_hierarchy))
+            return t
+        t = Tensor(self, global_shape, dtype, ds_hierarchy, self._norm_dgh(device_group_hierarchy, ds_hierarchy),
+                   None, name)
+        t.is_placeholder = True
+        self.placeholders.append(t)
+        return self._register(t)
+
+    def parallel_parameter(self, init, global_shape, ds_hierarchy, local_idx=None, dtype=torch.float32,
+                           requires_grad=True, device_group_hierarchy=None, name=None):
+        self._check_hierarchy(ds_hierarchy, "parallel_parameter")
+        if self._merge is not None:
+            t = self._by_name[name]
+            t.ds_hierarchy.extend(ds_hierarchy)
+            t.dg_hierarchy.extend(self._norm_dgh(device_group_hierarchy, ds_hierarchy))
+            return t
+        t = Tensor(self, global_shape, dtype, ds_hierarchy, self._norm_dgh(device_group_hierarchy, ds_hierarchy),
+                   None, name, requires_grad)
+        t.is_parameter = True
+        t.layer_index = None
+        self.parameters.append(t)
+        self.param_inits[t.id] = init
+        return self._register(t)
+
+    def from_numpy_parallel(self, data, ds_hierarchy, requires_grad=False, device_group_hierarchy=None, name=None):
+        self._check_hierarchy(ds_hierarchy, "from_numpy_parallel")
+        arr = np.asarray(data if not isinstance(data, list) else data[0])
+        if self._merge is not None:
+            t = self._by_name[name]
+            t.ds_hierarchy.extend(ds_hierarchy)
+            t.dg_hierarchy.extend(self._norm_dgh(device_group_hierarchy, ds_hierarchy))
+            return t
+        dtype = torch.from_numpy(arr[:0].copy()).dtype if arr.size else torch.float32
+        t = Tensor(self, list(arr.shape), dtype, ds_hierarchy, self._norm_dgh(device_group_hierarchy, ds_hierarchy),
+                   None, name, requires_grad)
+        self.constants[t.id] = arr
+        return self._register(t)
+
+    def _norm_dgh(self, dgh, ds_hierarchy):
+        """Per strategy: list[DeviceGroup].  Missing -> the first `device_num` ranks of the world."""
+        out = []
+        for s, union in enumerate(ds_hierarchy):
+            if dgh is not None and dgh[s] is not None:
+                groups = dgh[s]
+                groups = [groups] if isinstance(groups, M.DeviceGroup) else list(groups)
+                out.append([g if isinstance(g, M.DeviceGroup) else M.DeviceGroup(g) for g in groups])
+            else:
+                n = union.get(0).device_num // max(1, union.size() if union.is_hetero() else 1)
+                out.append([M.DeviceGroup(list(range(n)))])
+        return out
+
+    def begin_merge(self, count: int):
+        self._merge = {"count": count, "op_cursor": 0}
+
+    def end_merge(self):
+        self.num_strategy += self._merge["count"]
+        self._merge = None
+        self._executor = None if self._executor is None else self._executor.on_strategies_added()
+
+    def make_op(self, op_type, inputs, attrs, name, device_group_hierarchy=None) -> list[Tensor]:
+        impl = O.REGISTRY[op_type]
+        # promote python scalars / numpy inputs to constants
+        if self._merge is not None:
+            return self._merge_op(op_type, inputs, attrs, device_group_hierarchy)
+        op = Op(op_type, inputs, attrs, name, self)
+        op.autocast = self.autocast_dtype
+        infos = impl.infer(inputs, attrs)
+        n_out = len(infos)
+        ds_h = [[] for _ in range(n_out)]
+        dg_h = []
+        for s in range(self.num_strategy):
+            outs_members = self._deduce_strategy(impl, inputs, attrs, s, n_out)
+            for k in range(n_out):
+                ds_h[k].append(outs_members[k])
+            dg_h.append(self._deduce_groups(inputs, s, device_group_hierarchy))
+        for k, (shape, dtype) in enumerate(infos):
+            req = any(t.requires_grad for t in inputs) and dtype.is_floating_point
+            out_dtype = dtype
+            t = Tensor(self, shape, out_dtype, ds_h[k], [list(g) for g in dg_h], op,
+                       None if n_out == 1 and name is None else (f"{op.name}:{k}"), req)
+            op.outputs.append(t)
+        self.ops.append(op)
+        return op.outputs
+
+    def _deduce_strategy(self, impl, inputs, attrs, s, n_out):
+        unions = [t.ds_hierarchy[s] for t in inputs]
+        size = max([u.size() for u in unions], default=1)
+        hetero = next((u.hetero_dim for u in unions if u.is_hetero()), -3)
+        members = [[] for _ in range(n_out)]
+        for m in range(size):
+            in_ds = [u.get(min(m, u.size() - 1)) for u in unions]
+            outs = impl.deduce(in_ds, attrs, inputs)
+            for k in range(n_out):
+                members[k].append(outs[k])
+        return [DistributedStatesUnion(members[k], hetero) for k in range(n_out)]
+
+    def _deduce_groups(self, inputs, s, explicit):
+        if explicit is not None and explicit[s] is not None:
+            groups = explicit[s]
+            groups = [groups] if isinstance(groups, M.DeviceGroup) else list(groups)
+            return [g if isinstance(g, M.DeviceGroup) else M.DeviceGroup(g) for g in groups]
+        # parameters pin an op to their stage; otherwise follow the first non-placeholder input
+        for t in inputs:
+            if t.is_parameter:
+                return t.dg_hierarchy[s]
+        for t in inputs:
+            if not t.is_placeholder and t.id not in self.constants:
+                return t.dg_hierarchy[s]
+        return inputs[0].dg_hierarchy[s] if inputs else [M.DeviceGroup(list(range(M.mesh().world_size)))]
+
+    def make_comm_op(self, x: Tensor, dst_ds_hierarchy, dst_dg_hierarchy, name) -> Tensor:
+        self._check_hierarchy(dst_ds_hierarchy, "comm")
+        if self._merge is not None:
+            op = self._next_merge_op("comm")
+            out = op.outputs[0]
+            out.ds_hierarchy.extend(dst_ds_hierarchy)
+            out.dg_hierarchy.extend(self._comm_groups(x, dst_ds_hierarchy, dst_dg_hierarchy, len(out.dg_hierarchy)))
+            return out
+        op = Op("comm", [x], {}, name, self)
+        op.autocast = self.autocast_dtype
+        dgs = self._comm_groups(x, dst_ds_hierarchy, dst_dg_hierarchy, 0)
+        out = Tensor(self, x.symbolic_shape, x.dtype, dst_ds_hierarchy, dgs, op, None, x.requires_grad)
+        op.outputs.append(out)
+        self.ops.append(op)
+        return out
+
+    def _comm_groups(self, x, dst_ds_hierarchy, dst_dg_hierarchy, base):
+        out = []
+        for i in range(len(dst_ds_hierarchy)):
+            if dst_dg_hierarchy is not None and dst_dg_hierarchy[i] is not None:
+                groups = dst_dg_hierarchy[i]
+                groups = [groups] if isinstance(groups, M.DeviceGroup) else list(groups)
+                out.append([g if isinstance(g, M.DeviceGroup) else M.DeviceGroup(g) for g in groups])
+            else:
+                out.append(list(x.dg_hierarchy[base + i]))
+        return out
+
+    # ---- merging additional strategies -----------------------------------------------------------
+    def _next_merge_op(self, op_type) -> Op:
+        cur = self._merge["op_cursor"]
+        while cur < len(self.ops) and self.ops[cur].type != op_type:
+            cur += 1
+        if cur >= len(self.ops):
+            raise RuntimeError(f"merge_strategy: the re-traced program diverged at a '{op_type}' op")
+        self._merge["op_cursor"] = cur + 1
+        return self.ops[cur]
+
+    def _merge_op(self, op_type, inputs, attrs, device_group_hierarchy):
+        impl = O.REGISTRY[op_type]
+        cur = self._merge["op_cursor"]
+        if cur >= len(self.ops) or self.ops[cur].type != op_type:
+            raise RuntimeError(f"merge_strategy: expected op '{self.ops[cur].type if cur < len(self.ops) else None}', "
+                               f"got '{op_type}'")
+        op = self.ops[cur]
+        self._merge["op_cursor"] = cur + 1
+        base = self.num_strategy
+        for j in range(self._merge["count"]):
+            s = base + j
+            outs = self._deduce_strategy(impl, op.inputs, op.attrs, s, len(op.outputs))
+            dg = self._deduce_groups(op.inputs, s, None if device_group_hierarchy is None else
+                                     [None] * base + list(device_group_hierarchy))
+            for k, t in enumerate(op.outputs):
+                t.ds_hierarchy.append(outs[k])
+                t.dg_hierarchy.append(list(dg))
+        return op.outputs
+
+    # ---- execution ------------------------------------------------------------------------------
+    @property
+    def executor(self):
+        if self._executor is None:
+            from .executor import Executor
+            self._executor = Executor(self)
+        return self._executor
+
+    def run(self, loss=None, fetches=None, feed_dict=None, num_micro_batches: int = 1, cur_strategy_id: int = 0,
+            run_level: int = UPDATE, grad_scale: float = 1.0):
+        """Run one bucket under strategy `cur_strategy_id`.
+
+        run_level: TOPO build the plan only; ALLOC materialise parameters in this strategy's layout;
+        GRAD forward+backward, gradients accumulated (and handed to the home strategy);
+        UPDATE forward+backward, add every accumulated gradient, data-parallel reduce, optimizer step.
+        Returns the fetched values (loss: one value per micro-batch on the ranks that own it).
+        """
+        if isinstance(loss, (list, tuple)) and fetches is None:
+            loss, fetches = None, loss
+        self.cur_strategy_id = cur_strategy_id
+        return self.executor.run(loss, list(fetches or []), feed_dict or {}, num_micro_batches, cur_strategy_id,
+                                 run_level, grad_scale)
+
+    def get_local_data(self, t: Tensor):
+        return self.executor.get_local_data(t)
+
+    def reset_param_data(self, t: Tensor, array):
+        return self.executor.reset_param_data(t, array)
+
+
+# module-level front-ends -------------------------------------------------------------------------
+def parallel_placeholder(dtype, global_shape, ds_hierarchy, device_group_hierarchy=None, name=None):
+    return current_graph().parallel_placeholder(dtype, global_shape, ds_hierarchy, device_group_hierarchy, name)
+
+
+def parallel_parameter(init, global_shape, ds_hierarchy, local_idx=None, dtype=torch.float32, requires_grad=True,
+                       device_group_hierarchy=None, name=None):
+    return current_graph().parallel_parameter(init, global_shape, ds_hierarchy, local_idx, dtype, requires_grad,
+                                              device_group_hierarchy, name)
+
+
+def from_numpy_parallel(data, ds_hierarchy, requires_grad=False, device_group_hierarchy=None, name=None):
+    return current_graph().from_numpy_parallel(data, ds_hierarchy, requires_grad, device_group_hierarchy, name)
+
+
+def placeholder(dtype, shape, name=None):
+    n = M.mesh().world_size
+    ds = DistributedStatesUnion([DistributedStates(n, {-1: n}, [-1])])
+    g = current_graph()
+    return g.parallel_placeholder(dtype, shape, [ds] * g.num_strategy, None, name)

@@ -1,0 +1,889 @@
+"""Op library of the define-and-run graph.
+
+Each op type provides three things (the roles of InferMeta / DeduceStates / Compute of the
+reference's OpInterface, hetu/graph/operator.h:231-399):
+
+* ``infer(inputs, attrs)``          -> [(symbolic_shape, dtype), ...] of the outputs
+* ``deduce(in_ds, attrs, inputs)``  -> [DistributedStates, ...] of the outputs under one strategy
+* ``compute(rt, op, values)``       -> local torch tensors (differentiable; backward is torch autograd
+                                       through the custom Functions of ``hotspa_ae_b200.ops``)
+
+The functional front-end (``linear(x, w)`` ...) is what ``import hetu as ht`` re-exports.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Callable
+
+import numpy as np
+import torch
+
+from ..core import DistributedStates, DistributedStatesUnion, IntSymbol, deduce_linear, sym_value
+from ..ops import functional as Fn
+from ..ops.attention import attention_varlen
+from .tensor import Tensor, as_symbol
+
+REGISTRY: dict[str, Any] = {}
+
+
+def register(name: str):
+    def deco(cls):
+        REGISTRY[name] = cls
+        cls.type = name
+        return cls
+    return deco
+
+
+def _graph_of(*xs):
+    for x in xs:
+        if isinstance(x, Tensor):
+            return x.graph
+    from .graph import current_graph
+    return current_graph()
+
+
+def make_op_front(op_type: str, inputs, attrs=None, name=None, device_group_hierarchy=None):
+    g = _graph_of(*inputs)
+    return g.make_op(op_type, list(inputs), attrs or {}, name, device_group_hierarchy)
+
+
+def _dup_ds(n: int) -> DistributedStates:
+    return DistributedStates(n, {-1: n}, [-1])
+
+
+def _same_as_input(i: int = 0):
+    def deduce(in_ds, attrs, inputs):
+        return [in_ds[i]]
+    return staticmethod(deduce)
+
+
+# ---------------------------------------------------------------------------------------------
+# elementwise family
+# ---------------------------------------------------------------------------------------------
+def _broadcast_shape(a, b):
+    out = []
+    for i in range(max(len(a), len(b))):
+        x = a[len(a) - 1 - i] if i < len(a) else None
+        y = b[len(b) - 1 - i] if i < len(b) else None
+        if x is None:
+            out.append(y)
+        elif y is None:
+            out.append(x)
+        else:
+            out.append(y if (x.is_instantiated() and x.is_leaf() and sym_value(x) == 1) else x)
+    return list(reversed(out))
+
+
+def _binary_deduce(in_ds, attrs, inputs):
+    a, b = in_ds[0], in_ds[1] if len(in_ds) > 1 else None
+    if b is None or a.check_equal(b):
+        return [a]
+    # one side replicated (e.g. bias / norm weight): follow the other
+    if b.is_pure_duplicate:
+        return [a]
+    if a.is_pure_duplicate:
+        return [b]
+    # same splits, different duplicate bookkeeping: partial + dup is not allowed
+    if a.get_dim(-2) == 1 and b.get_dim(-2) == 1:
+        sa = {k: v for k, v in a.states.items() if k >= 0 and v > 1}
+        sb = {k: v for k, v in b.states.items() if k >= 0 and v > 1}
+        if sa == sb:
+            return [a]
+    raise ValueError(f"elementwise op: incompatible distributed states {a} vs {b}")
+
+
+def _register_binary(name: str, fn: Callable):
+    @register(name)
+    class _Bin:
+        @staticmethod
+        def infer(inputs, attrs):
+            if len(inputs) == 1:
+                return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+            return [(_broadcast_shape(inputs[0].symbolic_shape, inputs[1].symbolic_shape), inputs[0].dtype)]
+        deduce = staticmethod(_binary_deduce)
+
+        @staticmethod
+        def compute(rt, op, vals):
+            if len(vals) == 1:
+                return [fn(vals[0], op.attrs["const"])]
+            a, b = vals
+            if b.dtype != a.dtype and b.is_floating_point() and a.is_floating_point():
+                b = b.to(a.dtype)
+            return [fn(a, b)]
+    return _Bin
+
+
+_register_binary("add", lambda a, b: a + b)
+_register_binary("sub", lambda a, b: a - b)
+_register_binary("mul", lambda a, b: a * b)
+_register_binary("div", lambda a, b: a / b)
+_register_binary("pow", lambda a, b: a ** b)
+_register_binary("maximum", lambda a, b: torch.maximum(a, b) if isinstance(b, torch.Tensor) else a.clamp(min=b))
+_register_binary("minimum", lambda a, b: torch.minimum(a, b) if isinstance(b, torch.Tensor) else a.clamp(max=b))
+
+
+def _binary_front(name):
+    def f(a, b, name_=None):
+        if isinstance(b, Tensor) and isinstance(a, Tensor):
+            return make_op_front(name, [a, b], {}, name_)[0]
+        if isinstance(a, Tensor):
+            return make_op_front(name, [a], {"const": b}, name_)[0]
+        raise TypeError(f"{name}: first operand must be a graph tensor")
+    return f
+
+
+add, sub, mul, div, pow = (_binary_front(n) for n in ("add", "sub", "mul", "div", "pow"))  # noqa: A001
+maximum, minimum = _binary_front("maximum"), _binary_front("minimum")
+
+_UNARY = {
+    "neg": torch.neg, "abs": torch.abs, "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt,
+    "sin": torch.sin, "cos": torch.cos, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "relu": torch.relu,
+    "gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu, "ceil": torch.ceil, "floor": torch.floor,
+    "round": torch.round, "reciprocal": torch.reciprocal, "leaky_relu": torch.nn.functional.leaky_relu,
+    "contiguous": lambda x: x.contiguous(), "bool": lambda x: x != 0,
+}
+
+
+def _register_unary(name, fn):
+    @register(name)
+    class _Un:
+        @staticmethod
+        def infer(inputs, attrs):
+            return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+        deduce = _same_as_input(0)
+
+        @staticmethod
+        def compute(rt, op, vals):
+            return [fn(vals[0])]
+    return _Un
+
+
+for _n, _f in _UNARY.items():
+    _register_unary(_n, _f)
+
+
+def _unary_front(name):
+    def f(x, name_=None):
+        return make_op_front(name, [x], {}, name_)[0]
+    return f
+
+
+neg, abs, exp, log, sqrt, rsqrt, sin, cos, tanh, sigmoid, relu, gelu, silu, ceil, floor, round, reciprocal, \
+    leaky_relu, contiguous, bool = (_unary_front(n) for n in _UNARY)  # noqa: A001
+
+
+@register("dropout")
+class _Dropout:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        p = op.attrs["p"]
+        if p <= 0.0 or not rt.training:
+            return [vals[0]]
+        return [torch.nn.functional.dropout(vals[0], p, True)]
+
+
+def dropout(x, p: float, name=None):
+    return make_op_front("dropout", [x], {"p": float(p)}, name)[0]
+
+
+@register("softmax")
+class _Softmax:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        dim = attrs["dim"] % inputs[0].ndim
+        if in_ds[0].get_dim(dim) > 1:
+            raise ValueError("softmax over a split dimension is not supported")
+        return [in_ds[0]]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [torch.softmax(vals[0].float(), op.attrs["dim"]).to(vals[0].dtype)]
+
+
+def softmax(x, dim: int = -1, name=None):
+    return make_op_front("softmax", [x], {"dim": dim}, name)[0]
+
+
+@register("reduce")
+class _Reduce:
+    @staticmethod
+    def infer(inputs, attrs):
+        x = inputs[0]
+        axes = [a % x.ndim for a in attrs["axes"]] if attrs["axes"] else list(range(x.ndim))
+        if attrs["keepdims"]:
+            shape = [IntSymbol(1) if i in axes else s for i, s in enumerate(x.symbolic_shape)]
+        else:
+            shape = [s for i, s in enumerate(x.symbolic_shape) if i not in axes]
+        return [(shape, x.dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        x, ds = inputs[0], in_ds[0]
+        axes = sorted(a % x.ndim for a in attrs["axes"]) if attrs["axes"] else list(range(x.ndim))
+        mode = attrs["mode"]
+        partial = ds.get_dim(-2)
+        states, order = {}, []
+        newdim = {}
+        k = 0
+        for d in range(x.ndim):
+            if d in axes and not attrs["keepdims"]:
+                continue
+            newdim[d] = k
+            k += 1
+        for d, n in ds.states.items():
+            if d >= 0 and d in axes:
+                if n > 1:
+                    if mode not in ("sum", "mean"):
+                        raise ValueError(f"reduce {mode} over a split dimension is not supported")
+                    partial *= n
+            elif d >= 0:
+                states[newdim[d]] = n
+        states[-2] = partial
+        states[-1] = ds.get_dim(-1)
+        for o in ds.order:
+            if o >= 0 and o in axes:
+                if -2 not in order:
+                    order.append(-2)
+            elif o >= 0:
+                order.append(newdim[o])
+            elif o not in order:
+                order.append(o)
+        return [DistributedStates(ds.device_num, states, order)]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        x = vals[0]
+        axes = op.attrs["axes"] or list(range(x.dim()))
+        mode, keep = op.attrs["mode"], op.attrs["keepdims"]
+        if mode == "sum":
+            return [x.sum(axes, keepdim=keep)]
+        if mode == "mean":
+            # a mean over a split axis becomes a partial sum scaled by the global extent
+            t = op.inputs[0]
+            gshape = t.global_shape
+            if any(t.ds(rt.strategy_id).get_dim(a % x.dim()) > 1 for a in axes):
+                denom = 1
+                for a in axes:
+                    denom *= gshape[a % x.dim()]
+                return [x.sum(axes, keepdim=keep) / denom]
+            return [x.mean(axes, keepdim=keep)]
+        if mode == "max":
+            return [x.amax(axes, keepdim=keep)]
+        if mode == "min":
+            return [x.amin(axes, keepdim=keep)]
+        if mode == "prod":
+            y = x
+            for a in sorted((a % x.dim() for a in axes), reverse=True):
+                y = y.prod(a, keepdim=keep)
+            return [y]
+        raise ValueError(mode)
+
+
+def reduce(x, mode: str = "sum", axes=None, keepdims: bool = False, name=None):  # noqa: A001
+    axes = [] if axes is None else ([axes] if isinstance(axes, int) else list(axes))
+    return make_op_front("reduce", [x], {"mode": mode, "axes": axes, "keepdims": keepdims}, name)[0]
+
+
+def reduce_sum(x, axes=None, keepdims=False, name=None):
+    return reduce(x, "sum", axes, keepdims, name)
+
+
+def reduce_mean(x, axes=None, keepdims=False, name=None):
+    return reduce(x, "mean", axes, keepdims, name)
+
+
+def reduce_max(x, axes=None, keepdims=False, name=None):
+    return reduce(x, "max", axes, keepdims, name)
+
+
+# ---------------------------------------------------------------------------------------------
+# shape ops
+# ---------------------------------------------------------------------------------------------
+@register("reshape")
+class _Reshape:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [([as_symbol(s) for s in attrs["shape"]], inputs[0].dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        ds, x = in_ds[0], inputs[0]
+        in_nd, out_nd = x.ndim, len(attrs["shape"])
+        states, order_map = {-1: ds.get_dim(-1), -2: ds.get_dim(-2)}, {-1: -1, -2: -2}
+        for d, n in ds.states.items():
+            if d < 0 or n == 1:
+                continue
+            if d == 0:
+                nd = 0                      # leading (token / batch) split stays in front
+            elif d == in_nd - 1:
+                nd = out_nd - 1             # trailing (feature) split stays at the back
+            else:
+                raise ValueError("reshape: only the first or the last dimension may be split")
+            if nd in states:
+                raise ValueError("reshape: two split dims collapse into one")
+            states[nd] = n
+            order_map[d] = nd
+        order = [order_map[o] for o in ds.order]
+        return [DistributedStates(ds.device_num, states, order)]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        out = op.outputs[0]
+        ds = out.ds(rt.strategy_id)
+        local = [sym_value(s) // ds.get_dim(d) for d, s in enumerate(out.symbolic_shape)]
+        # tolerate a run-time token count that differs from the symbol (e.g. ragged micro-batches)
+        if math.prod(local) != vals[0].numel():
+            known = math.prod(local[1:]) if len(local) > 1 else 1
+            local[0] = vals[0].numel() // max(1, known)
+        return [vals[0].reshape(local)]
+
+
+def reshape(x, shape, name=None):
+    return make_op_front("reshape", [x], {"shape": list(shape)}, name)[0]
+
+
+@register("transpose")
+class _Transpose:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [([inputs[0].symbolic_shape[p] for p in attrs["perm"]], inputs[0].dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        ds, perm = in_ds[0], attrs["perm"]
+        inv = {p: i for i, p in enumerate(perm)}
+        states = {(inv[d] if d >= 0 else d): n for d, n in ds.states.items()}
+        order = [(inv[o] if o >= 0 else o) for o in ds.order]
+        return [DistributedStates(ds.device_num, states, order)]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [vals[0].permute(op.attrs["perm"])]
+
+
+def transpose(x, perm, name=None):
+    return make_op_front("transpose", [x], {"perm": list(perm)}, name)[0]
+
+
+@register("slice")
+class _Slice:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [([as_symbol(s) for s in attrs["size"]], inputs[0].dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        return [in_ds[0]]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        x = vals[0]
+        ds = op.inputs[0].ds(rt.strategy_id)
+        idx = []
+        for d, (b, s) in enumerate(zip(op.attrs["begin"], op.attrs["size"])):
+            n = ds.get_dim(d)
+            b, s = sym_value(b), sym_value(s)
+            if n > 1:
+                # slicing along a split dim must keep whole, equal shards
+                if b % n or s % n:
+                    raise ValueError("slice along a split dimension must be divisible by the split count")
+                b, s = b // n, s // n
+            idx.append(slice(b, b + s))
+        return [x[tuple(idx)]]
+
+
+def slice(x, begin, size, name=None):  # noqa: A001
+    return make_op_front("slice", [x], {"begin": list(begin), "size": list(size)}, name)[0]
+
+
+def split(x, num_chunks: int, dim: int, name=None):
+    """Equal split along `dim` into views (reference: ht.split -> Slice ops with symbolic begin/size)."""
+    dim = dim % x.ndim
+    outs = []
+    chunk = x.symbolic_shape[dim] / num_chunks
+    for i in range(num_chunks):
+        begin = [IntSymbol(0)] * x.ndim
+        size = list(x.symbolic_shape)
+        begin[dim] = chunk * i
+        size[dim] = chunk
+        outs.append(slice(x, begin, size, name=None if name is None else f"{name}_{i}"))
+    return outs
+
+
+@register("concat")
+class _Concat:
+    @staticmethod
+    def infer(inputs, attrs):
+        dim = attrs["dim"] % inputs[0].ndim
+        shape = list(inputs[0].symbolic_shape)
+        tot = inputs[0].symbolic_shape[dim]
+        for t in inputs[1:]:
+            tot = tot + t.symbolic_shape[dim]
+        shape[dim] = tot
+        return [(shape, inputs[0].dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        dim = attrs["dim"] % inputs[0].ndim
+        if in_ds[0].get_dim(dim) > 1:
+            raise ValueError("concat along a split dimension is not supported")
+        return [in_ds[0]]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [torch.cat(vals, dim=op.attrs["dim"])]
+
+
+def concat(xs, dim: int = 0, name=None):
+    return make_op_front("concat", list(xs), {"dim": dim}, name)[0]
+
+
+concatenate = concat
+
+
+# ---------------------------------------------------------------------------------------------
+# linear algebra
+# ---------------------------------------------------------------------------------------------
+@register("linear")
+class _Linear:
+    @staticmethod
+    def infer(inputs, attrs):
+        a, b = inputs[0], inputs[1]
+        ta, tb = attrs["trans_a"], attrs["trans_b"]
+        m = a.symbolic_shape[1] if ta else a.symbolic_shape[0]
+        n = b.symbolic_shape[0] if tb else b.symbolic_shape[1]
+        return [([m, n], a.dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        return [deduce_linear(in_ds[0], in_ds[1], attrs["trans_a"], attrs["trans_b"])]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        x, w = vals[0], vals[1]
+        if op.attrs["trans_a"]:
+            x = x.t()
+        if w.dtype != x.dtype:
+            w = w.to(x.dtype)
+        y = rt.linear(op, x, w, trans_b=op.attrs["trans_b"])
+        if len(vals) > 2 and vals[2] is not None:
+            y = y + vals[2].to(y.dtype)
+        return [y]
+
+
+def linear(a, b, bias=None, trans_a: bool = False, trans_b: bool = True, device_group_hierarchy=None, name=None):
+    ins = [a, b] + ([bias] if bias is not None else [])
+    return make_op_front("linear", ins, {"trans_a": trans_a, "trans_b": trans_b}, name, device_group_hierarchy)[0]
+
+
+def matmul(a, b, trans_a=False, trans_b=False, name=None):
+    return linear(a, b, None, trans_a, trans_b, name=name)
+
+
+@register("bmm")
+class _Bmm:
+    @staticmethod
+    def infer(inputs, attrs):
+        a, b = inputs
+        return [(list(a.symbolic_shape[:-1]) + [b.symbolic_shape[-1]], a.dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        nd = inputs[0].ndim
+        if in_ds[0].get_dim(nd - 1) > 1 or in_ds[1].get_dim(nd - 2) > 1:
+            raise ValueError("bmm: contraction dimension must not be split")
+        return [in_ds[0]]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [torch.matmul(vals[0], vals[1])]
+
+
+def bmm(a, b, name=None):
+    return make_op_front("bmm", [a, b], {}, name)[0]
+
+
+# ---------------------------------------------------------------------------------------------
+# LLM ops
+# ---------------------------------------------------------------------------------------------
+@register("rms_norm")
+class _RmsNorm:
+    @staticmethod
+    def infer(inputs, attrs):
+        x = inputs[0]
+        return [(x.symbolic_shape, x.dtype), (x.symbolic_shape, x.dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        if in_ds[0].get_dim(inputs[0].ndim - 1) > 1:
+            raise ValueError("norm over a split hidden dimension is not supported")
+        return [in_ds[0], in_ds[0]]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        a = op.attrs
+        x = vals[0]
+        k = 1
+        res = None
+        if a["has_residual"]:
+            res = vals[k]; k += 1
+        w = vals[k]; k += 1
+        b = vals[k] if a["has_bias"] else None
+        if a["is_rms_norm"]:
+            out = Fn.rms_norm(x, w, a["eps"], res)
+        else:
+            out = Fn.layer_norm(x, w, b, a["eps"], res)
+        if res is not None:
+            return [out[0], out[1]]
+        return [out, x]
+
+
+def rms_norm(x, residual, weight, bias=None, is_rms_norm: bool = True, eps: float = 1e-6,
+             device_group_hierarchy=None, name=None):
+    """Fused (residual add +) RMSNorm / LayerNorm.  Returns (y, x + residual)."""
+    ins = [x] + ([residual] if residual is not None else []) + [weight] + ([bias] if bias is not None else [])
+    attrs = {"has_residual": residual is not None, "has_bias": bias is not None, "is_rms_norm": is_rms_norm,
+             "eps": eps}
+    return make_op_front("rms_norm", ins, attrs, name, device_group_hierarchy)
+
+
+def fused_layernorm(x, weight, bias, normalized_shape=None, eps: float = 1e-5, device_group_hierarchy=None, name=None):
+    return rms_norm(x, None, weight, bias, is_rms_norm=False, eps=eps, device_group_hierarchy=device_group_hierarchy,
+                    name=name)
+
+
+layer_norm = fused_layernorm
+
+
+@register("swiglu")
+class _Swiglu:
+    @staticmethod
+    def infer(inputs, attrs):
+        x = inputs[0]
+        return [(list(x.symbolic_shape[:-1]) + [x.symbolic_shape[-1] / 2], x.dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [Fn.swiglu(vals[0])]
+
+
+def swiglu(x, name=None):
+    return make_op_front("swiglu", [x], {}, name)[0]
+
+
+@register("rotary_qkv")
+class _RotaryQkv:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        qkv, pos = vals
+        heads_local = op.attrs["heads"] // op.inputs[0].ds(rt.strategy_id).get_dim(op.inputs[0].ndim - 1)
+        return [Fn.rope_qkv(qkv, pos.reshape(-1), heads_local, op.attrs["head_dim"], op.attrs.get("max_pos"),
+                            op.attrs.get("base", 10000.0))]
+
+
+def rotary_qkv(qkv, position_ids, heads: int, head_dim: int, max_pos: int | None = None, base: float = 10000.0,
+               name=None):
+    """RoPE applied in place to q and k of the packed projection [T, heads*3*hd] (split over heads)."""
+    return make_op_front("rotary_qkv", [qkv, position_ids],
+                 {"heads": heads, "head_dim": head_dim, "max_pos": max_pos, "base": base}, name)[0]
+
+
+@register("rotary")
+class _Rotary:
+    """Generic rotary on a [.., seq, heads, hd]-like tensor with explicit cos/sin tables."""
+
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        x, c, s = vals
+        hd = x.shape[-1]
+        rot = c.shape[-1] * 2
+        x1, x2 = x[..., : rot // 2].float(), x[..., rot // 2: rot].float()
+        shape = [1] * (x.dim() - 1) + [rot // 2]
+        shape[-3] = c.shape[0]
+        c, s = c.float().reshape(shape), s.float().reshape(shape)
+        if op.attrs["interleaved"]:
+            raise NotImplementedError("interleaved rotary is not implemented")
+        out = torch.cat([x1 * c - x2 * s, x1 * s + x2 * c, x[..., rot:hd].float()], dim=-1)
+        return [out.to(x.dtype)]
+
+
+def rotary(x, cos, sin, interleaved: bool = False, inplace: bool = False, name=None):
+    return make_op_front("rotary", [x, cos, sin], {"interleaved": interleaved}, name)[0]
+
+
+@register("attn_packed")
+class _AttnPacked:
+    @staticmethod
+    def infer(inputs, attrs):
+        qkv = inputs[0]
+        return [([qkv.symbolic_shape[0], qkv.symbolic_shape[1] / 3], qkv.dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        qkv, cu = vals[0], vals[1]
+        heads_local = op.attrs["heads"] // op.inputs[0].ds(rt.strategy_id).get_dim(1)
+        return [attention_varlen(qkv, cu.reshape(-1).to(torch.int32), heads_local, op.attrs["head_dim"],
+                                 op.attrs.get("max_seqlen"), op.attrs.get("scale"))]
+
+
+def attn_packed(qkv, cu_seqlens, heads: int, head_dim: int, scale: float | None = None, name=None):
+    """Varlen causal attention on the packed projection [T, heads*3*hd]; heads may be split (tp)."""
+    return make_op_front("attn_packed", [qkv, cu_seqlens], {"heads": heads, "head_dim": head_dim, "scale": scale}, name)[0]
+
+
+@register("attn")
+class _Attn:
+    """q, k, v of shape [b, s, heads, hd]; causal softmax attention per batch row (reference ht.attn)."""
+
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        q, k, v = vals
+        b, s, h, d = q.shape
+        qkv = torch.stack([q, k, v], dim=3).reshape(b * s, h, 3 * d)
+        cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32, device=q.device)
+        scale = op.attrs["scale"]
+        out = attention_varlen(qkv, cu, h, d, s, None if (scale is None or scale <= 0) else scale)
+        return [out.reshape(b, s, h, d)]
+
+
+def attn(q, k, v, p_dropout: float = 0.0, softmax_scale: float = -1.0, is_causal: bool = True,
+         return_softmax: bool = False, name=None):
+    if not is_causal:
+        raise NotImplementedError("only causal attention is implemented")
+    return make_op_front("attn", [q, k, v], {"scale": softmax_scale}, name)
+
+
+@register("embedding_lookup")
+class _Embedding:
+    @staticmethod
+    def infer(inputs, attrs):
+        table, ids = inputs
+        return [(list(ids.symbolic_shape) + [table.symbolic_shape[1]], table.dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        tds, ids = in_ds
+        n = tds.device_num
+        vsplit = tds.get_dim(0)
+        if tds.get_dim(1) > 1:
+            raise ValueError("embedding table split along the hidden dimension is not supported")
+        states = {d: c for d, c in ids.states.items() if d >= 0}
+        states[-2] = vsplit
+        states[-1] = n // (vsplit * math.prod(states.get(d, 1) for d in states if d >= 0))
+        order = []
+        for o in ids.order:
+            if o >= 0:
+                order.append(o)
+            elif o == -1:
+                if vsplit > 1:
+                    order.append(-2)
+                if states[-1] > 1:
+                    order.append(-1)
+        for o in (-2, -1):
+            if states.get(o, 1) > 1 and o not in order:
+                order.append(o)
+        return [DistributedStates(n, states, order)]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        table, ids = vals
+        tds = op.inputs[0].ds(rt.strategy_id)
+        vstart = 0
+        if tds.get_dim(0) > 1:
+            idx = rt.device_index_of(op.inputs[0])
+            vstart = tds.map_device_to_state_index(idx).get(0, 0) * table.shape[0]
+        return [Fn.embedding(table, ids, vstart)]
+
+
+def embedding_lookup(table, ids, multi_offset=None, device_group_hierarchy=None, name=None):
+    return make_op_front("embedding_lookup", [table, ids], {}, name, device_group_hierarchy)[0]
+
+
+@register("vocab_parallel_cross_entropy")
+class _VocabCE:
+    @staticmethod
+    def infer(inputs, attrs):
+        logits = inputs[0]
+        if attrs["reduction"] == "none":
+            return [([logits.symbolic_shape[0]], torch.float32)]
+        return [([IntSymbol(1)], torch.float32)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        lds = in_ds[0]
+        n = lds.device_num
+        rows = lds.get_dim(0)
+        tp = lds.get_dim(1)
+        if attrs["reduction"] == "none":
+            states = {0: rows, -1: n // rows}
+            order = [o if o != 1 else -1 for o in lds.order]
+        else:
+            # a per-replica loss: every data-parallel replica holds the loss of its own rows
+            states = {0: rows, -1: n // rows}
+            order = [o if o != 1 else -1 for o in lds.order]
+        seen, od = set(), []
+        for o in order:
+            if states.get(o, 1) > 1 and o not in seen:
+                od.append(o); seen.add(o)
+        del tp
+        return [DistributedStates(n, states, od)]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        logits, labels = vals
+        lds = op.inputs[0].ds(rt.strategy_id)
+        tp = lds.get_dim(1)
+        vstart, group, combine = 0, None, None
+        if tp > 1:
+            idx = rt.device_index_of(op.inputs[0])
+            vstart = lds.map_device_to_state_index(idx).get(1, 0) * logits.shape[1]
+            group = rt.group_by_dim(op.inputs[0], 1)
+            combine = rt.combine_ce_stats
+        loss_rows = Fn.cross_entropy_rows(logits, labels.reshape(-1), op.attrs["ignored_index"], vstart, group, combine)
+        red = op.attrs["reduction"]
+        if red == "none":
+            return [loss_rows]
+        if red == "sum":
+            return [loss_rows.sum().reshape(1)]
+        valid = (labels.reshape(-1) != op.attrs["ignored_index"]).sum().clamp(min=1)
+        return [(loss_rows.sum() / valid).reshape(1)]
+
+
+def vocab_parallel_cross_entropy(logits, labels, ignored_index: int = -1, reduction: str = "mean", name=None):
+    return make_op_front("vocab_parallel_cross_entropy", [logits, labels],
+                 {"ignored_index": ignored_index, "reduction": reduction}, name)[0]
+
+
+softmax_cross_entropy_sparse = vocab_parallel_cross_entropy
+
+
+# ---------------------------------------------------------------------------------------------
+# communication: reshard `x` to a destination DS hierarchy (and device groups)
+# ---------------------------------------------------------------------------------------------
+@register("comm")
+class _Comm:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        raise RuntimeError("comm ops take their output DS from the call site")
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [rt.comm(op, vals[0])]
+
+
+def comm(x, dst_ds_hierarchy, dst_dg_hierarchy=None, name=None):
+    """Reshard to `dst_ds_hierarchy` (one DistributedStatesUnion per strategy), optionally onto other
+    device groups (pipeline stage boundary).  The executor picks the collective per strategy."""
+    g = x.graph
+    return g.make_comm_op(x, list(dst_ds_hierarchy), dst_dg_hierarchy, name)
+
+
+# ---------------------------------------------------------------------------------------------
+# misc
+# ---------------------------------------------------------------------------------------------
+@register("group")
+class _Group:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [([IntSymbol(1)], torch.float32)]
+
+    @staticmethod
+    def deduce(in_ds, attrs, inputs):
+        return [in_ds[0]] if in_ds else [_dup_ds(1)]
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [torch.zeros(1)]
+
+
+def group(tensors, name=None):
+    return make_op_front("group", list(tensors), {}, name)[0]
+
+
+@register("where")
+class _Where:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[1].symbolic_shape, inputs[1].dtype)]
+    deduce = _same_as_input(1)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [torch.where(vals[0].bool(), vals[1], vals[2])]
+
+
+def where(cond, a, b, name=None):
+    return make_op_front("where", [cond, a, b], {}, name)[0]
+
+
+@register("cast")
+class _Cast:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, attrs["dtype"])]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [vals[0].to(op.attrs["dtype"])]
+
+
+def cast(x, dtype, name=None):
+    return make_op_front("cast", [x], {"dtype": dtype}, name)[0]
+
+
+data_transfer = cast
+
+
+@register("mse_loss")
+class _Mse:
+    @staticmethod
+    def infer(inputs, attrs):
+        return [([IntSymbol(1)], torch.float32)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        return [torch.nn.functional.mse_loss(vals[0].float(), vals[1].float(), reduction=op.attrs["reduction"]).reshape(1)]
+
+
+def mse_loss(pred, target, reduction="mean", name=None):
+    return make_op_front("mse_loss", [pred, target], {"reduction": reduction}, name)[0]
+
+
+def ones_like(x, name=None):
+    return add(mul(x, 0.0), 1.0)
+
+
+def zeros_like(x, name=None):
+    return mul(x, 0.0)

@@ -1,0 +1,149 @@
+"""Graph tensors and ops of the define-and-run graph.
+
+A :class:`Tensor` is symbolic: it carries a symbolic global shape, a dtype and, for every parallel
+strategy of the graph, a distributed-states union plus the device groups it lives on.  Concrete
+per-rank values only exist inside an executor run.
+Reference counterparts: hetu/graph/tensor.h (TensorDef), hetu/graph/operator.h (OpDef).
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Any
+
+import numpy as np
+import torch
+
+from ..core import DistributedStates, DistributedStatesUnion, IntSymbol, sym_value
+
+float32, float16, bfloat16, int64, int32, bool_ = (torch.float32, torch.float16, torch.bfloat16, torch.int64,
+                                                    torch.int32, torch.bool)
+
+_tensor_ids = itertools.count()
+_op_ids = itertools.count()
+
+
+def as_symbol(x) -> IntSymbol:
+    return x if isinstance(x, IntSymbol) else IntSymbol(int(x))
+
+
+class Op:
+    def __init__(self, op_type: str, inputs: list["Tensor"], attrs: dict[str, Any], name: str | None, graph):
+        self.id = next(_op_ids)
+        self.type = op_type
+        self.inputs = inputs
+        self.attrs = attrs
+        self.name = name or f"{op_type}_{self.id}"
+        self.outputs: list[Tensor] = []
+        self.graph = graph
+        self.recompute_scope = graph.current_recompute_scope() if graph is not None else None
+
+    def __repr__(self) -> str:
+        return f"Op({self.name}: {self.type})"
+
+
+class Tensor:
+    def __init__(self, graph, symbolic_shape, dtype, ds_hierarchy, dg_hierarchy, producer: Op | None = None,
+                 name: str | None = None, requires_grad: bool = False):
+        self.id = next(_tensor_ids)
+        self.graph = graph
+        self.symbolic_shape = [as_symbol(s) for s in symbolic_shape]
+        self.dtype = dtype
+        self.ds_hierarchy: list[DistributedStatesUnion] = list(ds_hierarchy)
+        self.dg_hierarchy = list(dg_hierarchy)          # per strategy: list[DeviceGroup]
+        self.producer = producer
+        self.name = name or (f"{producer.name}:out" if producer is not None else f"tensor_{self.id}")
+        self.requires_grad = requires_grad
+        self.is_parameter = False
+        self.is_placeholder = False
+
+    # ---- shapes ---------------------------------------------------------------------------
+    @property
+    def ndim(self) -> int:
+        return len(self.symbolic_shape)
+
+    @property
+    def global_shape(self) -> list[int]:
+        return [sym_value(s) for s in self.symbolic_shape]
+
+    def local_shape(self, strategy_id: int | None = None, member: int = 0) -> list[int]:
+        ds = self.ds(strategy_id, member)
+        return [g // ds.get_dim(d) for d, g in enumerate(self.global_shape)]
+
+    @property
+    def shape(self) -> list[int]:
+        return self.local_shape()
+
+    # ---- distributed states ----------------------------------------------------------------
+    def ds(self, strategy_id: int | None = None, member: int = 0) -> DistributedStates:
+        sid = self.graph.cur_strategy_id if strategy_id is None else strategy_id
+        union = self.ds_hierarchy[sid]
+        return union.get(min(member, union.size() - 1))
+
+    @property
+    def distributed_states(self) -> DistributedStates:
+        return self.ds()
+
+    def check_ds_hierarchy_equal(self, other_hierarchy) -> bool:
+        if len(other_hierarchy) != len(self.ds_hierarchy):
+            return False
+        return all(a.check_equal(b) for a, b in zip(self.ds_hierarchy, other_hierarchy))
+
+    def get_device_group_union(self, strategy_id: int | None = None):
+        sid = self.graph.cur_strategy_id if strategy_id is None else strategy_id
+        return self.dg_hierarchy[sid]
+
+    # ---- sugar -----------------------------------------------------------------------------
+    def reshape(self, shape, name=None):
+        from . import ops
+        return ops.reshape(self, shape, name=name)
+
+    def transpose(self, perm, name=None):
+        from . import ops
+        return ops.transpose(self, perm, name=name)
+
+    def __add__(self, o):
+        from . import ops
+        return ops.add(self, o)
+
+    __radd__ = __add__
+
+    def __sub__(self, o):
+        from . import ops
+        return ops.sub(self, o)
+
+    def __rsub__(self, o):
+        from . import ops
+        return ops.add(ops.neg(self), o)
+
+    def __mul__(self, o):
+        from . import ops
+        return ops.mul(self, o)
+
+    __rmul__ = __mul__
+
+    def __truediv__(self, o):
+        from . import ops
+        return ops.div(self, o)
+
+    def __neg__(self):
+        from . import ops
+        return ops.neg(self)
+
+    # ---- data access (parameters / constants) ---------------------------------------------------
+    def get_data(self):
+        """Local value of a parameter / constant on this rank as numpy (after materialisation)."""
+        return self.graph.get_local_data(self)
+
+    def numpy(self, force: bool = True):
+        return self.get_data()
+
+    def reset_data(self, array: np.ndarray) -> None:
+        """Overwrite a parameter from a *global* numpy array (sliced by the current strategy-0 DS)."""
+        self.graph.reset_param_data(self, array)
+
+    def __repr__(self) -> str:
+        try:
+            shp = self.global_shape
+        except Exception:
+            shp = "?"
+        return f"Tensor({self.name}, global_shape={shp}, dtype={self.dtype})"

@@ -1,0 +1,172 @@
+"""Llama (RMSNorm, RoPE, SwiGLU, varlen causal attention) defined once over N parallel strategies.
+
+Activations are token-major 2-D tensors [T, h]; between blocks they are sequence-parallel (split over
+every device of the stage), the column-parallel projections all-gather them, the row-parallel ones
+reduce-scatter their partial outputs.  Residual adds are folded into the following RMSNorm.
+Reference model: hotspa/hetu_llama_multi_ds_parallel_symbolic_sp.py (which trains LayerNorm + no RoPE +
+plain causal attention over the packed row; ``LlamaConfig(reference_parity=True)`` reproduces that variant).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import hetu as ht
+
+from ..parallel.strategy_config import get_multi_ds_parallel_config
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    ffn_hidden_size: int = 11008
+    num_layers: int = 32
+    num_heads: int = 32
+    max_seq_len: int = 32768
+    rms_eps: float = 1e-6
+    rope_base: float = 10000.0
+    reference_parity: bool = False     # LayerNorm with bias, no RoPE (the reference's "LLaMA")
+    recompute: bool = False            # re-run each block in backward instead of keeping activations
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_heads
+
+
+PRESETS = {
+    "tiny": dict(num_layers=2, hidden_size=256, ffn_hidden_size=688, num_heads=4, vocab_size=1000),
+    "3b": dict(num_layers=16, hidden_size=2048, ffn_hidden_size=5120, num_heads=32),
+    "7b": dict(num_layers=32, hidden_size=4096, ffn_hidden_size=11008, num_heads=32),
+    "13b": dict(num_layers=40, hidden_size=5120, ffn_hidden_size=13824, num_heads=40),
+    "32b": dict(num_layers=60, hidden_size=6656, ffn_hidden_size=17920, num_heads=52),
+}
+
+
+def llama_config(size: str, **overrides) -> LlamaConfig:
+    kw = dict(PRESETS[size])
+    kw.update(overrides)
+    return LlamaConfig(**kw)
+
+
+def _norm(config, cfgs, name):
+    if config.reference_parity:
+        return ht.nn.HtMultiParallelLayerNorm(config.hidden_size, cfgs, sp=True, name=name)
+    return ht.nn.HtMultiParallelRMSNorm(config.hidden_size, cfgs, sp=True, eps=config.rms_eps, name=name)
+
+
+class LlamaAttention(ht.nn.Module):
+    def __init__(self, config: LlamaConfig, ds_parallel_configs, layer_idx: int, name="attn"):
+        super().__init__()
+        self.config = config
+        h = config.hidden_size
+        init = "normal_"
+        self.qkv_dense = ht.nn.HtMultiColumnParallelLinear(
+            h, 3 * h, get_multi_ds_parallel_config(ds_parallel_configs, "qkv", layer_idx), bias=False,
+            gather_output=False, init_method=init, name=f"colp_{name}")
+        self.dense = ht.nn.HtMultiRowParallelLinear(
+            h, h, get_multi_ds_parallel_config(ds_parallel_configs, "dense", layer_idx), sp=True, bias=False,
+            init_method=init, name=f"rowp_{name}")
+
+    def forward(self, x, position_ids, cu_seqlens):
+        c = self.config
+        qkv = self.qkv_dense(x)                                   # [T, 3h / tp], per head: q | k | v
+        if not c.reference_parity:
+            qkv = ht.rotary_qkv(qkv, position_ids, c.num_heads, c.head_dim, c.max_seq_len + 1, c.rope_base)
+        ctx = ht.attn_packed(qkv, cu_seqlens, c.num_heads, c.head_dim)   # [T, h / tp]
+        return self.dense(ctx)                                    # partial -> reduce-scatter -> [T / tp, h]
+
+
+class LlamaMLP(ht.nn.Module):
+    def __init__(self, config: LlamaConfig, ds_parallel_configs, layer_idx: int, name="mlp"):
+        super().__init__()
+        h, f = config.hidden_size, config.ffn_hidden_size
+        self.dense_h_to_4h = ht.nn.HtMultiColumnParallelLinear(
+            h, 2 * f, get_multi_ds_parallel_config(ds_parallel_configs, "dense_h_to_4h", layer_idx), bias=False,
+            gather_output=False, init_method="normal_", name=f"colp_{name}")
+        self.dense_4h_to_h = ht.nn.HtMultiRowParallelLinear(
+            f, h, get_multi_ds_parallel_config(ds_parallel_configs, "dense_4h_to_h", layer_idx), sp=True, bias=False,
+            init_method="normal_", name=f"rowp_{name}")
+
+    def forward(self, x):
+        return self.dense_4h_to_h(ht.swiglu(self.dense_h_to_4h(x)))
+
+
+class LlamaBlock(ht.nn.Module):
+    def __init__(self, config: LlamaConfig, ds_parallel_configs, layer_idx: int):
+        super().__init__()
+        self.config, self.layer_idx = config, layer_idx
+        self.rmsnorm_1 = _norm(config, get_multi_ds_parallel_config(ds_parallel_configs, "layernorm1", layer_idx),
+                               f"rmsnorm1_block{layer_idx}")
+        self.attn = LlamaAttention(config, ds_parallel_configs, layer_idx, name=f"attn_block{layer_idx}")
+        self.rmsnorm_2 = _norm(config, get_multi_ds_parallel_config(ds_parallel_configs, "layernorm2", layer_idx),
+                               f"rmsnorm2_block{layer_idx}")
+        self.mlp = LlamaMLP(config, ds_parallel_configs, layer_idx, name=f"mlp_block{layer_idx}")
+
+    def groups(self):
+        return self.rmsnorm_1.device_group_unions
+
+    def forward(self, x, residual, position_ids, cu_seqlens):
+        """x (+ residual) is the block input; returns (mlp_out, residual_out) with the final add left to the
+        next norm."""
+        if residual is None:
+            n1, h = self.rmsnorm_1(x), x
+        else:
+            n1, h = self.rmsnorm_1(x, residual)
+        a = self.attn(n1, position_ids, cu_seqlens)
+        n2, h2 = self.rmsnorm_2(a, h)
+        return self.mlp(n2), h2
+
+
+class LlamaModel(ht.nn.Module):
+    def __init__(self, config: LlamaConfig, ds_parallel_configs):
+        super().__init__()
+        self.config = config
+        self.wte = ht.nn.HtMultiVocabParallelEmbedding(
+            config.vocab_size, config.hidden_size, get_multi_ds_parallel_config(ds_parallel_configs, "wte"),
+            init_method="normal_", name="wte")
+        self.h = ht.nn.ModuleList([LlamaBlock(config, ds_parallel_configs, i) for i in range(config.num_layers)])
+        self.rmsnorm_f = _norm(config, get_multi_ds_parallel_config(ds_parallel_configs, "layernorm_final"),
+                               "rmsnorm_final")
+
+    def forward(self, input_ids, position_ids, cu_seqlens):
+        c = self.config
+        x = self.wte(input_ids)                                   # [b, s, h] (partial over tp when vocab-parallel)
+        x = x.reshape([c.mbs_times_dp_symbol * c.seq_len_symbol, ht.IntSymbol(c.hidden_size)])
+        residual = None
+        prev_groups = None
+        for block in self.h:
+            groups = block.groups()
+            crosses = prev_groups is not None and any(
+                [g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, groups))
+            if crosses and residual is not None:
+                x, residual = x + residual, None                  # one tensor crosses the stage boundary
+            x = ht.comm(x, block.rmsnorm_1.ds_union_map["split0"], groups, name=f"pipeline_layer_{block.layer_idx}_comm")
+            if c.recompute:
+                with ht.recompute():
+                    x, residual = block(x, residual, position_ids, cu_seqlens)
+            else:
+                x, residual = block(x, residual, position_ids, cu_seqlens)
+            prev_groups = groups
+        fin_groups = self.rmsnorm_f.device_group_unions
+        if any([g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, fin_groups)):
+            x, residual = x + residual, None
+            x = ht.comm(x, self.rmsnorm_f.ds_union_map["split0"], fin_groups, name="pipeline_final_comm")
+        return self.rmsnorm_f(x, residual)[0] if residual is not None else self.rmsnorm_f(x)
+
+
+class LlamaLMHeadModel(ht.nn.Module):
+    def __init__(self, config: LlamaConfig, ds_parallel_configs):
+        super().__init__()
+        self.config = config
+        self.transformer = LlamaModel(config, ds_parallel_configs)
+        self.lm_head = ht.nn.HtMultiColumnParallelLinear(
+            config.hidden_size, config.vocab_size, get_multi_ds_parallel_config(ds_parallel_configs, "lm_head"),
+            bias=False, gather_output=False, init_method="normal_", name="lm_head")
+
+    def forward(self, input_ids, position_ids, cu_seqlens, labels=None, reduction: str = "mean"):
+        hidden = self.transformer(input_ids, position_ids, cu_seqlens)    # [T / tp, h]
+        logits = self.lm_head(hidden)                                     # all-gather -> [T, V / tp]
+        if labels is None:
+            return logits
+        return ht.vocab_parallel_cross_entropy(logits, labels, ignored_index=-1, reduction=reduction)

@@ -1,0 +1,135 @@
+"""torch-like Module system over graph tensors (reference: python_refactor/hetu/nn/modules/module.py)."""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import numpy as np
+
+from ..graph.tensor import Tensor
+
+
+class Module:
+    def __init__(self):
+        object.__setattr__(self, "_parameters", OrderedDict())
+        object.__setattr__(self, "_modules", OrderedDict())
+        object.__setattr__(self, "_buffers", OrderedDict())
+        object.__setattr__(self, "training", True)
+
+    def __setattr__(self, name, value):
+        if isinstance(value, Tensor) and value.is_parameter:
+            self._parameters[name] = value
+        elif isinstance(value, Module):
+            self._modules[name] = value
+        object.__setattr__(self, name, value)
+
+    def register_buffer(self, name, tensor):
+        self._buffers[name] = tensor
+        object.__setattr__(self, name, tensor)
+
+    def add_module(self, name, module):
+        self._modules[name] = module
+        object.__setattr__(self, name, module)
+
+    def __call__(self, *args, **kwargs):
+        return self.forward(*args, **kwargs)
+
+    def forward(self, *args, **kwargs):
+        raise NotImplementedError
+
+    def named_parameters(self, prefix: str = "", recurse: bool = True):
+        for n, p in self._parameters.items():
+            if p is not None:
+                yield (prefix + n, p)
+        if recurse:
+            for mn, m in self._modules.items():
+                if m is not None:
+                    yield from m.named_parameters(prefix + mn + ".", True)
+
+    def parameters(self, recurse: bool = True):
+        for _, p in self.named_parameters(recurse=recurse):
+            yield p
+
+    def named_modules(self, prefix: str = ""):
+        yield prefix.rstrip("."), self
+        for mn, m in self._modules.items():
+            if m is not None:
+                yield from m.named_modules(prefix + mn + ".")
+
+    def children(self):
+        return iter(m for m in self._modules.values() if m is not None)
+
+    def train(self, mode: bool = True):
+        object.__setattr__(self, "training", mode)
+        for m in self.children():
+            m.train(mode)
+        return self
+
+    def eval(self):
+        return self.train(False)
+
+    def state_dict(self, format: str = "numpy", prefix: str = ""):
+        """name -> local value ('numpy') or graph tensor ('hetu')."""
+        out = OrderedDict()
+        for n, p in self.named_parameters(prefix):
+            out[n] = p.get_data() if format == "numpy" else p
+        return out
+
+    def load_state_dict(self, state_dict, local_device=None, strict: bool = True):
+        """Values are *global* arrays; every rank keeps the slice its distributed states assign to it."""
+        own = dict(self.named_parameters())
+        missing = [k for k in own if k not in state_dict]
+        unexpected = [k for k in state_dict if k not in own]
+        if strict and (missing or unexpected):
+            raise KeyError(f"load_state_dict: missing {missing}, unexpected {unexpected}")
+        for k, p in own.items():
+            if k in state_dict:
+                arr = state_dict[k]
+                arr = arr.detach().float().cpu().numpy() if hasattr(arr, "detach") else np.asarray(arr)
+                if list(arr.shape) != list(p.global_shape):
+                    raise ValueError(f"{k}: checkpoint shape {list(arr.shape)} != global shape {p.global_shape}")
+                p.reset_data(arr)
+        return missing, unexpected
+
+
+class ModuleList(Module):
+    def __init__(self, modules=None):
+        super().__init__()
+        for m in (modules or []):
+            self.append(m)
+
+    def append(self, module):
+        self.add_module(str(len(self._modules)), module)
+        return self
+
+    def __len__(self):
+        return len(self._modules)
+
+    def __iter__(self):
+        return iter(self._modules.values())
+
+    def __getitem__(self, i):
+        return list(self._modules.values())[i]
+
+
+class Sequential(ModuleList):
+    def forward(self, x):
+        for m in self:
+            x = m(x)
+        return x
+
+
+class Dropout(Module):
+    def __init__(self, p: float = 0.0):
+        super().__init__()
+        self.p = p
+
+    def forward(self, x):
+        if self.p <= 0:
+            return x
+        from ..graph import ops
+        return ops.dropout(x, self.p)
+
+
+class Identity(Module):
+    def forward(self, x):
+        return x

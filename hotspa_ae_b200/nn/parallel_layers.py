@@ -1,0 +1,296 @@
+"""Multi-strategy tensor/sequence-parallel layers.
+
+Each layer takes one JSON leaf per strategy (``{"split": {dim: [n]}, "dup": [n], "device_group_union":
+[[ranks]], "type": "variable"|"placeholder", "zero": bool}``), turns it into a DistributedStatesUnion +
+device groups with :func:`config2ds`, creates its parameters with one DS per strategy and exposes the
+layouts it consumes/produces as ``ds_union_map`` (keys 'dup', 'split0', 'split0_dup', 'dup_split0',
+'split01', ...).  Interface parity with python_refactor/hetu/nn/modules/parallel_multi_ds.py.
+"""
+from __future__ import annotations
+
+import numbers
+
+import numpy as np
+
+from .. import core as C
+from ..graph import graph as G
+from ..graph import init as I
+from ..graph import ops as O
+from ..graph.tensor import float32
+from ..parallel import mesh as M
+from .module import Module
+
+DS, DSU = C.DistributedStates, C.DistributedStatesUnion
+
+
+def get_local_index(device_group_union):
+    """(index of the union member holding this rank, index of the rank inside it) or (-1, -1)."""
+    local = M.local_device()
+    for gi, group in enumerate(device_group_union):
+        if group.contains(local):
+            return gi, group.get_index(local)
+    return -1, -1
+
+
+def config2ds(config):
+    """JSON leaf -> (DistributedStatesUnion, [DeviceGroup])."""
+    kind = config["type"]
+    if kind not in ("placeholder", "variable"):
+        raise RuntimeError(f"unsupported type {kind}!")
+    hetero_sum = len(config["device_group_union"])
+    hetero_dim = -3 if hetero_sum == 1 else (0 if kind == "placeholder" else -1)
+    ds_list, dg_list = [], []
+    for h in range(hetero_sum):
+        n = len(config["device_group_union"][h]) * hetero_sum
+        split = {int(k): v[h] for k, v in config["split"].items()}
+        states = {-1: config["dup"][h], **split}
+        if kind == "placeholder":
+            order, zero = sorted(split) + [-1], False
+        else:
+            order = [-1] + sorted(split)
+            if "zero" not in config:
+                raise AssertionError("variable config must have zero!")
+            zero = bool(config["zero"])
+        ds_list.append(DS(n, states, order, zero))
+        dg_list.append(M.DeviceGroup(config["device_group_union"][h]))
+    return DSU(ds_list, hetero_dim), dg_list
+
+
+def parallel_data_provider(global_data, ds_union, device_group_index, device_index):
+    """Slice of a global numpy array that `device_index` of union member `device_group_index` holds."""
+    ds = ds_union.get_local(device_group_index)
+    local_map = C.map_to_local_data(ds, device_index)
+    out = global_data
+    for dim in ds.order:
+        if dim < 0:
+            continue
+        n = ds.states[dim]
+        k = local_map[dim]
+        size = global_data.shape[dim] // n
+        out = out.take(range(k * size, (k + 1) * size), axis=dim)
+    return out
+
+
+def parallel_multi_data_provider(global_data, ds_unions, device_group_unions):
+    outs = []
+    for ds_union, dgu in zip(ds_unions, device_group_unions):
+        gi, di = get_local_index(dgu)
+        outs.append(parallel_data_provider(global_data, ds_union, max(gi, 0), max(di, 0)))
+    return outs
+
+
+def _init(name: str):
+    return getattr(I, f"{name}initializer")()
+
+
+class _NormBase(Module):
+    def __init__(self, normalized_shape, multi_ds_parallel_config, sp, eps, dtype, name, with_bias):
+        super().__init__()
+        if isinstance(normalized_shape, numbers.Integral):
+            normalized_shape = [normalized_shape]
+        self.normalized_shape = list(normalized_shape)
+        self.sp, self.eps, self.name = sp, eps, name
+        self.ds_union_map = {"dup": [], "split0": []}
+        self.device_index, self.device_group_unions = [], []
+        for cfg in multi_ds_parallel_config:
+            ds_dup, dgu = config2ds(cfg)
+            self.device_group_unions.append(dgu)
+            hs, hd = len(dgu), ds_dup.hetero_dim
+            assert hd in (-1, -3), "parallel norm only supports hetero on dup"
+            self.device_index.append(get_local_index(dgu)[1])
+            split0 = [DS(dgu[i].num_devices * hs, {0: dgu[i].num_devices * hs}, [0]) for i in range(hs)]
+            self.ds_union_map["dup"].append(ds_dup)
+            self.ds_union_map["split0"].append(DSU(split0, 0 if hd != -3 else -3))
+        self.weight = G.parallel_parameter(I.ones_initializer(), self.normalized_shape, self.ds_union_map["dup"],
+                                           self.device_index, dtype=dtype, requires_grad=True,
+                                           device_group_hierarchy=self.device_group_unions, name=f"{name}_weight")
+        self.bias = None
+        if with_bias:
+            self.bias = G.parallel_parameter(I.zeros_initializer(), self.normalized_shape, self.ds_union_map["dup"],
+                                             self.device_index, dtype=dtype, requires_grad=True,
+                                             device_group_hierarchy=self.device_group_unions, name=f"{name}_bias")
+
+    def _check(self, x):
+        if self.sp and not x.check_ds_hierarchy_equal(self.ds_union_map["split0"]):
+            raise AssertionError(f"for sequence parallel, norm {self.name} needs its input fully sharded in "
+                                 f"dimension 0, but found {x.ds_hierarchy}")
+
+
+class HtMultiParallelRMSNorm(_NormBase):
+    def __init__(self, normalized_shape, multi_ds_parallel_config, sp=False, eps=1e-6, dtype=float32, name="rmsnorm"):
+        super().__init__(normalized_shape, multi_ds_parallel_config, sp, eps, dtype, name, False)
+
+    def forward(self, x, residual=None):
+        """Returns y, or (y, x + residual) when a residual is given (fused add + norm)."""
+        self._check(x)
+        outs = O.rms_norm(x, residual, self.weight, None, is_rms_norm=True, eps=self.eps,
+                          device_group_hierarchy=self.device_group_unions, name=self.name + ("_sp" if self.sp else ""))
+        return outs[0] if residual is None else (outs[0], outs[1])
+
+
+class HtMultiParallelLayerNorm(_NormBase):
+    def __init__(self, normalized_shape, multi_ds_parallel_config, sp=False, eps=1e-5, dtype=float32, name="ln"):
+        super().__init__(normalized_shape, multi_ds_parallel_config, sp, eps, dtype, name, True)
+
+    def forward(self, x, residual=None):
+        self._check(x)
+        outs = O.rms_norm(x, residual, self.weight, self.bias, is_rms_norm=False, eps=self.eps,
+                          device_group_hierarchy=self.device_group_unions, name=self.name + ("_sp" if self.sp else ""))
+        return outs[0] if residual is None else (outs[0], outs[1])
+
+
+class HtMultiParallelEmbedding(Module):
+    def __init__(self, num_embeddings, embedding_dim, multi_ds_parallel_config, init_method="xavier_normal_",
+                 dtype=float32, name="embedding"):
+        super().__init__()
+        self.num_embeddings, self.embedding_dim, self.name = num_embeddings, embedding_dim, name
+        self.ds_union_map = {"dup": []}
+        self.device_index, self.device_group_unions = [], []
+        for cfg in multi_ds_parallel_config:
+            ds_dup, dgu = config2ds(cfg)
+            self.device_group_unions.append(dgu)
+            self.device_index.append(get_local_index(dgu)[1])
+            self.ds_union_map["dup"].append(ds_dup)
+        self.embedding_table = G.parallel_parameter(_init(init_method), [num_embeddings, embedding_dim],
+                                                    self.ds_union_map["dup"], self.device_index, dtype=dtype,
+                                                    requires_grad=True, device_group_hierarchy=self.device_group_unions,
+                                                    name=f"{name}_table")
+
+    def forward(self, ids):
+        return O.embedding_lookup(self.embedding_table, ids, device_group_hierarchy=self.device_group_unions,
+                                  name=self.name)
+
+
+class HtMultiVocabParallelEmbedding(Module):
+    def __init__(self, num_embeddings, embedding_dim, multi_ds_parallel_config, init_method="xavier_normal_",
+                 dtype=float32, name="vocab_embedding"):
+        super().__init__()
+        self.num_embeddings, self.embedding_dim, self.name = num_embeddings, embedding_dim, name
+        self.ds_union_map = {"split0_dup": [], "dup_split0": []}
+        self.device_index, self.device_group_unions, self.vocab_start_index = [], [], []
+        for cfg in multi_ds_parallel_config:
+            ds_tab, dgu = config2ds(cfg)
+            self.device_group_unions.append(dgu)
+            hs, hd = len(dgu), ds_tab.hetero_dim
+            dp = [ds_tab.get(i).get_dim(-1) for i in range(hs)]
+            tp = [ds_tab.get(i).get_dim(0) for i in range(hs)]
+            assert hd in (-1, -3), "VocabParallelEmbedding only supports hetero on dup"
+            assert all(dp[i] * tp[i] // hs == dgu[i].num_devices for i in range(hs)), \
+                f"VocabParallelEmbedding got a wrong ds_parallel_config: {cfg}!"
+            gi, di = get_local_index(dgu)
+            self.device_index.append(di)
+            data = [DS(dgu[i].num_devices * hs, {-1: tp[i], 0: dp[i]}, [0, -1]) for i in range(hs)]
+            self.ds_union_map["split0_dup"].append(DSU(data, 0 if hd != -3 else -3))
+            self.ds_union_map["dup_split0"].append(ds_tab)
+            start = 0
+            if gi >= 0:
+                start = num_embeddings // tp[gi] * ds_tab.get_local(gi).get_dup_group_index(di)
+            self.vocab_start_index.append(start)
+        self.embedding_table = G.parallel_parameter(_init(init_method), [num_embeddings, embedding_dim],
+                                                    self.ds_union_map["dup_split0"], self.device_index, dtype=dtype,
+                                                    requires_grad=True, device_group_hierarchy=self.device_group_unions,
+                                                    name=f"{name}_table")
+
+    def forward(self, ids):
+        x = ids if ids.check_ds_hierarchy_equal(self.ds_union_map["split0_dup"]) else \
+            O.comm(ids, self.ds_union_map["split0_dup"])
+        out = O.embedding_lookup(self.embedding_table, x, self.vocab_start_index,
+                                 device_group_hierarchy=self.device_group_unions, name=f"{self.name}_{x.name}")
+        if out.check_ds_hierarchy_equal(self.ds_union_map["split0_dup"]):
+            return out
+        return O.comm(out, self.ds_union_map["split0_dup"])
+
+
+class HtMultiColumnParallelLinear(Module):
+    """Y = X A^T, A stored [out, in] and split along out (dim 0) over the tensor-parallel ranks."""
+
+    def __init__(self, in_features, out_features, multi_ds_parallel_config, bias=True, gather_output=True,
+                 init_method="xavier_normal_", dtype=float32, name="colp"):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.gather_output, self.name = gather_output, name
+        self.ds_union_map = {"dup_split0": [], "split0_dup": []}
+        self.device_index, self.device_group_unions = [], []
+        for cfg in multi_ds_parallel_config:
+            ds_cfg, dgu = config2ds(cfg)               # math layout [in, out] split on dim 1
+            self.device_group_unions.append(dgu)
+            zero = cfg["zero"]
+            hs, hd = len(dgu), ds_cfg.hetero_dim
+            dp = [ds_cfg.get(i).get_dim(-1) for i in range(hs)]
+            tp = [ds_cfg.get(i).get_dim(1) for i in range(hs)]
+            assert hd in (-1, -3), "ColumnParallelLinear only supports hetero on dup"
+            assert all(dp[i] * tp[i] // hs == dgu[i].num_devices for i in range(hs)), \
+                f"ColumnParallelLinear got a wrong ds_parallel_config: {cfg}!"
+            self.device_index.append(get_local_index(dgu)[1])
+            w = [DS(dgu[i].num_devices * hs, {-1: dp[i], 0: tp[i]}, [-1, 0], zero) for i in range(hs)]
+            d = [DS(dgu[i].num_devices * hs, {-1: tp[i], 0: dp[i]}, [0, -1]) for i in range(hs)]
+            self.ds_union_map["dup_split0"].append(DSU(w, -1 if hd != -3 else -3))
+            self.ds_union_map["split0_dup"].append(DSU(d, 0 if hd != -3 else -3))
+        self.weight = G.parallel_parameter(_init(init_method), [out_features, in_features],
+                                           self.ds_union_map["dup_split0"], self.device_index, dtype=dtype,
+                                           requires_grad=True, device_group_hierarchy=self.device_group_unions,
+                                           name=f"{name}_weight")
+        self.bias = None
+        if bias:
+            self.bias = G.parallel_parameter(I.zeros_initializer(), [out_features], self.ds_union_map["dup_split0"],
+                                             self.device_index, dtype=dtype, requires_grad=True,
+                                             device_group_hierarchy=self.device_group_unions, name=f"{name}_bias")
+
+    def forward(self, x):
+        if not x.check_ds_hierarchy_equal(self.ds_union_map["split0_dup"]):
+            x = O.comm(x, self.ds_union_map["split0_dup"])            # sequence parallel: all-gather
+        y = O.linear(x, self.weight, self.bias, trans_a=False, trans_b=True,
+                     device_group_hierarchy=self.device_group_unions, name=self.name)
+        if not self.gather_output or y.check_ds_hierarchy_equal(self.ds_union_map["split0_dup"]):
+            return y
+        return O.comm(y, self.ds_union_map["split0_dup"])
+
+
+class HtMultiRowParallelLinear(Module):
+    """Y = X A, A stored [in, out] and split along in (dim 0); the output is partial over the tp ranks and
+    is reduce-scattered (sequence parallel) or all-reduced."""
+
+    def __init__(self, in_features, out_features, multi_ds_parallel_config, sp=False, bias=True,
+                 init_method="xavier_normal_", dtype=float32, name="rowp"):
+        super().__init__()
+        self.in_features, self.out_features, self.name, self.sp = in_features, out_features, name, sp
+        keys = ("dup_split0", "dup_split1", "dup", "split0", "split01", "split0_dup")
+        self.ds_union_map = {k: [] for k in keys}
+        self.device_index, self.device_group_unions = [], []
+        for cfg in multi_ds_parallel_config:
+            ds_w, dgu = config2ds(cfg)
+            self.device_group_unions.append(dgu)
+            zero = cfg["zero"]
+            hs, hd = len(dgu), ds_w.hetero_dim
+            dp = [ds_w.get(i).get_dim(-1) for i in range(hs)]
+            tp = [ds_w.get(i).get_dim(0) for i in range(hs)]
+            assert hd in (-1, -3), "RowParallelLinear only supports hetero on dup"
+            assert all(dp[i] * tp[i] // hs == dgu[i].num_devices for i in range(hs)), \
+                f"RowParallelLinear got a wrong ds_parallel_config: {cfg}!"
+            self.device_index.append(get_local_index(dgu)[1])
+            n = [dgu[i].num_devices * hs for i in range(hs)]
+            mk = lambda f: [f(i) for i in range(hs)]   # noqa: E731
+            hw, hdat = (-1 if hd != -3 else -3), (0 if hd != -3 else -3)
+            self.ds_union_map["dup_split0"].append(ds_w)
+            self.ds_union_map["dup_split1"].append(DSU(mk(lambda i: DS(n[i], {-1: dp[i], 1: tp[i]}, [-1, 1], zero)), hw))
+            self.ds_union_map["dup"].append(DSU(mk(lambda i: DS(n[i], {-1: dp[i] * tp[i]}, [-1], zero)), hw))
+            self.ds_union_map["split0"].append(DSU(mk(lambda i: DS(n[i], {0: dp[i] * tp[i]}, [0])), hdat))
+            self.ds_union_map["split01"].append(DSU(mk(lambda i: DS(n[i], {0: dp[i], 1: tp[i]}, [0, 1])), hdat))
+            self.ds_union_map["split0_dup"].append(DSU(mk(lambda i: DS(n[i], {0: dp[i], -1: tp[i]}, [0, -1])), hdat))
+        self.weight = G.parallel_parameter(_init(init_method), [in_features, out_features],
+                                           self.ds_union_map["dup_split0"], self.device_index, dtype=dtype,
+                                           requires_grad=True, device_group_hierarchy=self.device_group_unions,
+                                           name=f"{name}_weight")
+        self.bias = None
+        if bias:
+            self.bias = G.parallel_parameter(I.zeros_initializer(), [out_features], self.ds_union_map["dup"],
+                                             self.device_index, dtype=dtype, requires_grad=True,
+                                             device_group_hierarchy=self.device_group_unions, name=f"{name}_bias")
+
+    def forward(self, x):
+        if not x.check_ds_hierarchy_equal(self.ds_union_map["split01"]):
+            x = O.comm(x, self.ds_union_map["split01"])
+        y = O.linear(x, self.weight, trans_a=False, trans_b=False, device_group_hierarchy=self.device_group_unions,
+                     name=self.name)
+        y = O.comm(y, self.ds_union_map["split0"] if self.sp else self.ds_union_map["split0_dup"])
+        return y + self.bias if self.bias is not None else y

@@ -1,0 +1,92 @@
+"""Varlen causal attention over packed documents.
+
+Input is the packed projection ``qkv`` of shape [T, heads, 3*hd] (per head: q | k | v, RoPE already
+applied), ``cu_seqlens`` (int32, [ndocs + 1]) marks document boundaries inside the T packed tokens:
+every document attends causally to itself only.  Output: [T, heads*hd].
+
+Backends: ``hsb`` = the tcgen05 flash-attention kernels of this library (GPU), ``torch`` = a
+per-document fp32 softmax reference (CPU tests, numerics oracle).
+Reference counterpart: hetu/graph/ops/Attention.cc + hetu/impl/kernel/FlashAttention.cu, which
+runs FlashAttention-2 with plain causal masking over the whole packed row (no document boundaries).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+
+def _attn_torch_fwd(qkv, cu, heads, hd, scale):
+    T = qkv.shape[0]
+    v4 = qkv.reshape(T, heads, 3, hd).float()
+    out = torch.zeros((T, heads, hd), dtype=torch.float32, device=qkv.device)
+    lse = torch.zeros((heads, T), dtype=torch.float32, device=qkv.device)
+    bounds = cu.tolist()
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if b <= a:
+            continue
+        q, k, v = (v4[a:b, :, i, :].transpose(0, 1) for i in range(3))      # [heads, L, hd]
+        s = torch.matmul(q, k.transpose(1, 2)) * scale
+        L = b - a
+        mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        p = (s - l[..., None]).exp()
+        out[a:b] = torch.matmul(p, v).transpose(0, 1)
+        lse[:, a:b] = l
+    return out, lse
+
+
+class _AttnTorchFn(torch.autograd.Function):
+    """Differentiable fp32 reference (manual backward so it mirrors the kernel's math)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cu, heads, hd, scale):
+        out, lse = _attn_torch_fwd(qkv, cu, heads, hd, scale)
+        ctx.save_for_backward(qkv, cu, out, lse)
+        ctx.heads, ctx.hd, ctx.scale = heads, hd, scale
+        return out.reshape(qkv.shape[0], heads * hd).to(qkv.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, cu, out, lse = ctx.saved_tensors
+        heads, hd, scale = ctx.heads, ctx.hd, ctx.scale
+        T = qkv.shape[0]
+        v4 = qkv.reshape(T, heads, 3, hd).float()
+        do = dout.reshape(T, heads, hd).float()
+        dqkv = torch.zeros((T, heads, 3, hd), dtype=torch.float32, device=qkv.device)
+        delta = (do * out).sum(-1)                                              # [T, heads]
+        bounds = cu.tolist()
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            if b <= a:
+                continue
+            q, k, v = (v4[a:b, :, i, :].transpose(0, 1) for i in range(3))
+            L = b - a
+            s = torch.matmul(q, k.transpose(1, 2)) * scale
+            mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
+            p = (s - lse[:, a:b, None]).exp().masked_fill(~mask, 0.0)
+            dO = do[a:b].transpose(0, 1)
+            dv = torch.matmul(p.transpose(1, 2), dO)
+            dp = torch.matmul(dO, v.transpose(1, 2))
+            ds = p * (dp - delta[a:b].transpose(0, 1)[..., None]) * scale
+            dq = torch.matmul(ds, k)
+            dk = torch.matmul(ds.transpose(1, 2), q)
+            dqkv[a:b, :, 0] = dq.transpose(0, 1)
+            dqkv[a:b, :, 1] = dk.transpose(0, 1)
+            dqkv[a:b, :, 2] = dv.transpose(0, 1)
+        return dqkv.reshape(qkv.shape).to(qkv.dtype), None, None, None, None
+
+
+def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, heads: int, hd: int, max_seqlen: int | None = None,
+                     scale: float | None = None, backend: str | None = None) -> torch.Tensor:
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    T = qkv.shape[0]
+    qkv3 = qkv.reshape(T, heads, 3 * hd)
+    if backend is None:
+        backend = "hsb" if (qkv.is_cuda and qkv.dtype == torch.bfloat16) else "torch"
+    if backend == "hsb":
+        from .flash_attn import flash_attn_varlen
+        return flash_attn_varlen(qkv3, cu_seqlens, heads, hd, max_seqlen, scale)
+    return _AttnTorchFn.apply(qkv3, cu_seqlens, heads, hd, scale)

@@ -1,0 +1,375 @@
+"""Local (single-device) differentiable ops of the Llama step.
+
+Every function dispatches to the sm_100a kernel library when its inputs live on a GPU and to a
+plain PyTorch expression otherwise (the CPU path is what the unit tests of the upper layers and
+the numerics oracles use).  Weight gradients are accumulated straight into the parameter's fp32
+``main_grad`` when one is attached (Megatron-style), so no bf16 ``.grad`` tensors are materialised.
+
+Reference counterparts: hetu/graph/ops/{Linear,RMSNorm,LayerNorm,Rotary,SwiGLU,Attention,
+EmbeddingLookup,VocabParallelCrossEntropyLoss}.cc and their kernels under hetu/impl/kernel/.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .gemm import linear  # noqa: F401  (re-exported)
+
+
+def _cuda(*ts) -> bool:
+    return all(t is None or t.is_cuda for t in ts)
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def main_grad_of(p):
+    return getattr(p, "main_grad", None)
+
+
+def _accumulate_param_grad(p_main_grad, value: torch.Tensor):
+    """Add `value` into an fp32 main grad, or hand it back to autograd when there is none."""
+    if p_main_grad is not None:
+        p_main_grad.add_(value.to(p_main_grad.dtype))
+        return None
+    return value
+
+
+# --------------------------------------------------------------------------------------------
+# RMSNorm / LayerNorm with optional fused residual add
+# --------------------------------------------------------------------------------------------
+_scratch: dict = {}
+
+
+def _norm_scratch(device, n_floats: int) -> torch.Tensor:
+    key = (device.index, "norm")
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < n_floats:
+        buf = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, res, w, b, eps, is_rms, w_mg, b_mg):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        rows = x2.shape[0]
+        ctx.is_rms, ctx.has_res, ctx.w_mg, ctx.b_mg, ctx.shape = is_rms, res is not None, w_mg, b_mg, x.shape
+        if _cuda(x) and x.dtype == torch.bfloat16:
+            x2 = x2.contiguous()
+            r2 = res.reshape(-1, H).contiguous() if res is not None else None
+            wk = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+            bk = None if b is None else (b if b.dtype == torch.bfloat16 else b.to(torch.bfloat16))
+            y = torch.empty_like(x2)
+            h = torch.empty_like(x2) if res is not None else None
+            rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+            mean = None if is_rms else torch.empty(rows, dtype=torch.float32, device=x.device)
+            _lib.check(_lib.lib().hsb_norm_fwd(x2.data_ptr(), _ptr(r2), wk.data_ptr(), _ptr(bk), y.data_ptr(), _ptr(h),
+                                               _ptr(mean), rstd.data_ptr(), rows, H, float(eps), int(is_rms),
+                                               _lib.stream_ptr()), "hsb_norm_fwd")
+            _lib.count_launch()
+            xin = h if h is not None else x2
+            ctx.save_for_backward(xin, wk, mean, rstd)
+            ctx.cuda_path = True
+        else:
+            hsum = x2 if res is None else x2 + res.reshape(-1, H)
+            xf = hsum.float()
+            if is_rms:
+                mean = None
+                rstd = torch.rsqrt(xf.pow(2).mean(-1) + eps)
+                yf = xf * rstd[:, None] * w.float()
+            else:
+                mean = xf.mean(-1)
+                rstd = torch.rsqrt(xf.var(-1, unbiased=False) + eps)
+                yf = (xf - mean[:, None]) * rstd[:, None] * w.float()
+                if b is not None:
+                    yf = yf + b.float()
+            y = yf.to(x.dtype)
+            h = hsum if res is not None else None
+            ctx.save_for_backward(hsum, w, mean, rstd)
+            ctx.cuda_path = False
+        y = y.reshape(x.shape)
+        if res is not None:
+            return y, h.reshape(x.shape)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dh=None):
+        xin, w, mean, rstd = ctx.saved_tensors
+        H = xin.shape[-1]
+        rows = xin.shape[0]
+        dy2 = dy.reshape(-1, H)
+        dh2 = None if dh is None else dh.reshape(-1, H)
+        dw = db = None
+        if ctx.cuda_path:
+            dy2 = dy2.contiguous()
+            if dh2 is not None:
+                dh2 = dh2.contiguous()
+            dx = torch.empty_like(xin)
+            parts = _lib.lib().hsb_norm_bwd_parts(rows, 0)
+            scratch = _norm_scratch(xin.device, parts * 2 * H)
+            acc = ctx.w_mg is not None
+            dw_t = ctx.w_mg if acc else torch.empty(H, dtype=torch.float32, device=xin.device)
+            db_t = None
+            if not ctx.is_rms:
+                db_t = ctx.b_mg if (acc and ctx.b_mg is not None) else torch.empty(H, dtype=torch.float32, device=xin.device)
+            _lib.check(_lib.lib().hsb_norm_bwd(dy2.data_ptr(), xin.data_ptr(), w.data_ptr(), _ptr(mean), rstd.data_ptr(),
+                                               _ptr(dh2), dx.data_ptr(), dw_t.data_ptr(), _ptr(db_t),
+                                               scratch.data_ptr(), rows, H, int(ctx.is_rms), int(acc), 0,
+                                               _lib.stream_ptr()), "hsb_norm_bwd")
+            _lib.count_launch(2)
+            if not acc:
+                dw = dw_t
+                db = db_t
+        else:
+            xf = xin.float()
+            g = dy2.float() * w.float()
+            if ctx.is_rms:
+                xh = xf * rstd[:, None]
+                dxf = rstd[:, None] * (g - xh * (g * xh).mean(-1, keepdim=True))
+            else:
+                xh = (xf - mean[:, None]) * rstd[:, None]
+                dxf = rstd[:, None] * (g - g.mean(-1, keepdim=True) - xh * (g * xh).mean(-1, keepdim=True))
+            if dh2 is not None:
+                dxf = dxf + dh2.float()
+            dx = dxf.to(dy.dtype)
+            dw = _accumulate_param_grad(ctx.w_mg, (dy2.float() * xh).sum(0))
+            if not ctx.is_rms:
+                db = _accumulate_param_grad(ctx.b_mg, dy2.float().sum(0))
+        dx = dx.reshape(ctx.shape)
+        dres = dx if ctx.has_res else None
+        return dx, dres, dw, db, None, None, None, None
+
+
+def rms_norm(x, weight, eps: float = 1e-6, residual=None):
+    """y = rmsnorm(x + residual) * weight.  Returns y, or (y, x + residual) when a residual is given."""
+    return _NormFn.apply(x, residual, weight, None, eps, True, main_grad_of(weight), None)
+
+
+def layer_norm(x, weight, bias, eps: float = 1e-5, residual=None):
+    """LayerNorm with the same residual contract as :func:`rms_norm`."""
+    return _NormFn.apply(x, residual, weight, bias, eps, False, main_grad_of(weight),
+                         main_grad_of(bias) if bias is not None else None)
+
+
+# --------------------------------------------------------------------------------------------
+# RoPE on the packed qkv tensor [T, heads, 3*hd]  (per head: q | k | v)
+# --------------------------------------------------------------------------------------------
+_rope_cache: dict = {}
+
+
+def rope_tables(max_pos: int, hd: int, device, base: float = 10000.0):
+    key = (max_pos, hd, str(device), base)
+    t = _rope_cache.get(key)
+    if t is None:
+        inv = 1.0 / (base ** (torch.arange(0, hd, 2, dtype=torch.float32, device=device) / hd))
+        ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+        t = (ang.cos().contiguous(), ang.sin().contiguous())
+        _rope_cache[key] = t
+    return t
+
+
+def _rope_torch(qkv, pos, cos_t, sin_t, heads, hd, sign):
+    T = qkv.shape[0]
+    v = qkv.reshape(T, heads, 3, hd)
+    c = cos_t[pos.long()][:, None, None, :].to(torch.float32)
+    s = sin_t[pos.long()][:, None, None, :].to(torch.float32) * sign
+    qk = v[:, :, :2, :].float()
+    x1, x2 = qk[..., : hd // 2], qk[..., hd // 2:]
+    rot = torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1).to(qkv.dtype)
+    return torch.cat([rot, v[:, :, 2:, :]], dim=2).reshape(qkv.shape)
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, pos, cos_t, sin_t, heads, hd):
+        ctx.save_for_backward(pos, cos_t, sin_t)
+        ctx.heads, ctx.hd = heads, hd
+        if _cuda(qkv) and qkv.dtype == torch.bfloat16:
+            ctx.mark_dirty(qkv)
+            _lib.check(_lib.lib().hsb_rope_qkv(qkv.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
+                                               qkv.shape[0], heads, hd, 0, _lib.stream_ptr()), "hsb_rope_qkv")
+            _lib.count_launch()
+            return qkv
+        return _rope_torch(qkv, pos, cos_t, sin_t, heads, hd, 1.0)
+
+    @staticmethod
+    def backward(ctx, d):
+        pos, cos_t, sin_t = ctx.saved_tensors
+        if _cuda(d) and d.dtype == torch.bfloat16:
+            d = d.contiguous().clone() if not d.is_contiguous() else d.clone()
+            _lib.check(_lib.lib().hsb_rope_qkv(d.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
+                                               d.shape[0], ctx.heads, ctx.hd, 1, _lib.stream_ptr()), "hsb_rope_qkv")
+            _lib.count_launch()
+            return d, None, None, None, None, None
+        return _rope_torch(d, pos, cos_t, sin_t, ctx.heads, ctx.hd, -1.0), None, None, None, None, None
+
+
+def rope_qkv(qkv, positions, heads: int, hd: int, max_pos: int | None = None, base: float = 10000.0):
+    """Rotate q and k of a packed qkv tensor [T, heads*3*hd] in place; positions: int32 [T]."""
+    T = qkv.shape[0]
+    if max_pos is None:
+        max_pos = 1 << max(12, int(math.ceil(math.log2(max(2, T + 1)))))
+    cos_t, sin_t = rope_tables(max_pos, hd, qkv.device, base)
+    pos = positions.to(torch.int32)
+    flat = qkv.reshape(T, heads * 3 * hd)
+    if not flat.is_contiguous():
+        flat = flat.contiguous()
+    if flat.is_leaf and flat.requires_grad:
+        flat = flat.clone()        # never rotate a leaf in place
+    return _RopeFn.apply(flat, pos, cos_t, sin_t, heads, hd).reshape(qkv.shape)
+
+
+# --------------------------------------------------------------------------------------------
+# SwiGLU: [rows, 2d] -> [rows, d]   (gate = first half, up = second half)
+# --------------------------------------------------------------------------------------------
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        d = x.shape[-1] // 2
+        x2 = x.reshape(-1, 2 * d)
+        ctx.shape = x.shape
+        if _cuda(x) and x.dtype == torch.bfloat16 and d % 8 == 0:
+            x2 = x2.contiguous()
+            out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+            _lib.check(_lib.lib().hsb_swiglu_fwd(x2.data_ptr(), out.data_ptr(), x2.shape[0], d, _lib.stream_ptr()),
+                       "hsb_swiglu_fwd")
+            _lib.count_launch()
+            ctx.cuda_path = True
+        else:
+            g, u = x2[:, :d].float(), x2[:, d:].float()
+            out = (F.silu(g) * u).to(x.dtype)
+            ctx.cuda_path = False
+        ctx.save_for_backward(x2)
+        return out.reshape(*x.shape[:-1], d)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        d = x2.shape[-1] // 2
+        dy2 = dy.reshape(-1, d)
+        if ctx.cuda_path:
+            dy2 = dy2.contiguous()
+            dx = torch.empty_like(x2)
+            _lib.check(_lib.lib().hsb_swiglu_bwd(x2.data_ptr(), dy2.data_ptr(), dx.data_ptr(), x2.shape[0], d,
+                                                 _lib.stream_ptr()), "hsb_swiglu_bwd")
+            _lib.count_launch()
+        else:
+            g, u, dyf = x2[:, :d].float(), x2[:, d:].float(), dy2.float()
+            sg = torch.sigmoid(g)
+            silu = g * sg
+            dx = torch.cat([dyf * u * (sg + silu * (1 - sg)), dyf * silu], dim=-1).to(dy.dtype)
+        return dx.reshape(ctx.shape)
+
+
+def swiglu(x):
+    return _SwigluFn.apply(x)
+
+
+# --------------------------------------------------------------------------------------------
+# Embedding with vocabulary offset (rows outside the local shard give zeros -> partial sum over tp)
+# --------------------------------------------------------------------------------------------
+class _EmbedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, ids, vocab_start, mg):
+        Vloc, H = table.shape
+        flat = ids.reshape(-1).contiguous()
+        ctx.vocab_start, ctx.mg, ctx.tshape = vocab_start, mg, table.shape
+        ctx.save_for_backward(flat)
+        if _cuda(table) and table.dtype == torch.bfloat16 and H % 8 == 0:
+            out = torch.empty((flat.numel(), H), dtype=table.dtype, device=table.device)
+            _lib.check(_lib.lib().hsb_embed_fwd(table.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(), H,
+                                                Vloc, vocab_start, _lib.stream_ptr()), "hsb_embed_fwd")
+            _lib.count_launch()
+            ctx.cuda_path = True
+        else:
+            loc = flat - vocab_start
+            ok = (loc >= 0) & (loc < Vloc)
+            out = table[loc.clamp(0, Vloc - 1)] * ok[:, None].to(table.dtype)
+            ctx.cuda_path = False
+        return out.reshape(*ids.shape, H)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (flat,) = ctx.saved_tensors
+        Vloc, H = ctx.tshape
+        d2 = dout.reshape(-1, H)
+        if ctx.cuda_path:
+            d2 = d2.contiguous()
+            tgt = ctx.mg if ctx.mg is not None else torch.zeros((Vloc, H), dtype=torch.float32, device=dout.device)
+            _lib.check(_lib.lib().hsb_embed_bwd(d2.data_ptr(), flat.data_ptr(), tgt.data_ptr(), flat.numel(), H, Vloc,
+                                                ctx.vocab_start, _lib.stream_ptr()), "hsb_embed_bwd")
+            _lib.count_launch()
+            return (None if ctx.mg is not None else tgt), None, None, None
+        loc = flat - ctx.vocab_start
+        ok = (loc >= 0) & (loc < Vloc)
+        g = torch.zeros((Vloc, H), dtype=torch.float32, device=dout.device)
+        g.index_add_(0, loc[ok], d2[ok].float())
+        return _accumulate_param_grad(ctx.mg, g) if ctx.mg is not None else g.to(dout.dtype), None, None, None
+
+
+def embedding(table, ids, vocab_start: int = 0):
+    return _EmbedFn.apply(table, ids, vocab_start, main_grad_of(table))
+
+
+# --------------------------------------------------------------------------------------------
+# (Vocab-parallel) softmax cross-entropy.  Returns the per-row loss (0 for ignored rows); the
+# gradient overwrites the logits buffer in place on the CUDA path.
+# --------------------------------------------------------------------------------------------
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index, vocab_start, group, combine):
+        rows, V = logits.shape
+        labels = labels.reshape(-1).contiguous()
+        valid = labels != ignore_index
+        cuda_path = _cuda(logits) and logits.dtype == torch.bfloat16 and logits.stride(0) % 8 == 0 and logits.stride(1) == 1
+        if cuda_path:
+            stats = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
+            _lib.check(_lib.lib().hsb_ce_stats(logits.data_ptr(), labels.data_ptr(), stats.data_ptr(), rows, V,
+                                               logits.stride(0), vocab_start, _lib.stream_ptr()), "hsb_ce_stats")
+            _lib.count_launch()
+        else:
+            lf = logits.float()
+            m = lf.max(-1).values
+            s = (lf - m[:, None]).exp().sum(-1)
+            loc = labels - vocab_start
+            ok = (loc >= 0) & (loc < V)
+            tgt = lf.gather(1, loc.clamp(0, V - 1)[:, None])[:, 0] * ok
+            stats = torch.stack([m, s, tgt], dim=1)
+        if combine is not None:
+            stats = combine(stats, group)          # -> (gmax, gsum, gtgt) over the tensor-parallel group
+        gmax, gsum, gtgt = stats[:, 0], stats[:, 1], stats[:, 2]
+        loss = (gsum.log() + gmax - gtgt) * valid
+        ctx.save_for_backward(logits, labels, torch.stack([gmax, gsum], dim=1).contiguous(), valid)
+        ctx.vocab_start, ctx.cuda_path = vocab_start, cuda_path
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        logits, labels, gstats, valid = ctx.saved_tensors
+        rows, V = logits.shape
+        scale = (dloss.float() * valid).contiguous()
+        if ctx.cuda_path:
+            _lib.check(_lib.lib().hsb_ce_grad(logits.data_ptr(), labels.data_ptr(), gstats.data_ptr(), scale.data_ptr(),
+                                              rows, V, logits.stride(0), ctx.vocab_start, _lib.stream_ptr()),
+                       "hsb_ce_grad")
+            _lib.count_launch()
+            return logits, None, None, None, None, None
+        p = (logits.float() - gstats[:, :1]).exp() / gstats[:, 1:2]
+        loc = labels - ctx.vocab_start
+        ok = (loc >= 0) & (loc < V)
+        onehot = torch.zeros_like(p)
+        onehot.scatter_(1, loc.clamp(0, V - 1)[:, None], ok[:, None].to(p.dtype))
+        return ((p - onehot) * scale[:, None]).to(logits.dtype), None, None, None, None, None
+
+
+def cross_entropy_rows(logits, labels, ignore_index: int = -1, vocab_start: int = 0, group=None, combine=None):
+    """Per-row loss of a (possibly vocab-sharded) logits matrix.  The logits buffer is consumed:
+    its storage holds the gradient after backward."""
+    return _CrossEntropyFn.apply(logits, labels, ignore_index, vocab_start, group, combine)

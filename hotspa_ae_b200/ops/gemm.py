@@ -21,7 +21,7 @@ def _use_cuda(*ts: torch.Tensor) -> bool:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
-         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, tile_n: int = 0) -> torch.Tensor:
+         out_dtype: torch.dtype | None = None, accumulate: bool = False, tile_n: int = 0) -> torch.Tensor:
     """``out (=|+=) op(a) @ op(b).T`` with fp32 accumulation.
 
     a: [M, K] (or [K, M] when ``a_mn``), b: [N, K] (or [K, N] when ``b_mn``), bf16, last dim contiguous.
@@ -39,6 +39,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if accumulate:
         assert out is not None and out.dtype == torch.float32
     if out is None:
+        if out_dtype is None:
+            out_dtype = torch.bfloat16 if a.is_cuda else a.dtype
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     assert out.shape == (M, N) and out.stride(-1) == 1
 
@@ -101,7 +103,7 @@ class LinearFn(torch.autograd.Function):
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
                 dw = None  # accumulated in place; the optimizer reads main_grad
             else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype if w.dtype != torch.bfloat16 else torch.bfloat16)
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
         return dx, dw, None
 
 

@@ -1,0 +1,77 @@
+"""Graph-level optimizers.  ``minimize(loss)`` returns the train op; running it at run level UPDATE makes
+the executor reduce the gradients and call :meth:`apply_flat` once per flat shard (not once per tensor).
+Reference: hetu/graph/optim/optimizer.cc, hetu/graph/ops/optimizer_update.cc, hetu/impl/kernel/Optimizers.cu.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..graph import ops as O
+from ..ops import _lib
+
+
+class Optimizer:
+    def __init__(self, lr: float):
+        self.lr = lr
+        self.loss = None
+
+    def minimize(self, loss, var_list=None, name=None):
+        g = loss.graph
+        self.loss = loss
+        self.var_list = var_list
+        g.optimizer = self
+        train_op = O.group([loss], name=name or "train_op")
+        train_op.is_train_op = True
+        g.train_op = train_op
+        return train_op
+
+    def apply_flat(self, master, m, v, grad, out_compute, step, grad_scale=1.0):
+        raise NotImplementedError
+
+
+class SGDOptimizer(Optimizer):
+    def __init__(self, lr: float = 0.01, momentum: float = 0.0, nesterov: bool = False, weight_decay: float = 0.0):
+        super().__init__(lr)
+        self.momentum, self.nesterov, self.weight_decay = momentum, nesterov, weight_decay
+
+    def apply_flat(self, master, m, v, grad, out_compute, step, grad_scale=1.0):
+        g = grad * grad_scale if grad_scale != 1.0 else grad
+        if self.weight_decay:
+            g = g + self.weight_decay * master
+        if self.momentum > 0:
+            m.mul_(self.momentum).add_(g)
+            g = g + self.momentum * m if self.nesterov else m
+        master.add_(g, alpha=-self.lr)
+        out_compute.copy_(master)
+        grad.zero_()
+
+
+class AdamOptimizer(Optimizer):
+    """Adam with bias correction and decoupled weight decay (0 by default); one fused kernel per flat shard
+    that also emits the compute-dtype parameter copy and clears the gradient."""
+
+    def __init__(self, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                 weight_decay: float = 0.0):
+        super().__init__(lr)
+        self.beta1, self.beta2, self.eps, self.weight_decay = beta1, beta2, eps, weight_decay
+
+    def apply_flat(self, master, m, v, grad, out_compute, step, grad_scale=1.0):
+        bc1 = 1.0 - self.beta1 ** step
+        bc2 = 1.0 - self.beta2 ** step
+        n = master.numel()
+        if master.is_cuda and out_compute.dtype == torch.bfloat16:
+            rc = _lib.lib().hsb_adam(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(),
+                                     out_compute.data_ptr(), n, self.lr, self.beta1, self.beta2, self.eps,
+                                     self.weight_decay, bc1, bc2, grad_scale, 1, _lib.stream_ptr())
+            _lib.check(rc, "hsb_adam")
+            _lib.count_launch()
+            return
+        g = grad * grad_scale if grad_scale != 1.0 else grad
+        m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
+        v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
+        upd = (m / bc1) / ((v / bc2).sqrt() + self.eps)
+        if self.weight_decay:
+            upd = upd + self.weight_decay * master
+        master.add_(upd, alpha=-self.lr)
+        out_compute.copy_(master)
+        grad.zero_()

@@ -1,0 +1,175 @@
+"""Process mesh: one process per GPU, rank <-> device mapping, cached process groups.
+
+Replaces the reference's MPI bootstrap (hetu/impl/communication/mpi_comm_group.cc:650-815) and NCCL
+communicator cache (nccl_comm_group.cu:644-697) with torchrun + ``torch.distributed``: NCCL on GPUs,
+gloo on CPU.  Communicators are created once per distinct rank list and never destroyed.
+A *virtual* mesh (``init_comm_group(world_size=N, rank=r, virtual=True)``) carries topology only,
+so planners and DS deduction can be exercised for any world size in one CPU process.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class Device:
+    index: int                 # global rank
+    local_index: int = 0       # GPU ordinal on its node
+    hostname: str = "localhost"
+    type: str = "cuda"
+
+    def __repr__(self) -> str:
+        return f"{self.hostname}:{self.type}:{self.local_index}(rank {self.index})"
+
+
+class DeviceGroup:
+    """Ordered list of devices (reference: hetu/core/device.h DeviceGroup)."""
+
+    def __init__(self, devices):
+        devs = []
+        for d in devices:
+            devs.append(d if isinstance(d, Device) else mesh().device_of(int(d)))
+        self._devices = tuple(devs)
+
+    @property
+    def num_devices(self) -> int:
+        return len(self._devices)
+
+    def __len__(self) -> int:
+        return len(self._devices)
+
+    def contains(self, dev) -> bool:
+        idx = dev.index if isinstance(dev, Device) else int(dev)
+        return any(d.index == idx for d in self._devices)
+
+    def get(self, i: int) -> Device:
+        return self._devices[i]
+
+    def get_index(self, dev) -> int:
+        idx = dev.index if isinstance(dev, Device) else int(dev)
+        for i, d in enumerate(self._devices):
+            if d.index == idx:
+                return i
+        raise ValueError(f"{dev} is not in {self}")
+
+    def ranks(self) -> list[int]:
+        return [d.index for d in self._devices]
+
+    def __iter__(self):
+        return iter(self._devices)
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, DeviceGroup) and self.ranks() == other.ranks()
+
+    def __hash__(self) -> int:
+        return hash(tuple(self.ranks()))
+
+    def __repr__(self) -> str:
+        return f"DeviceGroup({self.ranks()})"
+
+
+class Mesh:
+    def __init__(self, world_size: int, rank: int, gpus_per_node: int, virtual: bool):
+        self.world_size = world_size
+        self.rank = rank
+        self.gpus_per_node = gpus_per_node
+        self.virtual = virtual
+        self._groups: dict[tuple, object] = {}
+        self.use_cuda = torch.cuda.is_available() and not virtual
+        self.local_rank = int(os.environ.get("LOCAL_RANK", rank % max(1, gpus_per_node)))
+        if self.use_cuda:
+            torch.cuda.set_device(self.local_rank % torch.cuda.device_count())
+            self.torch_device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            self.torch_device = torch.device("cpu")
+
+    def device_of(self, rank: int) -> Device:
+        return Device(index=rank, local_index=rank % max(1, self.gpus_per_node),
+                      type="cuda" if self.use_cuda else "cpu")
+
+    def local_device(self) -> Device:
+        return self.device_of(self.rank)
+
+    def global_group(self) -> DeviceGroup:
+        return DeviceGroup([self.device_of(r) for r in range(self.world_size)])
+
+    def group(self, ranks):
+        """torch.distributed group over `ranks` (None for single-member / virtual meshes)."""
+        ranks = tuple(int(r) for r in ranks)
+        if self.virtual or len(ranks) <= 1 or self.world_size == 1:
+            return None
+        if ranks == tuple(range(self.world_size)):
+            return dist.group.WORLD
+        key = tuple(ranks)
+        if key not in self._groups:
+            raise RuntimeError(f"process group {ranks} was not created; call mesh().ensure_groups() collectively")
+        return self._groups[key]
+
+    def ensure_groups(self, rank_lists) -> None:
+        """Collectively create every group in `rank_lists` (same order on all ranks)."""
+        if self.virtual or self.world_size == 1:
+            return
+        for ranks in sorted({tuple(int(r) for r in rl) for rl in rank_lists}):
+            if len(ranks) <= 1 or ranks == tuple(range(self.world_size)) or ranks in self._groups:
+                continue
+            self._groups[ranks] = dist.new_group(list(ranks))
+
+    def barrier(self) -> None:
+        if not self.virtual and self.world_size > 1:
+            dist.barrier()
+
+
+_MESH: Mesh | None = None
+
+
+def init_comm_group(gpus_per_node: int = 8, *, world_size: int | None = None, rank: int | None = None,
+                    virtual: bool = False, timeout_s: float = 600.0) -> Mesh:
+    """Set up the process mesh.  Under torchrun the world comes from RANK/WORLD_SIZE; a single plain
+    process becomes a world of one."""
+    global _MESH
+    if virtual:
+        _MESH = Mesh(int(world_size or 1), int(rank or 0), gpus_per_node, True)
+        return _MESH
+    env_ws = int(os.environ.get("WORLD_SIZE", "1"))
+    if env_ws > 1:
+        if not dist.is_initialized():
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+            local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+            kwargs = {}
+            if backend == "nccl":
+                torch.cuda.set_device(local_rank % torch.cuda.device_count())
+                kwargs["device_id"] = torch.device("cuda", local_rank % torch.cuda.device_count())
+            dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+        _MESH = Mesh(dist.get_world_size(), dist.get_rank(), gpus_per_node, False)
+    else:
+        _MESH = Mesh(1, 0, gpus_per_node, False)
+    return _MESH
+
+
+def mesh() -> Mesh:
+    global _MESH
+    if _MESH is None:
+        init_comm_group()
+    return _MESH
+
+
+def reset_mesh() -> None:
+    global _MESH
+    _MESH = None
+
+
+def local_device() -> Device:
+    return mesh().local_device()
+
+
+def global_device_group() -> DeviceGroup:
+    return mesh().global_group()
+
+
+def global_comm_barrier() -> None:
+    mesh().barrier()

@@ -1,0 +1,366 @@
+"""Parameter / gradient / optimizer-state arenas for every strategy, and the hot switch between them.
+
+Layout policy (one flat arena per strategy and rank, stable addresses):
+  * compute arena   parameters in the compute dtype (bf16 under autocast) in strategy k's local layout
+  * grad arena      fp32 gradients in the same layout (weight-gradient GEMMs accumulate into it)
+  * home strategy   additionally owns the fp32 master weights and Adam moments, sharded over each
+                    parameter's duplicate group when ZeRO-1 is on
+Parameters are grouped into *reduce classes* by the set of ranks that hold duplicates of them, so the
+data-parallel reduction is one collective per class over a contiguous range instead of one per tensor.
+
+Hot switch = resharding between two strategies' arenas with a plan from the C++ ReshardPlanner:
+  * parameters: every needed slice is copied from one chosen owner
+  * gradients:  every owner's partial sum is ADDED into one holder of the home layout (the home
+                strategy's own data-parallel reduction then completes the sum), so non-home strategies
+                never run a data-parallel all-reduce.
+Two executors implement a plan: ``nccl`` (pack -> grouped isend/irecv -> unpack: the reference's scheme,
+hetu/graph/switch_exec_graph.cc:1294-1435) and ``fused`` (one pull kernel over peer memory, see
+parallel/symm.py).  Reference policy for what lives where: hetu/graph/define_and_run_graph.cc:929-1093.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..core import ReshardPlanner, regions_of
+from . import mesh as M
+
+ALIGN = 256  # elements; keeps every tensor 512-byte aligned in bf16 and 16-byte rules for TMA trivially true
+
+
+@dataclass
+class Entry:
+    param: object
+    local_shape: list
+    numel: int
+    offset: int
+    cls: int
+    device_index: int
+
+
+@dataclass
+class ReduceClass:
+    ranks: tuple
+    start: int
+    end: int          # padded so that (end - start) % (len(ranks) * ALIGN) == 0
+    my_pos: int
+
+    @property
+    def chunk(self) -> int:
+        return (self.end - self.start) // len(self.ranks)
+
+
+@dataclass
+class Layout:
+    rank: int
+    entries: dict = field(default_factory=dict)      # param id -> Entry
+    classes: list = field(default_factory=list)
+    total: int = 0
+
+
+def build_layout(graph, sid: int, rank: int) -> Layout:
+    """Arena layout of strategy `sid` on `rank` (pure function of the graph: any rank can compute any rank's)."""
+    lay = Layout(rank)
+    by_class: dict[tuple, list] = {}
+    for p in graph.parameters:
+        for member, group in enumerate(p.dg_hierarchy[sid]):
+            if not group.contains(rank):
+                continue
+            ds = p.ds(sid, member)
+            idx = group.get_index(rank)
+            dup_ranks = tuple(ds.get_devices_by_dim(-1, idx, group.ranks()))
+            by_class.setdefault(dup_ranks, []).append((p, ds, idx))
+    off = 0
+    for ci, ranks in enumerate(sorted(by_class)):
+        start = off
+        for p, ds, idx in by_class[ranks]:
+            shape = list(ds.local_shape(p.global_shape))
+            n = 1
+            for s in shape:
+                n *= s
+            off = (off + ALIGN - 1) // ALIGN * ALIGN
+            lay.entries[p.id] = Entry(p, shape, n, off, ci, idx)
+            off += n
+        unit = len(ranks) * ALIGN
+        off = start + ((off - start + unit - 1) // unit) * unit
+        lay.classes.append(ReduceClass(ranks, start, off, ranks.index(rank)))
+    lay.total = off
+    return lay
+
+
+class ParamStore:
+    def __init__(self, graph):
+        self.graph = graph
+        self.mesh = M.mesh()
+        self.device = self.mesh.torch_device
+        self.rank = self.mesh.rank
+        self.layouts: dict[tuple, Layout] = {}
+        self.compute: dict[int, torch.Tensor] = {}
+        self.grads: dict[int, torch.Tensor] = {}
+        self.views: dict[int, dict] = {}
+        self.home: int | None = None
+        self.master = self.exp_avg = self.exp_avg_sq = None    # per class lists (home only)
+        self.valid: set[int] = set()
+        self.step_count = 0
+        self.switch_mode = "nccl"
+        self.plans: dict = {}
+        self.switch_log: list[dict] = []
+        self.sender_policy = 3
+        self.seed = 2023
+        self.symm = None
+
+    # ---- layouts / arenas ------------------------------------------------------------------------
+    @property
+    def compute_dtype(self):
+        return self.graph.autocast_dtype or torch.float32
+
+    def zero_enabled(self, sid: int) -> bool:
+        return any(p.ds(sid).zero for p in self.graph.parameters)
+
+    def layout(self, sid: int, rank: int | None = None) -> Layout:
+        rank = self.rank if rank is None else rank
+        key = (sid, rank)
+        if key not in self.layouts:
+            self.layouts[key] = build_layout(self.graph, sid, rank)
+        return self.layouts[key]
+
+    def _alloc(self, numel: int, dtype) -> torch.Tensor:
+        if self.symm is not None:
+            return self.symm.alloc(numel, dtype)
+        return torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+
+    def arena(self, sid: int) -> torch.Tensor:
+        if sid not in self.compute:
+            self.compute[sid] = self._alloc(self.layout(sid).total, self.compute_dtype)
+        return self.compute[sid]
+
+    def grad_arena(self, sid: int) -> torch.Tensor:
+        if sid not in self.grads:
+            self.grads[sid] = self._alloc(self.layout(sid).total, torch.float32)
+        return self.grads[sid]
+
+    def param_views(self, sid: int) -> dict:
+        """param id -> leaf tensor viewing the compute arena, with ``.main_grad`` viewing the grad arena."""
+        if sid not in self.views:
+            lay, arena, garena = self.layout(sid), self.arena(sid), self.grad_arena(sid)
+            out = {}
+            for pid, e in lay.entries.items():
+                v = arena[e.offset:e.offset + e.numel].view(e.local_shape).detach()
+                v.requires_grad_(e.param.requires_grad)
+                v.main_grad = garena[e.offset:e.offset + e.numel].view(e.local_shape)
+                out[pid] = v
+            self.views[sid] = out
+        return self.views[sid]
+
+    # ---- materialisation ---------------------------------------------------------------------------
+    def _init_local(self, p, e: Entry, sid: int) -> torch.Tensor:
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(self.seed + 7919 * self.graph.parameters.index(p))
+        full = self.graph.param_inits[p.id].fill(list(p.global_shape), gen, self.device)
+        sl = p.ds(sid).local_slice(p.global_shape, e.device_index)
+        idx = tuple(slice(o, o + n) for o, n in sl)
+        return full[idx].reshape(-1)
+
+    def materialize_home(self, sid: int) -> None:
+        if self.home is not None:
+            return
+        self.home = sid
+        lay, arena = self.layout(sid), self.arena(sid)
+        self.grad_arena(sid)
+        zero = self.zero_enabled(sid)
+        self.master, self.exp_avg, self.exp_avg_sq = [], [], []
+        for c in lay.classes:
+            n = c.chunk if (zero and len(c.ranks) > 1) else (c.end - c.start)
+            self.master.append(torch.zeros(n, dtype=torch.float32, device=self.device))
+            self.exp_avg.append(None)
+            self.exp_avg_sq.append(None)
+        for pid, e in lay.entries.items():
+            flat = self._init_local(e.param, e, sid)
+            arena[e.offset:e.offset + e.numel].copy_(flat)
+            c = lay.classes[e.cls]
+            lo, hi = self._owned_range(c, zero)
+            a, b = max(lo, e.offset), min(hi, e.offset + e.numel)
+            if a < b:
+                self.master[e.cls][a - lo:b - lo].copy_(flat[a - e.offset:b - e.offset])
+        self.valid = {sid}
+
+    def _owned_range(self, c: ReduceClass, zero: bool):
+        if zero and len(c.ranks) > 1:
+            return c.start + c.my_pos * c.chunk, c.start + (c.my_pos + 1) * c.chunk
+        return c.start, c.end
+
+    def ensure_compute(self, sid: int) -> None:
+        """Make strategy `sid`'s compute arena hold the current weights (hot switch when needed)."""
+        if self.home is None:
+            self.materialize_home(sid)
+            return
+        if sid in self.valid:
+            return
+        src = self.home if self.home in self.valid else next(iter(self.valid))
+        self.switch(src, sid, "param")
+        self.valid.add(sid)
+
+    # ---- hot switch -----------------------------------------------------------------------------------
+    def _plan(self, src: int, dst: int, kind: str):
+        key = (src, dst, kind)
+        if key in self.plans:
+            return self.plans[key]
+        t0 = time.perf_counter()
+        planner = ReshardPlanner(self.mesh.world_size, self.sender_policy)
+        for i, p in enumerate(self.graph.parameters):
+            shape = list(p.global_shape)
+            s_regs, d_regs = [], []
+            for member, group in enumerate(p.dg_hierarchy[src]):
+                s_regs += regions_of(shape, p.ds(src, member), group.ranks(), -1)
+            for member, group in enumerate(p.dg_hierarchy[dst]):
+                d_regs += regions_of(shape, p.ds(dst, member), group.ranks(), i if kind == "grad" else -1)
+            planner.add_tensor_regions(i, s_regs, d_regs, kind == "grad")
+        sends: dict[int, list] = {}
+        recvs: dict[int, list] = {}
+        local: list = []
+        for c in planner.copies():
+            if c.src_rank == self.rank and c.dst_rank == self.rank:
+                local.append(c)
+            elif c.src_rank == self.rank:
+                sends.setdefault(c.dst_rank, []).append(c)
+            elif c.dst_rank == self.rank:
+                recvs.setdefault(c.src_rank, []).append(c)
+        st = planner.stats
+        plan = {"sends": sends, "recvs": recvs, "local": local, "all": planner.copies(),
+                "remote_elems": st.remote_elems, "local_elems": st.local_elems,
+                "sent_elems": list(st.sent_elems), "recv_elems": list(st.recv_elems),
+                "plan_ms": (time.perf_counter() - t0) * 1e3}
+        self.plans[key] = plan
+        return plan
+
+    def _slice_view(self, arena, lay: Layout, c, side: str) -> torch.Tensor:
+        p = self.graph.parameters[c.tensor_id]
+        e = lay.entries[p.id]
+        off, ld = (c.src_off, c.src_ld) if side == "src" else (c.dst_off, c.dst_ld)
+        base = arena[e.offset:e.offset + e.numel]
+        return torch.as_strided(base, (c.rows, c.row_elems), (ld, 1), off)
+
+    def switch(self, src: int, dst: int, kind: str) -> None:
+        """Reshard `kind` ('param' copies, 'grad' adds) from strategy src's arena into dst's."""
+        plan = self._plan(src, dst, kind)
+        t_dev0 = t_dev1 = None
+        if self.device.type == "cuda":
+            t_dev0, t_dev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_dev0.record()
+        t0 = time.perf_counter()
+        if self.switch_mode == "fused" and self.symm is not None:
+            self.symm.reshard(self, plan, src, dst, kind)
+        else:
+            self._switch_nccl(plan, src, dst, kind)
+        if t_dev1 is not None:
+            t_dev1.record()
+        self.switch_log.append({"src": src, "dst": dst, "kind": kind, "mode": self.switch_mode,
+                                "remote_elems": plan["remote_elems"], "local_elems": plan["local_elems"],
+                                "host_ms": (time.perf_counter() - t0) * 1e3, "events": (t_dev0, t_dev1)})
+
+    def _switch_nccl(self, plan, src: int, dst: int, kind: str) -> None:
+        s_lay, d_lay = self.layout(src), self.layout(dst)
+        if kind == "param":
+            s_arena, d_arena = self.arena(src), self.arena(dst)
+        else:
+            s_arena, d_arena = self.grad_arena(src), self.grad_arena(dst)
+        dtype = s_arena.dtype
+        ops, recv_bufs, send_bufs = [], {}, {}
+        for peer in sorted(plan["recvs"]):
+            n = sum(c.rows * c.row_elems for c in plan["recvs"][peer])
+            recv_bufs[peer] = torch.empty(n, dtype=dtype, device=self.device)
+        for peer in sorted(plan["sends"]):
+            parts = [self._slice_view(s_arena, s_lay, c, "src").reshape(-1) for c in plan["sends"][peer]]
+            send_bufs[peer] = torch.cat(parts) if len(parts) > 1 else parts[0].contiguous()
+        for peer in sorted(set(recv_bufs) | set(send_bufs)):
+            if peer in send_bufs:
+                ops.append(dist.P2POp(dist.isend, send_bufs[peer], peer))
+            if peer in recv_bufs:
+                ops.append(dist.P2POp(dist.irecv, recv_bufs[peer], peer))
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        for c in plan["local"]:
+            d = self._slice_view(d_arena, d_lay, c, "dst")
+            s = self._slice_view(s_arena, s_lay, c, "src")
+            d.add_(s) if kind == "grad" else d.copy_(s)
+        for r in reqs:
+            r.wait()
+        for peer, buf in recv_bufs.items():
+            o = 0
+            for c in plan["recvs"][peer]:
+                n = c.rows * c.row_elems
+                d = self._slice_view(d_arena, d_lay, c, "dst")
+                piece = buf[o:o + n].view(c.rows, c.row_elems)
+                d.add_(piece) if kind == "grad" else d.copy_(piece)
+                o += n
+
+    def hand_grads_home(self, sid: int) -> None:
+        """Add strategy `sid`'s accumulated gradients into the home strategy's grad arena and clear them."""
+        if sid == self.home:
+            return
+        self.switch(sid, self.home, "grad")
+        self.grad_arena(sid).zero_()
+
+    # ---- optimizer step (home strategy) ------------------------------------------------------------------
+    def reduce_and_step(self, opt, grad_scale: float = 1.0) -> None:
+        sid = self.home
+        lay, arena, garena = self.layout(sid), self.arena(sid), self.grad_arena(sid)
+        zero = self.zero_enabled(sid)
+        self.step_count += 1
+        for ci, c in enumerate(lay.classes):
+            group = self.mesh.group(c.ranks)
+            seg = garena[c.start:c.end]
+            lo, hi = self._owned_range(c, zero)
+            if len(c.ranks) > 1 and group is not None:
+                if zero:
+                    own = garena[lo:hi]
+                    if self.device.type == "cuda":
+                        dist.reduce_scatter_tensor(own, seg, group=group)
+                    else:
+                        dist.all_reduce(seg, group=group)
+                else:
+                    dist.all_reduce(seg, group=group)
+            n = hi - lo
+            if self.exp_avg[ci] is None:
+                self.exp_avg[ci] = torch.zeros(n, dtype=torch.float32, device=self.device)
+                self.exp_avg_sq[ci] = torch.zeros(n, dtype=torch.float32, device=self.device)
+            opt.apply_flat(self.master[ci], self.exp_avg[ci], self.exp_avg_sq[ci], garena[lo:hi], arena[lo:hi],
+                           self.step_count, grad_scale)
+            if zero and len(c.ranks) > 1 and group is not None:
+                dist.all_gather_into_tensor(arena[c.start:c.end], arena[lo:hi], group=group) \
+                    if self.device.type == "cuda" else self._gloo_all_gather(arena, c, lo, hi, group)
+        self.valid = {sid}
+
+    def _gloo_all_gather(self, arena, c, lo, hi, group):
+        parts = [torch.empty(hi - lo, dtype=arena.dtype) for _ in c.ranks]
+        dist.all_gather(parts, arena[lo:hi].clone(), group=group)
+        for i, part in enumerate(parts):
+            arena[c.start + i * c.chunk:c.start + (i + 1) * c.chunk].copy_(part)
+
+    # ---- access by global value (checkpoint, tests) ---------------------------------------------------------
+    def local_value(self, p, sid: int | None = None) -> torch.Tensor:
+        sid = self.home if sid is None else sid
+        e = self.layout(sid).entries.get(p.id)
+        if e is None:
+            return None
+        return self.arena(sid)[e.offset:e.offset + e.numel].view(e.local_shape)
+
+    def load_global(self, p, array: torch.Tensor) -> None:
+        """Overwrite parameter `p` from its global value (home layout; master and compute copies)."""
+        sid = self.home
+        lay = self.layout(sid)
+        e = lay.entries.get(p.id)
+        if e is None:
+            return
+        sl = p.ds(sid).local_slice(p.global_shape, e.device_index)
+        idx = tuple(slice(o, o + n) for o, n in sl)
+        flat = array[idx].reshape(-1).to(self.device, torch.float32)
+        self.arena(sid)[e.offset:e.offset + e.numel].copy_(flat)
+        c = lay.classes[e.cls]
+        lo, hi = self._owned_range(c, self.zero_enabled(sid))
+        a, b = max(lo, e.offset), min(hi, e.offset + e.numel)
+        if a < b:
+            self.master[e.cls][a - lo:b - lo].copy_(flat[a - e.offset:b - e.offset])
+        self.valid = {sid}

@@ -1,0 +1,130 @@
+"""Strategy description files: one JSON per (gpus, dp, tp, pp) with the distributed-states recipe of every
+placeholder and parameter of the Llama/GPT model.
+
+Schema (interchange-compatible with the reference's hotspa/ds_parallel_config/generate_llama_3d_config.py):
+top keys ``zero, devices, input, llama{wte, wpe, blocks{blocks<a>-<b>{range, layernorm1, attn{qkv, dense},
+layernorm2, mlp{dense_h_to_4h, dense_4h_to_h}}}, layernorm_final}, lm_head, label``; every leaf is
+``{split: {dim: [n]}, dup: [n], device_group_union: [[ranks]], type: variable|placeholder[, zero]}`` with one
+list entry per member of a heterogeneous union.  Pipeline stage s owns ranks [s*N/pp, (s+1)*N/pp).
+"""
+from __future__ import annotations
+
+import json
+import os
+
+
+def _leaf(split: dict, dup: int, ranks: list, kind: str) -> dict:
+    return {"split": {str(k): [v] for k, v in split.items()}, "dup": [dup], "device_group_union": [list(ranks)],
+            "type": kind}
+
+
+def generate_llama_3d_config(num_layers: int = 32, num_gpus: int = 8, dp: int = 2, tp: int = 2, pp: int = 2,
+                             zero: bool = True, device_offset: int = 0) -> dict:
+    if dp * tp * pp != num_gpus:
+        raise ValueError(f"dp*tp*pp = {dp * tp * pp} != num_gpus = {num_gpus}")
+    if num_layers % pp:
+        raise ValueError("num_layers must be divisible by pp")
+    zero = bool(zero) and dp > 1
+    per_stage, width = num_layers // pp, num_gpus // pp
+    stage_ranks = [[device_offset + s * width + i for i in range(width)] for s in range(pp)]
+    first, last = stage_ranks[0], stage_ranks[-1]
+    var, ph = "variable", "placeholder"
+    cfg = {
+        "zero": zero,
+        "devices": [device_offset + i for i in range(num_gpus)],
+        "input": _leaf({0: dp}, tp, first, ph),
+        "llama": {
+            "wte": _leaf({0: tp}, dp, first, var),
+            "wpe": _leaf({}, dp * tp, first, var),
+            "blocks": {},
+            "layernorm_final": _leaf({}, dp * tp, last, var),
+        },
+        "lm_head": _leaf({1: tp}, dp, last, var),
+        "label": _leaf({0: dp}, tp, last, ph),
+    }
+    for s, ranks in enumerate(stage_ranks):
+        a, b = s * per_stage, (s + 1) * per_stage - 1
+        cfg["llama"]["blocks"][f"blocks{a}-{b}"] = {
+            "range": [a, b],
+            "layernorm1": _leaf({}, dp * tp, ranks, var),
+            "attn": {"qkv": _leaf({1: tp}, dp, ranks, var), "dense": _leaf({0: tp}, dp, ranks, var)},
+            "layernorm2": _leaf({}, dp * tp, ranks, var),
+            "mlp": {"dense_h_to_4h": _leaf({1: tp}, dp, ranks, var), "dense_4h_to_h": _leaf({0: tp}, dp, ranks, var)},
+        }
+    return cfg
+
+
+generate_gpt_3d_config = generate_llama_3d_config
+
+
+def propagate_zero(cfg: dict) -> dict:
+    """Copy the top-level ``zero`` flag onto every variable leaf that does not set its own."""
+    zero = cfg.get("zero", False)
+    stack = [cfg]
+    while stack:
+        node = stack.pop()
+        for v in node.values():
+            if isinstance(v, dict):
+                if "type" in v:
+                    if v["type"] == "variable" and "zero" not in v:
+                        v["zero"] = zero
+                else:
+                    stack.append(v)
+    return cfg
+
+
+def read_ds_parallel_config(paths) -> list[dict]:
+    if isinstance(paths, str):
+        paths = paths.split(",") if "," in paths else paths.split()
+    return [propagate_zero(json.load(open(p))) for p in paths]
+
+
+def find_config(cfg: dict, module_name: str, layer_idx: int = -1):
+    """The leaf (or sub-dict) called `module_name`, searching nested dicts; a dict with a ``range`` is only
+    entered when it contains `layer_idx`."""
+    stack = [cfg]
+    while stack:
+        node = stack.pop(0)
+        if module_name in node:
+            return node[module_name]
+        for v in node.values():
+            if isinstance(v, dict):
+                if "range" in v and not (v["range"][0] <= layer_idx <= v["range"][-1]):
+                    continue
+                stack.append(v)
+    raise KeyError(f"{module_name} (layer {layer_idx}) not found in the strategy config")
+
+
+def get_multi_ds_parallel_config(ds_parallel_configs: list[dict], module_name: str, layer_idx: int = -1) -> list:
+    return [find_config(c, module_name, layer_idx) for c in ds_parallel_configs]
+
+
+def write_config(cfg: dict, directory: str, dp: int, tp: int, pp: int) -> str:
+    os.makedirs(directory, exist_ok=True)
+    path = os.path.join(directory, f"dp{dp}_tp{tp}_pp{pp}.json")
+    with open(path, "w") as f:
+        json.dump(cfg, f, indent=4)
+    return path
+
+
+def strategy_name(cfg: dict) -> str:
+    inp = cfg["input"]
+    dp = inp["split"].get("0", [1])[0]
+    tp = inp["dup"][0]
+    pp = len(cfg["llama"]["blocks"])
+    return f"dp{dp}tp{tp}pp{pp}"
+
+
+if __name__ == "__main__":
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--num_layers", type=int, default=32)
+    ap.add_argument("--num_gpus", type=int, default=8)
+    ap.add_argument("--dp", type=int, default=2)
+    ap.add_argument("--tp", type=int, default=2)
+    ap.add_argument("--pp", type=int, default=2)
+    ap.add_argument("--zero", action="store_true")
+    ap.add_argument("--out_dir", type=str, default="ds_parallel_config")
+    a = ap.parse_args()
+    print(write_config(generate_llama_3d_config(a.num_layers, a.num_gpus, a.dp, a.tp, a.pp, a.zero), a.out_dir,
+                       a.dp, a.tp, a.pp))

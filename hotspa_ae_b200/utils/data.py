@@ -1,0 +1,109 @@
+"""Synthetic variable-length data, bucketing, packing and micro-batch construction.
+
+Sequences are bucketed by length (descending bounds, e.g. 32768/16384/4096/0), packed first-fit into rows
+of ``bucket_max + 1`` tokens (C++ packer in csrc/core/planner.cc), and every row becomes one micro-batch of
+``bucket_max`` (input, label) pairs with per-document positions and cu_seqlens.
+Reference: hotspa/llama_hot_switch.py:125-208 (Bucket, sort_and_pack_for_global_batch) and
+hotspa/data_utils.  Differences on purpose: labels at document ends and on padding are masked (-1),
+positions restart per document, attention is restricted to the document (cu_seqlens), rows are balanced
+over data-parallel ranks by tokens and never dropped.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .. import core as C
+
+IGNORE = -1
+
+
+def lognormal_lengths(total_tokens: int, seed: int = 0, median: float = 800.0, sigma: float = 1.25,
+                      min_len: int = 16, max_len: int = 32768) -> np.ndarray:
+    """Lengths with median ~`median`, ~90 % <= 4K for the defaults, clipped to [min_len, max_len], drawn until
+    they sum to at least `total_tokens` (the last one is trimmed so the sum is exact)."""
+    rng = np.random.default_rng(seed)
+    out, tot = [], 0
+    while tot < total_tokens:
+        n = int(np.clip(rng.lognormal(np.log(median), sigma), min_len, max_len))
+        n = min(n, total_tokens - tot)
+        if n < min_len and out:
+            out[-1] += n
+            tot += n
+            break
+        out.append(n)
+        tot += n
+    return np.asarray(out, dtype=np.int64)
+
+
+def synthetic_sequences(lengths, vocab_size: int, seed: int = 0) -> list[np.ndarray]:
+    rng = np.random.default_rng(seed + 1)
+    return [rng.integers(0, vocab_size, size=int(n), dtype=np.int64) for n in lengths]
+
+
+@dataclass
+class PackedRows:
+    max_len: int
+    min_len: int
+    rows: list = field(default_factory=list)          # list of lists of sequence indices
+    real_sequences: int = 0
+    tokens: int = 0
+
+
+def bucket_and_pack(lengths, bucket_bounds, shift: int = 1, drop_short: bool = False) -> list[PackedRows]:
+    res = C.bucket_and_pack([int(x) for x in lengths], [int(b) for b in bucket_bounds], shift, drop_short)
+    out = []
+    for b in res:
+        toks = int(sum(lengths[i] for i in b.members))
+        out.append(PackedRows(int(b.max_len), int(b.min_len), [list(r) for r in b.rows], len(b.members), toks))
+    return out
+
+
+def build_row(seqs: list[np.ndarray], max_len: int, pad_id: int = 0, max_docs: int | None = None):
+    """One packed row -> (input_ids, labels, position_ids, cu_seqlens) of `max_len` tokens."""
+    cap = max_len + 1
+    row = np.full(cap, pad_id, dtype=np.int64)
+    labels = np.full(max_len, IGNORE, dtype=np.int64)
+    pos = np.zeros(max_len, dtype=np.int64)
+    cu = [0]
+    o = 0
+    for s in seqs:
+        n = len(s)
+        assert o + n <= cap, "row overflow"
+        row[o:o + n] = s
+        e = min(o + n, max_len)
+        if e > o:
+            pos[o:e] = np.arange(e - o)
+            last = min(o + n - 1, max_len)           # the last token of a document has no target
+            labels[o:last] = row[o + 1:last + 1]
+            cu.append(e)
+        o += n
+    if cu[-1] < max_len:
+        pos[cu[-1]:] = np.arange(max_len - cu[-1])
+        cu.append(max_len)
+    if max_docs is not None:
+        assert len(cu) <= max_docs + 1, "too many documents in a row"
+        cu = cu + [max_len] * (max_docs + 1 - len(cu))
+    return row[:max_len].copy(), labels, pos, np.asarray(cu, dtype=np.int32)
+
+
+def micro_batches_for_rank(seqs, packed: PackedRows, dp: int, dp_rank: int, pad_id: int = 0, balance: bool = True):
+    """Rows of one bucket assigned to data-parallel rank `dp_rank`: arrays [n_mb, max_len] (+ cu [n_mb, D+1]).
+    Every rank gets the same number of micro-batches (empty rows are all padding) so collectives line up."""
+    row_tokens = [int(sum(len(seqs[i]) for i in r)) for r in packed.rows]
+    if balance:
+        assign = C.balance_rows(row_tokens, dp)
+    else:
+        assign = [list(range(r, len(packed.rows), dp)) for r in range(dp)]
+    n_mb = max(1, max(len(a) for a in assign))
+    max_docs = max([len(r) for r in packed.rows] + [1]) + 1
+    ids, labs, poss, cus, ntok = [], [], [], [], 0
+    mine = assign[dp_rank]
+    for k in range(n_mb):
+        members = [seqs[i] for i in packed.rows[mine[k]]] if k < len(mine) else []
+        a, b, c, d = build_row(members, packed.max_len, pad_id, max_docs)
+        ids.append(a); labs.append(b); poss.append(c); cus.append(d)
+        ntok += int((b != IGNORE).sum())
+    return {"input_ids": np.stack(ids), "labels": np.stack(labs), "position_ids": np.stack(poss),
+            "cu_seqlens": np.stack(cus), "num_micro_batches": n_mb, "valid_tokens": ntok}

@@ -1,0 +1,93 @@
+"""Shared test helpers: a plain-PyTorch Llama used as the numerics oracle, and graph builders."""
+import math
+
+import numpy as np
+import torch
+
+import hetu as ht
+from hotspa_ae_b200.models.llama import LlamaConfig, LlamaLMHeadModel
+from hotspa_ae_b200.parallel.strategy_config import generate_llama_3d_config, propagate_zero
+from hotspa_ae_b200.utils import data as D
+
+
+def build_llama_graph(config: LlamaConfig, strategies, world: int, lr=1e-3, autocast=None, reduction="mean"):
+    """strategies: list of (dp, tp, pp, zero).  Returns dict with graph, model, placeholders, loss, train_op."""
+    cfgs = [propagate_zero(generate_llama_3d_config(config.num_layers, world, dp, tp, pp, zero))
+            for dp, tp, pp, zero in strategies]
+    ctx = ht.graph("define_and_run", num_strategy=len(cfgs))
+    g = ctx.__enter__()
+    ac = ht.autocast(autocast) if autocast is not None else None
+    if ac is not None:
+        ac.__enter__()
+    model = LlamaLMHeadModel(config, cfgs)
+    in_ds, in_dg, lab_ds, lab_dg = [], [], [], []
+    for c in cfgs:
+        u, dg = ht.nn.config2ds(c["input"]); in_ds.append(u); in_dg.append(dg)
+        u, dg = ht.nn.config2ds(c["label"]); lab_ds.append(u); lab_dg.append(dg)
+    dp0 = in_ds[0].get(0).get_dim(0)
+    config.mbs_times_dp_symbol = ht.IntSymbol(dp0)
+    config.seq_len_symbol = ht.IntSymbol(128)
+    docs_symbol = ht.IntSymbol(3)
+    shape = [config.mbs_times_dp_symbol, config.seq_len_symbol]
+    input_ids = ht.parallel_placeholder(ht.int64, shape, in_ds, in_dg, name="input_ids")
+    position_ids = ht.parallel_placeholder(ht.int64, shape, in_ds, in_dg, name="position_ids")
+    cu_seqlens = ht.parallel_placeholder(ht.int32, [config.mbs_times_dp_symbol, docs_symbol], in_ds, in_dg, name="cu_seqlens")
+    labels = ht.parallel_placeholder(ht.int64, shape, lab_ds, lab_dg, name="labels")
+    loss = model(input_ids, position_ids, cu_seqlens, labels, reduction=reduction)
+    opt = ht.AdamOptimizer(lr=lr)
+    train_op = opt.minimize(loss)
+    if ac is not None:
+        ac.__exit__(None, None, None)
+    ctx.__exit__(None, None, None)
+    return dict(graph=g, model=model, input_ids=input_ids, position_ids=position_ids, cu_seqlens=cu_seqlens,
+                labels=labels, loss=loss, train_op=train_op, config=config, cfgs=cfgs, in_ds=in_ds)
+
+
+def torch_llama_loss(weights: dict, config: LlamaConfig, ids, labels, pos, cu, reduction="mean"):
+    """Plain fp32 PyTorch Llama forward on one packed row; weights are *global* tensors keyed like the model."""
+    h, nh, hd = config.hidden_size, config.num_heads, config.head_dim
+    x = weights["transformer.wte.embedding_table"][ids]
+    T = x.shape[0]
+    inv = 1.0 / (config.rope_base ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    ang = pos.float()[:, None] * inv[None]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def rms(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + config.rms_eps) * w
+
+    for i in range(config.num_layers):
+        p = f"transformer.h.{i}."
+        n1 = rms(x, weights[p + "rmsnorm_1.weight"])
+        qkv = (n1 @ weights[p + "attn.qkv_dense.weight"].t()).reshape(T, nh, 3, hd)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+
+        def rope(t):
+            t1, t2 = t[..., : hd // 2], t[..., hd // 2:]
+            return torch.cat([t1 * cos - t2 * sin, t1 * sin + t2 * cos], -1)
+        q, k = rope(q), rope(k)
+        out = torch.zeros(T, nh, hd)
+        b = cu.tolist()
+        for a, e in zip(b[:-1], b[1:]):
+            if e <= a:
+                continue
+            s = torch.einsum("qhd,khd->hqk", q[a:e], k[a:e]) / math.sqrt(hd)
+            m = torch.ones(e - a, e - a, dtype=torch.bool).tril()
+            s = s.masked_fill(~m, float("-inf")).softmax(-1)
+            out[a:e] = torch.einsum("hqk,khd->qhd", s, v[a:e])
+        x = x + out.reshape(T, h) @ weights[p + "attn.dense.weight"]
+        n2 = rms(x, weights[p + "rmsnorm_2.weight"])
+        gu = n2 @ weights[p + "mlp.dense_h_to_4h.weight"].t()
+        f = gu.shape[-1] // 2
+        x = x + (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]) @ weights[p + "mlp.dense_4h_to_h.weight"]
+    x = rms(x, weights["transformer.rmsnorm_f.weight"])
+    logits = x @ weights["lm_head.weight"].t()
+    return torch.nn.functional.cross_entropy(logits, labels, ignore_index=-1, reduction=reduction)
+
+
+def tiny_batch(seed=0, vocab=1000, lengths=(64, 128, 200, 512), max_len=512):
+    rng = np.random.default_rng(seed)
+    seqs = [rng.integers(0, vocab, size=n, dtype=np.int64) for n in lengths]
+    rows = []
+    for s in seqs:
+        rows.append(D.build_row([s], max_len, 0, 2))
+    return seqs, rows

@@ -61,7 +61,10 @@ __global__ void rope_qkv_kernel(__nv_bfloat16* __restrict__ qkv, const int* __re
 }
 
 // ---------------------------------------------------------------------------------------------
-// SwiGLU:  in [rows, 2d] (gate = first half, up = second half of the local shard) -> out [rows, d]
+// SwiGLU:  in [rows, 2d] with gate and up INTERLEAVED (column 2j = gate_j, 2j+1 = up_j) -> out [rows, d].
+// Interleaving makes the function independent of how the 2d columns are sharded over tensor-parallel
+// ranks (any contiguous shard holds whole pairs), which hot switching between tp degrees requires.
+// (The reference pairs the first and second half of the *local shard*, hetu/impl/kernel/SwiGLU.cu.)
 // ---------------------------------------------------------------------------------------------
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long rows,
                                   int d) {
@@ -71,11 +74,15 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfl
        idx += static_cast<long>(gridDim.x) * blockDim.x) {
     const long r = idx / vec;
     const int v = static_cast<int>(idx - r * vec);
-    float g[8], u[8], o[8];
-    ld8(in + r * 2 * d + v * 8, g);
-    ld8(in + r * 2 * d + d + v * 8, u);
+    float a[8], b[8], o[8];
+    ld8(in + r * 2 * d + v * 16, a);
+    ld8(in + r * 2 * d + v * 16 + 8, b);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    for (int j = 0; j < 4; ++j) {
+      const float g0 = a[2 * j], u0 = a[2 * j + 1], g1 = b[2 * j], u1 = b[2 * j + 1];
+      o[j] = g0 / (1.f + __expf(-g0)) * u0;
+      o[4 + j] = g1 / (1.f + __expf(-g1)) * u1;
+    }
     st8(out + r * d + v * 8, o);
   }
 }
@@ -87,19 +94,25 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __
        idx += static_cast<long>(gridDim.x) * blockDim.x) {
     const long r = idx / vec;
     const int v = static_cast<int>(idx - r * vec);
-    float g[8], u[8], dy[8], dg[8], du[8];
-    ld8(in + r * 2 * d + v * 8, g);
-    ld8(in + r * 2 * d + d + v * 8, u);
+    float a[8], b[8], dy[8], da[8], db[8];
+    ld8(in + r * 2 * d + v * 16, a);
+    ld8(in + r * 2 * d + v * 16 + 8, b);
     ld8(dout + r * d + v * 8, dy);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float sg = 1.f / (1.f + __expf(-g[j]));
-      const float silu = g[j] * sg;
-      du[j] = dy[j] * silu;
-      dg[j] = dy[j] * u[j] * (sg + silu * (1.f - sg));
+    for (int j = 0; j < 4; ++j) {
+      {
+        const float g = a[2 * j], u = a[2 * j + 1], sg = 1.f / (1.f + __expf(-g)), silu = g * sg;
+        da[2 * j] = dy[j] * u * (sg + silu * (1.f - sg));
+        da[2 * j + 1] = dy[j] * silu;
+      }
+      {
+        const float g = b[2 * j], u = b[2 * j + 1], sg = 1.f / (1.f + __expf(-g)), silu = g * sg;
+        db[2 * j] = dy[4 + j] * u * (sg + silu * (1.f - sg));
+        db[2 * j + 1] = dy[4 + j] * silu;
+      }
     }
-    st8(din + r * 2 * d + v * 8, dg);
-    st8(din + r * 2 * d + d + v * 8, du);
+    st8(din + r * 2 * d + v * 16, da);
+    st8(din + r * 2 * d + v * 16 + 8, db);
   }
 }
 

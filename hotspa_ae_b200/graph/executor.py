@@ -96,9 +96,13 @@ class Runtime:
         b_col = b_ds.get_dim(0 if trans_b else 1)
         # a duplicated activation multiplied by column-sharded weights: its gradient is partial over
         # those shards -> all-reduce in backward (tensor parallel without sequence parallel)
+        # ... unless the activation was just all-gathered: that comm's backward (reduce-scatter) already sums it.
         if b_col > 1 and a_ds.get_dim(-1) > 1 and x.requires_grad:
+            prod = a.producer
+            gathered = (prod is not None and prod.type == "comm" and prod.id in self.plan.comm
+                        and self.plan.comm[prod.id].kind == C._C.COMM_ALL_GATHER)
             ranks = self.group_ranks_by_dim(a, -1)
-            if len(ranks) > 1 and not self.mesh.virtual:
+            if not gathered and len(ranks) > 1 and not self.mesh.virtual:
                 x = PC.CopyToGroup.apply(x, self.mesh.group(ranks))
         return gemm_linear(x, w, getattr(w, "main_grad", None), trans_b=trans_b)
 

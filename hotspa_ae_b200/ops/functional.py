@@ -227,7 +227,7 @@ def rope_qkv(qkv, positions, heads: int, hd: int, max_pos: int | None = None, ba
 
 
 # --------------------------------------------------------------------------------------------
-# SwiGLU: [rows, 2d] -> [rows, d]   (gate = first half, up = second half)
+# SwiGLU: [rows, 2d] -> [rows, d]   (gate and up interleaved: column 2j = gate_j, 2j+1 = up_j)
 # --------------------------------------------------------------------------------------------
 class _SwigluFn(torch.autograd.Function):
     @staticmethod
@@ -243,7 +243,7 @@ class _SwigluFn(torch.autograd.Function):
             _lib.count_launch()
             ctx.cuda_path = True
         else:
-            g, u = x2[:, :d].float(), x2[:, d:].float()
+            g, u = x2[:, 0::2].float(), x2[:, 1::2].float()
             out = (F.silu(g) * u).to(x.dtype)
             ctx.cuda_path = False
         ctx.save_for_backward(x2)
@@ -261,10 +261,10 @@ class _SwigluFn(torch.autograd.Function):
                                                  _lib.stream_ptr()), "hsb_swiglu_bwd")
             _lib.count_launch()
         else:
-            g, u, dyf = x2[:, :d].float(), x2[:, d:].float(), dy2.float()
+            g, u, dyf = x2[:, 0::2].float(), x2[:, 1::2].float(), dy2.float()
             sg = torch.sigmoid(g)
             silu = g * sg
-            dx = torch.cat([dyf * u * (sg + silu * (1 - sg)), dyf * silu], dim=-1).to(dy.dtype)
+            dx = torch.stack([dyf * u * (sg + silu * (1 - sg)), dyf * silu], dim=-1).reshape(x2.shape).to(dy.dtype)
         return dx.reshape(ctx.shape)
 
 

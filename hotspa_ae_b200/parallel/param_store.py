@@ -240,8 +240,7 @@ class ParamStore:
         p = self.graph.parameters[c.tensor_id]
         e = lay.entries[p.id]
         off, ld = (c.src_off, c.src_ld) if side == "src" else (c.dst_off, c.dst_ld)
-        base = arena[e.offset:e.offset + e.numel]
-        return torch.as_strided(base, (c.rows, c.row_elems), (ld, 1), off)
+        return torch.as_strided(arena, (c.rows, c.row_elems), (ld, 1), arena.storage_offset() + e.offset + off)
 
     def switch(self, src: int, dst: int, kind: str) -> None:
         """Reshard `kind` ('param' copies, 'grad' adds) from strategy src's arena into dst's."""

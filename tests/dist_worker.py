@@ -1,0 +1,115 @@
+"""Multi-process worker for the distributed parity tests (launched by torch.distributed.run).
+
+Every rank builds the same tiny Llama over the given strategies, runs one optimizer step made of one or
+more buckets (hot switch when several strategies are used) and compares its local parameter shards after
+the update with a single-process plain-PyTorch reference of the same global batch.
+"""
+import argparse
+import json
+import sys
+import os
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.models.llama import llama_config  # noqa: E402
+from hotspa_ae_b200.utils import data as D  # noqa: E402
+from helpers import build_llama_graph, torch_llama_loss  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--strategies", type=str, required=True)      # json [[dp,tp,pp,zero], ...]
+    ap.add_argument("--plan", type=str, required=True)            # json [[sid, level, seq_len, n_rows], ...]
+    ap.add_argument("--switch_mode", type=str, default="nccl")
+    ap.add_argument("--device", type=str, default="cpu")
+    ap.add_argument("--tol", type=float, default=2e-4)
+    args = ap.parse_args()
+    strategies = [tuple(s) for s in json.loads(args.strategies)]
+    plan = json.loads(args.plan)
+    ht.init_comm_group(8)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    cfg = llama_config("tiny", max_seq_len=256, num_layers=4)
+    b = build_llama_graph(cfg, strategies, world, lr=1e-3)
+    g = b["graph"]
+    g.executor.store.switch_mode = args.switch_mode
+    rng = np.random.default_rng(1234)
+    weights = None
+    ref_loss_terms = []
+    for step_i, (sid, level, seq_len, n_rows) in enumerate(plan):
+        dp = b["in_ds"][sid].get(0).get_dim(0)
+        # global rows of this bucket (same on all ranks)
+        rows = []
+        for _ in range(n_rows):
+            n1 = int(rng.integers(seq_len // 4, seq_len // 2))
+            n2 = int(rng.integers(seq_len // 4, seq_len // 2))
+            seqs = [rng.integers(0, cfg.vocab_size, size=n1), rng.integers(0, cfg.vocab_size, size=n2)]
+            rows.append(D.build_row(seqs, seq_len, 0, 3))
+        assert n_rows % dp == 0
+        nmb = n_rows // dp
+        # rank's dp index under this strategy
+        inp = b["input_ids"]
+        my_dp = 0
+        for st in g.executor.plan(sid).stages:
+            if rank in st:
+                my_dp = inp.ds(sid).get_dup_group_index(list(st).index(rank))
+        mine = rows[my_dp::dp]
+        cfg.mbs_times_dp_symbol.set_data(dp)
+        cfg.seq_len_symbol.set_data(seq_len)
+        feed = {b["input_ids"]: np.stack([r[0] for r in mine]), b["labels"]: np.stack([r[1] for r in mine]),
+                b["position_ids"]: np.stack([r[2] for r in mine]), b["cu_seqlens"]: np.stack([r[3] for r in mine])}
+        lvl = ht.run_level(level)
+        if level == "alloc":
+            g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, sid, lvl)
+            continue
+        if weights is None:
+            # global initial weights: re-create them exactly as the store does
+            weights = {}
+            store = g.executor.store
+            for k, p in b["model"].named_parameters():
+                gen = torch.Generator(device="cpu")
+                gen.manual_seed(store.seed + 7919 * g.parameters.index(p))
+                weights[k] = g.param_inits[p.id].fill(list(p.global_shape), gen, "cpu").requires_grad_(True)
+        g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, sid, lvl)
+        for r in rows:
+            ref_loss_terms.append((r, 1.0 / n_rows))
+    total = 0.0
+    for r, wgt in ref_loss_terms:
+        total = total + wgt * torch_llama_loss(weights, cfg, torch.tensor(r[0]), torch.tensor(r[1]),
+                                               torch.tensor(r[2]), torch.tensor(r[3]))
+    total.backward()
+    worst = 0.0
+    store = g.executor.store
+    home = store.home
+    for k, p in b["model"].named_parameters():
+        e = store.layout(home).entries.get(p.id)
+        if e is None:
+            continue
+        gr = weights[k].grad
+        upd = gr / (gr.abs() + 1e-8)
+        want = weights[k].detach() - 1e-3 * upd
+        sl = p.ds(home).local_slice(p.global_shape, e.device_index)
+        idx = tuple(slice(o, o + n) for o, n in sl)
+        got = store.local_value(p).detach().float().cpu()
+        mask = gr[idx].abs() > 1e-6
+        diff = (got - want[idx]).abs()[mask]
+        if diff.numel():
+            worst = max(worst, float(diff.max()))
+            if float(diff.max()) > args.tol and os.environ.get("HSB_TEST_VERBOSE"):
+                print(f"rank {rank}: {k} diff {float(diff.max()):.3e}", flush=True)
+    ok = worst < args.tol
+    print(f"rank {rank}: worst param diff {worst:.3e} ok={ok}", flush=True)
+    if world > 1:
+        t = torch.tensor([0 if ok else 1])
+        torch.distributed.all_reduce(t)
+        ok = int(t.item()) == 0
+    sys.exit(0 if ok else 3)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,18 @@
+// C entry points of the tcgen05 flash-attention kernels (flash_attn_fwd.cu, flash_attn_bwd.cu).
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+// Upper bound on the number of 128-row query tiles of T packed tokens in ndocs documents.
+int hsb_fa_max_tiles(int T, int ndocs);
+// table: int32 scratch with 2 + 4 * hsb_fa_max_tiles(T, ndocs) entries (rebuilt by every call).
+// lse is written in the log2 domain: log2(sum_j exp2(scale*log2(e)*q.k_j)).
+int hsb_fa_fwd(const void* qkv, const int* cu, int ndocs, void* out, float* lse, int* table, int T, int heads,
+               int hd, float scale, int* status, void* stream, int num_sms);
+int hsb_fa_bwd(const void* qkv, const void* out, const void* dout, const float* lse, const int* cu, int ndocs,
+               void* dqkv, float* delta, float* dq_acc, int* table, int T, int heads, int hd, float scale, int* status,
+               void* stream, int num_sms);
+#ifdef __cplusplus
+}
+#endif

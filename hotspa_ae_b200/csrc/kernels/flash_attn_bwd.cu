@@ -1,0 +1,444 @@
+// Varlen causal flash attention, backward, on tcgen05 tensor cores (sm_100a).
+//
+// One work item = (kv tile j of a document, head).  The CTA keeps K_j, V_j in shared memory and the
+// dK_j, dV_j accumulators in TMEM while it walks the query tiles i >= j of the document:
+//     S^T  = K_j Q_i^T          dP^T = V_j dO_i^T                      (TMEM, rows = kv)
+//     P^T  = exp2(scale*S^T - lse_i),  dS^T = P^T * (dP^T - delta_i)   (softmax warps -> bf16 smem tiles)
+//     dV_j += P^T dO_i          dK_j += dS^T Q_i          dQ_i = dS K_j (TMEM -> red.add into fp32 dq_acc)
+// The dS^T tile feeds dK as a K-major A operand and dQ as an MN-major A operand without a transpose;
+// dO_i, Q_i and K_j are consumed as MN-major B operands from their row-major tiles.
+// delta = rowsum(dO * O) and the final dQ fp32 -> bf16 conversion are small helper kernels.
+// Reference counterpart: flash_bwd_kernel.h of the reference's flash_attn tarball (mma.sync, fixed length).
+#include "common.cuh"
+#include "fa_api.h"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace hsb {
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, uint32_t box_cols);
+
+constexpr int FB_T = 128;          // tile edge for both q and kv
+constexpr int FB_THREADS = 192;
+
+// table: [0] = item count, then 4 ints per item: kv_start, doc_start, doc_end, j; costliest (smallest j) first
+__global__ void fa_build_kv_tiles_kernel(const int* __restrict__ cu, int ndocs, int* __restrict__ table,
+                                         int max_tiles) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int max_nt = 0, total = 0;
+  for (int d = 0; d < ndocs; ++d) {
+    const int len = cu[d + 1] - cu[d];
+    if (len <= 0) continue;
+    const int nt = (len + FB_T - 1) / FB_T;
+    total += nt;
+    if (nt > max_nt) max_nt = nt;
+  }
+  if (total > max_tiles) total = 0;
+  table[0] = total;
+  if (total == 0) return;
+  int written = 0;
+  for (int cost = max_nt; cost >= 1; --cost) {       // cost = number of q tiles this kv tile meets
+    for (int d = 0; d < ndocs; ++d) {
+      const int len = cu[d + 1] - cu[d];
+      if (len <= 0) continue;
+      const int nt = (len + FB_T - 1) / FB_T;
+      if (nt >= cost) {
+        const int j = nt - cost;
+        int* t = table + 2 + 4 * written;
+        t[0] = cu[d] + j * FB_T;
+        t[1] = cu[d];
+        t[2] = cu[d + 1];
+        t[3] = j;
+        ++written;
+      }
+    }
+  }
+}
+
+// delta[h, t] = sum_d dout[t, h, d] * out[t, h, d]
+__global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                float* __restrict__ delta, int T, int heads, int hd) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long gw = static_cast<long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long total = static_cast<long>(T) * heads;
+  for (long idx = gw; idx < total; idx += static_cast<long>(gridDim.x) * warps_per_block) {
+    const int t = static_cast<int>(idx / heads), h = static_cast<int>(idx % heads);
+    const __nv_bfloat16* o = out + idx * hd;
+    const __nv_bfloat16* d = dout + idx * hd;
+    float acc = 0.f;
+    for (int c = lane * 2; c < hd; c += 64) {
+      const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + c));
+      const float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(d + c));
+      acc += a.x * b.x + a.y * b.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) delta[static_cast<size_t>(h) * T + t] = acc;
+  }
+}
+
+// dqkv[t, h, 0:hd] = bf16(dq_acc[t, h, :] * scale)
+__global__ void fa_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, long n_rows,
+                                     int hd, float scale) {
+  const int vec = hd >> 2;
+  const long total = n_rows * vec;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = idx / vec;
+    const int v = static_cast<int>(idx - r * vec);
+    const float4 f = reinterpret_cast<const float4*>(dq_acc + r * hd)[v];
+    uint2 o;
+    o.x = pack_bf16x2(f.x * scale, f.y * scale);
+    o.y = pack_bf16x2(f.z * scale, f.w * scale);
+    reinterpret_cast<uint2*>(dqkv + r * 3 * hd)[v] = o;
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void softmax_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int HD>
+struct FbCfg {
+  static constexpr int SUB = HD / 64;
+  static constexpr int TILE_BYTES = FB_T * HD * 2;
+  static constexpr int PT_BYTES = FB_T * FB_T * 2;
+  static constexpr int SMEM_BYTES = 4 * TILE_BYTES + 2 * PT_BYTES + 1024 /*lse, delta*/ + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 384;   // dQ reuses S_COL
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FB_THREADS, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+              const int* __restrict__ table, const float* __restrict__ lse, const float* __restrict__ delta,
+              __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dq_acc, int T, int heads, float scale,
+              float scale_log2, int* __restrict__ status) {
+  using Cfg = FbCfg<HD>;
+  constexpr int SUB = Cfg::SUB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::TILE_BYTES;
+  uint8_t* sQ = sV + Cfg::TILE_BYTES;
+  uint8_t* sdO = sQ + Cfg::TILE_BYTES;
+  uint8_t* sPT = sdO + Cfg::TILE_BYTES;
+  uint8_t* sdST = sPT + Cfg::PT_BYTES;
+  float* sLse = reinterpret_cast<float*>(sdST + Cfg::PT_BYTES);
+  float* sDelta = sLse + FB_T;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sLse) + 1024);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* kv_empty = bars + 1;
+  uint64_t* qdo_full = bars + 2;
+  uint64_t* qdo_empty = bars + 3;
+  uint64_t* sdp_full = bars + 4;
+  uint64_t* pds_full = bars + 5;
+  uint64_t* dq_full = bars + 6;
+  uint64_t* dq_drained = bars + 7;
+  uint64_t* dkv_drained = bars + 8;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_items = table[0];
+  const long n_work = static_cast<long>(n_items) * heads;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(kv_empty, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1); mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_drained, 4);
+    mbar_init(dkv_drained, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_holder, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------ TMA producer ------------------------------------
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_qkv);
+      tma_prefetch_desc(&tm_do);
+      uint32_t n_kv = 0, n_q = 0;
+      bool ok = true;
+      for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int item = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+        const int* t = table + 2 + 4 * item;
+        const int kv_start = t[0], doc_start = t[1], doc_end = t[2], j = t[3];
+        const int nq = (doc_end - doc_start + FB_T - 1) / FB_T;
+        const int col_q = h * 3 * HD, col_k = col_q + HD, col_v = col_q + 2 * HD;
+        if (!mbar_wait(kv_empty, (n_kv & 1) ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < SUB; ++s) {
+          tma_load_2d(sK + s * (FB_T * 128), &tm_qkv, kv_full, col_k + s * 64, kv_start);
+          tma_load_2d(sV + s * (FB_T * 128), &tm_qkv, kv_full, col_v + s * 64, kv_start);
+        }
+        ++n_kv;
+        for (int i = j; i < nq && ok; ++i) {
+          const int q_start = doc_start + i * FB_T;
+          if (!mbar_wait(qdo_empty, (n_q & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(qdo_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+          for (int s = 0; s < SUB; ++s) {
+            tma_load_2d(sQ + s * (FB_T * 128), &tm_qkv, qdo_full, col_q + s * 64, q_start);
+            tma_load_2d(sdO + s * (FB_T * 128), &tm_do, qdo_full, h * HD + s * 64, q_start);
+          }
+          ++n_q;
+        }
+      }
+      if (!ok) atomicCAS(status, ST_OK, ST_TIMEOUT_PRODUCER);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------ MMA issuer --------------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(FB_T, FB_T, 0, 0);   // S^T, dP^T: both operands K-major
+      constexpr uint32_t idesc_kn = make_idesc_bf16(FB_T, HD, 0, 1);     // dV, dK: A K-major, B MN-major
+      constexpr uint32_t idesc_nn = make_idesc_bf16(FB_T, HD, 1, 1);     // dQ: A MN-major, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      const uint32_t aPT = smem_u32(sPT), adST = smem_u32(sdST);
+      uint32_t n_kv = 0, n_q = 0, n_dq = 0, n_pds = 0, n_item = 0;
+      bool ok = true;
+      for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int item = static_cast<int>(w / heads);
+        const int* t = table + 2 + 4 * item;
+        const int doc_start = t[1], doc_end = t[2], j = t[3];
+        const int nq = (doc_end - doc_start + FB_T - 1) / FB_T;
+        if (!mbar_wait(kv_full, n_kv & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(dkv_drained, (n_item & 1) ^ 1, abort_flag)) { ok = false; break; }
+        for (int i = j; i < nq && ok; ++i) {
+          if (!mbar_wait(qdo_full, n_q & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(dq_drained, (n_dq & 1) ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * (FB_T * 128) + (kk % 4) * 32;
+            umma_bf16_ss(tmem_base + Cfg::S_COL, make_smem_desc_sw128(aK + off, 16, 1024),
+                         make_smem_desc_sw128(aQ + off, 16, 1024), idesc_st, kk != 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * (FB_T * 128) + (kk % 4) * 32;
+            umma_bf16_ss(tmem_base + Cfg::DP_COL, make_smem_desc_sw128(aV + off, 16, 1024),
+                         make_smem_desc_sw128(adO + off, 16, 1024), idesc_st, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(sdp_full);
+          if (!mbar_wait(pds_full, n_pds & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t acc = i > j ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {
+            const uint32_t a_off = (kk / 4) * (FB_T * 128) + (kk % 4) * 32;      // K-major A, k = q
+            const uint32_t b_off = kk * 2048;                                     // MN-major B, 16 q rows
+            umma_bf16_ss(tmem_base + Cfg::DV_COL, make_smem_desc_sw128(aPT + a_off, 16, 1024),
+                         make_smem_desc_sw128(adO + b_off, FB_T * 128, 1024), idesc_kn, (acc | (kk != 0)) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {
+            const uint32_t a_off = (kk / 4) * (FB_T * 128) + (kk % 4) * 32;
+            const uint32_t b_off = kk * 2048;
+            umma_bf16_ss(tmem_base + Cfg::DK_COL, make_smem_desc_sw128(adST + a_off, 16, 1024),
+                         make_smem_desc_sw128(aQ + b_off, FB_T * 128, 1024), idesc_kn, (acc | (kk != 0)) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {
+            const uint32_t off = kk * 2048;                                       // both MN-major, k = kv rows
+            umma_bf16_ss(tmem_base + Cfg::S_COL, make_smem_desc_sw128(adST + off, FB_T * 128, 1024),
+                         make_smem_desc_sw128(aK + off, FB_T * 128, 1024), idesc_nn, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(dq_full);
+          umma_commit(qdo_empty);
+          ++n_q; ++n_dq; ++n_pds;
+        }
+        if (!ok) break;
+        umma_commit(kv_empty);
+        ++n_kv; ++n_item;
+      }
+      if (!ok) atomicCAS(status, ST_OK, ST_TIMEOUT_MMA);
+    }
+  } else {
+    // ------------------------------------ softmax / dS / drains ---------------------------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                 // kv row inside the tile == TMEM lane
+    const int tid128 = threadIdx.x - 64;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    uint32_t n_sdp = 0, n_dq = 0;
+    bool ok = true;
+    for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const int item = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+      const int* t = table + 2 + 4 * item;
+      const int kv_start = t[0], doc_start = t[1], doc_end = t[2], j = t[3];
+      const int nq = (doc_end - doc_start + FB_T - 1) / FB_T;
+      for (int i = j; i < nq && ok; ++i) {
+        const int q_start = doc_start + i * FB_T;
+        // per-query statistics of this q tile
+        softmax_group_sync();
+        {
+          const int qi = q_start + tid128;
+          const bool v = qi < doc_end && qi < T;
+          sLse[tid128] = v ? lse[static_cast<size_t>(h) * T + qi] : 0.f;
+          sDelta[tid128] = v ? delta[static_cast<size_t>(h) * T + qi] : 0.f;
+        }
+        softmax_group_sync();
+        if (!mbar_wait(sdp_full, n_sdp & 1, abort_flag)) { ok = false; break; }
+        ++n_sdp;
+        tc_fence_after();
+        const int q_valid = min(FB_T, doc_end - q_start);     // columns >= q_valid are outside the document
+        uint8_t* prow = sPT + row * 128;
+        uint8_t* drow = sdST + row * 128;
+#pragma unroll 1
+        for (int c = 0; c < FB_T; c += 32) {
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + Cfg::S_COL + c, rs);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + Cfg::DP_COL + c, rp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float p[8], ds[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int col = c + g * 8 + e;
+              const bool keep = col < q_valid && (i > j || col >= row);
+              const float pv = exp2f(__uint_as_float(rs[g * 8 + e]) * scale_log2 - sLse[col]);
+              p[e] = keep ? pv : 0.f;
+              ds[e] = keep ? pv * (__uint_as_float(rp[g * 8 + e]) - sDelta[col]) : 0.f;
+            }
+            uint4 pk, dk;
+            pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
+            pk.z = pack_bf16x2(p[4], p[5]); pk.w = pack_bf16x2(p[6], p[7]);
+            dk.x = pack_bf16x2(ds[0], ds[1]); dk.y = pack_bf16x2(ds[2], ds[3]);
+            dk.z = pack_bf16x2(ds[4], ds[5]); dk.w = pack_bf16x2(ds[6], ds[7]);
+            const int col0 = c + g * 8;
+            const int sub = col0 >> 6, chunk = (col0 & 63) >> 3;
+            const int off = sub * (FB_T * 128) + ((chunk ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(prow + off) = pk;
+            *reinterpret_cast<uint4*>(drow + off) = dk;
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pds_full);
+        // drain dQ_i (rows = queries) into the fp32 accumulator
+        if (!mbar_wait(dq_full, n_dq & 1, abort_flag)) { ok = false; break; }
+        ++n_dq;
+        tc_fence_after();
+        {
+          const int qi = q_start + row;
+          const bool v = qi < doc_end && qi < T;
+          float* dst = dq_acc + (static_cast<size_t>(qi) * heads + h) * HD;
+#pragma unroll
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + Cfg::S_COL + c, r);
+            tmem_ld_wait();
+            if (v) {
+#pragma unroll
+              for (int e = 0; e < 32; e += 4)
+                red_add_v4(dst + c + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                           __uint_as_float(r[e + 3]));
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_drained);
+      }
+      if (!ok) break;
+      // dV_j, dK_j are final: the last dq_full covered every MMA of this item
+      {
+        const int ki = kv_start + row;
+        const bool v = ki < doc_end && ki < T;
+        __nv_bfloat16* dk_dst = dqkv + (static_cast<size_t>(ki) * heads + h) * 3 * HD + HD;
+        __nv_bfloat16* dv_dst = dk_dst + HD;
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t rk[32], rv[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + Cfg::DK_COL + c, rk);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + Cfg::DV_COL + c, rv);
+          tmem_ld_wait();
+          if (v) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 ok_, ov_;
+              ok_.x = pack_bf16x2(__uint_as_float(rk[8 * q4 + 0]) * scale, __uint_as_float(rk[8 * q4 + 1]) * scale);
+              ok_.y = pack_bf16x2(__uint_as_float(rk[8 * q4 + 2]) * scale, __uint_as_float(rk[8 * q4 + 3]) * scale);
+              ok_.z = pack_bf16x2(__uint_as_float(rk[8 * q4 + 4]) * scale, __uint_as_float(rk[8 * q4 + 5]) * scale);
+              ok_.w = pack_bf16x2(__uint_as_float(rk[8 * q4 + 6]) * scale, __uint_as_float(rk[8 * q4 + 7]) * scale);
+              ov_.x = pack_bf16x2(__uint_as_float(rv[8 * q4 + 0]), __uint_as_float(rv[8 * q4 + 1]));
+              ov_.y = pack_bf16x2(__uint_as_float(rv[8 * q4 + 2]), __uint_as_float(rv[8 * q4 + 3]));
+              ov_.z = pack_bf16x2(__uint_as_float(rv[8 * q4 + 4]), __uint_as_float(rv[8 * q4 + 5]));
+              ov_.w = pack_bf16x2(__uint_as_float(rv[8 * q4 + 6]), __uint_as_float(rv[8 * q4 + 7]));
+              reinterpret_cast<uint4*>(dk_dst + c)[q4] = ok_;
+              reinterpret_cast<uint4*>(dv_dst + c)[q4] = ov_;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dkv_drained);
+    }
+    if (!ok && lane == 0) atomicCAS(status, ST_OK, ST_TIMEOUT_EPILOGUE);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int HD>
+static int launch_fa_bwd(const void* qkv, const void* out, const void* dout, const float* lse, const int* cu, int ndocs,
+                         void* dqkv, float* delta, float* dq_acc, int* table, int max_tiles, int T, int heads,
+                         float scale, int* status, cudaStream_t st, int num_sms) {
+  using Cfg = FbCfg<HD>;
+  CUtensorMap tm_qkv, tm_do;
+  const uint64_t ld_qkv = static_cast<uint64_t>(heads) * 3 * HD, ld_o = static_cast<uint64_t>(heads) * HD;
+  if (make_tmap_bf16_2d(&tm_qkv, qkv, T, ld_qkv, ld_qkv, FB_T, 64)) return -2;
+  if (make_tmap_bf16_2d(&tm_do, dout, T, ld_o, ld_o, FB_T, 64)) return -2;
+  fa_build_kv_tiles_kernel<<<1, 32, 0, st>>>(cu, ndocs, table, max_tiles);
+  fa_delta_kernel<<<148 * 4, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                           reinterpret_cast<const __nv_bfloat16*>(dout), delta, T, heads, HD);
+  if (cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * heads * HD * sizeof(float), st) != cudaSuccess) return -5;
+  auto kern = fa_bwd_kernel<HD>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  const long work = static_cast<long>(max_tiles) * heads;
+  const int grid = static_cast<int>(work < num_sms ? work : num_sms);
+  kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tm_qkv, tm_do, table, lse, delta,
+                                                 reinterpret_cast<__nv_bfloat16*>(dqkv), dq_acc, T, heads, scale,
+                                                 scale * 1.4426950408889634f, status);
+  fa_dq_convert_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv),
+                                                static_cast<long>(T) * heads, HD, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace hsb
+
+// delta: [heads, T] fp32 scratch; dq_acc: [T, heads, hd] fp32 scratch; table as for hsb_fa_fwd.
+extern "C" int hsb_fa_bwd(const void* qkv, const void* out, const void* dout, const float* lse, const int* cu,
+                          int ndocs, void* dqkv, float* delta, float* dq_acc, int* table, int T, int heads, int hd,
+                          float scale, int* status, void* stream, int num_sms) {
+  if (T <= 0 || ndocs <= 0 || heads <= 0 || !status || !table || !delta || !dq_acc) return -10;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return -11;
+  if (num_sms <= 0) num_sms = 148;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int max_tiles = hsb_fa_max_tiles(T, ndocs);
+  if (hd == 128)
+    return hsb::launch_fa_bwd<128>(qkv, out, dout, lse, cu, ndocs, dqkv, delta, dq_acc, table, max_tiles, T, heads,
+                                   scale, status, st, num_sms);
+  if (hd == 64)
+    return hsb::launch_fa_bwd<64>(qkv, out, dout, lse, cu, ndocs, dqkv, delta, dq_acc, table, max_tiles, T, heads,
+                                  scale, status, st, num_sms);
+  return -12;
+}

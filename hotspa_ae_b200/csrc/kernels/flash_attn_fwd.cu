@@ -1,0 +1,391 @@
+// Varlen causal flash attention, forward, on tcgen05 tensor cores (sm_100a).
+//
+//   qkv : [T, heads, 3*HD] bf16, per head q | k | v (RoPE already applied), T packed tokens
+//   cu  : [ndocs + 1] int32 document boundaries; every document attends causally to itself only
+//   out : [T, heads*HD] bf16        lse : [heads, T] fp32, log2-domain log-sum-exp of scale*q.k
+//
+// Replaces the reference's FlashAttention-2 wrapper (hetu/impl/kernel/FlashAttention.cu + the
+// mma.sync/cp.async kernels of its flash_attn tarball), which runs fixed-length causal attention
+// over the whole packed row.  Structure (persistent CTAs, 192 threads, work sorted longest-first):
+//   warp 0     TMA producer: Q tile once per work item, K and V tiles through 2-stage rings
+//   warp 1     MMA issuer:   S = Q K^T  (TMEM, double buffered)  and  O += P V  (TMEM)
+//   warps 2-5  softmax: one query row per thread; S row from TMEM -> exp2 -> P (bf16) into a
+//              128B-swizzled smem tile that feeds the PV MMA; the O accumulator is only rescaled when
+//              the running max moved by more than 2^8 (lazy rescale), then normalised in the epilogue.
+// K/Q tiles are K-major UMMA operands, V is consumed as an MN-major B operand straight from its
+// row-major [kv, HD] layout, so no transposes are materialised.
+#include "common.cuh"
+#include "fa_api.h"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace hsb {
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, uint32_t box_cols);
+
+constexpr int FA_BM = 128;      // query rows per tile
+constexpr int FA_BN = 128;      // kv rows per tile
+constexpr int FA_THREADS = 192;
+constexpr float FA_RESCALE_THRESHOLD = 8.0f;   // log2 units
+
+// work table layout (int32): [0] = number of tiles, [1] = scratch, then 4 ints per tile:
+// q_start (token), doc_start, doc_end, qt (query tile index inside the document)
+__global__ void fa_build_tiles_kernel(const int* __restrict__ cu, int ndocs, int* __restrict__ table, int max_tiles) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  // counting sort by qt, descending, so that the costliest tiles are scheduled first
+  int max_qt = 0, total = 0;
+  for (int d = 0; d < ndocs; ++d) {
+    const int len = cu[d + 1] - cu[d];
+    if (len <= 0) continue;
+    const int nt = (len + FA_BM - 1) / FA_BM;
+    total += nt;
+    if (nt - 1 > max_qt) max_qt = nt - 1;
+  }
+  if (total > max_tiles) total = 0;   // caller sized the table from an upper bound; never overflow it
+  table[0] = total;
+  if (total == 0) return;
+  // position of the first tile with a given qt in the descending order = number of tiles with larger qt.
+  // tiles with qt = k exist for every document with at least k+1 tiles.
+  int written = 0;
+  for (int k = max_qt; k >= 0; --k) {
+    for (int d = 0; d < ndocs; ++d) {
+      const int len = cu[d + 1] - cu[d];
+      if (len <= 0) continue;
+      const int nt = (len + FA_BM - 1) / FA_BM;
+      if (nt - 1 >= k) {
+        int* t = table + 2 + 4 * written;
+        t[0] = cu[d] + k * FA_BM;
+        t[1] = cu[d];
+        t[2] = cu[d + 1];
+        t[3] = k;
+        ++written;
+      }
+    }
+  }
+}
+
+template <int HD>
+struct FaCfg {
+  static constexpr int SUB = HD / 64;                 // 64-column (128-byte) sub-tiles per operand tile
+  static constexpr int TILE_BYTES = FA_BM * HD * 2;   // Q, K, V tiles
+  static constexpr int P_BYTES = FA_BM * FA_BN * 2;
+  static constexpr int KV_STAGES = 2;
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict__ table,
+              __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int T, int heads, float scale_log2,
+              int* __restrict__ status) {
+  using Cfg = FaCfg<HD>;
+  constexpr int SUB = Cfg::SUB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::TILE_BYTES;
+  uint8_t* sV = sK + Cfg::KV_STAGES * Cfg::TILE_BYTES;
+  uint8_t* sP = sV + Cfg::KV_STAGES * Cfg::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::P_BYTES);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* k_full = bars + 2;    // [2]
+  uint64_t* k_empty = bars + 4;   // [2]
+  uint64_t* v_full = bars + 6;    // [2]
+  uint64_t* v_empty = bars + 8;   // [2]
+  uint64_t* s_full = bars + 10;   // [2]
+  uint64_t* s_empty = bars + 12;  // [2]
+  uint64_t* p_full = bars + 14;
+  uint64_t* pv_done = bars + 15;
+  uint64_t* o_empty = bars + 16;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = table[0];
+  const long n_work = static_cast<long>(n_tiles) * heads;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1); mbar_init(q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4); mbar_init(pv_done, 1); mbar_init(o_empty, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_holder, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------ TMA producer ------------------------------------
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_qkv);
+      uint32_t n_q = 0, n_k = 0, n_v = 0;
+      bool ok = true;
+      for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int tile = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+        const int* t = table + 2 + 4 * tile;
+        const int q_start = t[0], doc_start = t[1], qt = t[3];
+        const int col_q = h * 3 * HD, col_k = col_q + HD, col_v = col_q + 2 * HD;
+        if (!mbar_wait(q_empty, (n_q & 1) ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(q_full, Cfg::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < SUB; ++s) tma_load_2d(sQ + s * (FA_BM * 128), &tm_qkv, q_full, col_q + s * 64, q_start);
+        ++n_q;
+        for (int j = 0; j <= qt && ok; ++j) {
+          const int kv_start = doc_start + j * FA_BN;
+          {
+            const int st = n_k & 1;
+            if (!mbar_wait(&k_empty[st], ((n_k >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(&k_full[st], Cfg::TILE_BYTES);
+#pragma unroll
+            for (int s = 0; s < SUB; ++s)
+              tma_load_2d(sK + st * Cfg::TILE_BYTES + s * (FA_BN * 128), &tm_qkv, &k_full[st], col_k + s * 64, kv_start);
+            ++n_k;
+          }
+          {
+            const int st = n_v & 1;
+            if (!mbar_wait(&v_empty[st], ((n_v >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(&v_full[st], Cfg::TILE_BYTES);
+#pragma unroll
+            for (int s = 0; s < SUB; ++s)
+              tma_load_2d(sV + st * Cfg::TILE_BYTES + s * (FA_BN * 128), &tm_qkv, &v_full[st], col_v + s * 64, kv_start);
+            ++n_v;
+          }
+        }
+      }
+      if (!ok) atomicCAS(status, ST_OK, ST_TIMEOUT_PRODUCER);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------ MMA issuer --------------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, FA_BN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(FA_BM, HD, 0, 1);
+      uint32_t n_q = 0, n_k = 0, n_v = 0, n_s = 0, n_p = 0, n_o = 0;
+      bool ok = true;
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+      auto issue_pv = [&](bool first) -> bool {
+        // O (+)= P V_{j}: needs P in smem (p_full) and the V tile
+        if (!mbar_wait(p_full, n_p & 1, abort_flag)) return false;
+        const int st = n_v & 1;
+        if (!mbar_wait(&v_full[st], (n_v >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t vb = aV + st * Cfg::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+          // A = P: K-major, kv 0..63 in sub-tile 0, 64..127 in sub-tile 1
+          const uint64_t ad = make_smem_desc_sw128(aP + (kk / 4) * (FA_BM * 128) + (kk % 4) * 32, 16, 1024);
+          // B = V: MN-major ([kv rows, HD cols]); 16 kv rows = 2048 bytes; 64-column blocks FA_BN*128 apart
+          const uint64_t bd = make_smem_desc_sw128(vb + kk * 2048, FA_BN * 128, 1024);
+          umma_bf16_ss(tmem_base + Cfg::O_COL, ad, bd, idesc_pv, (first && kk == 0) ? 0u : 1u);
+        }
+        umma_commit(pv_done);
+        umma_commit(&v_empty[st]);
+        ++n_p; ++n_v;
+        return true;
+      };
+      for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int tile = static_cast<int>(w / heads);
+        const int qt = table[2 + 4 * tile + 3];
+        if (!mbar_wait(q_full, n_q & 1, abort_flag)) { ok = false; break; }
+        // the previous work item's epilogue must have drained O before PV_0 overwrites it
+        if (!mbar_wait(o_empty, (n_o & 1) ^ 1, abort_flag)) { ok = false; break; }
+        for (int j = 0; j <= qt && ok; ++j) {
+          const int st = n_k & 1, sb = n_s & 1;
+          if (!mbar_wait(&k_full[st], (n_k >> 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[sb], ((n_s >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t kb = aK + st * Cfg::TILE_BYTES;
+          const uint32_t d_s = tmem_base + (sb ? Cfg::S_COL1 : Cfg::S_COL0);
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint64_t ad = make_smem_desc_sw128(aQ + (kk / 4) * (FA_BM * 128) + (kk % 4) * 32, 16, 1024);
+            const uint64_t bd = make_smem_desc_sw128(kb + (kk / 4) * (FA_BN * 128) + (kk % 4) * 32, 16, 1024);
+            umma_bf16_ss(d_s, ad, bd, idesc_s, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[sb]);
+          umma_commit(&k_empty[st]);
+          if (j == qt) umma_commit(q_empty);     // Q is free once the last S of this item retires
+          ++n_k; ++n_s;
+          if (j > 0) { if (!issue_pv(j == 1)) { ok = false; break; } }
+        }
+        if (!ok) break;
+        if (!issue_pv(qt == 0)) { ok = false; break; }
+        ++n_q; ++n_o;
+      }
+      if (!ok) atomicCAS(status, ST_OK, ST_TIMEOUT_MMA);
+    }
+  } else {
+    // ------------------------------------ softmax + epilogue ---------------------------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                 // row inside the query tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    uint32_t n_s = 0, n_pv = 0;
+    bool ok = true;
+    for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const int tile = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+      const int* t = table + 2 + 4 * tile;
+      const int q_start = t[0], doc_end = t[2], qt = t[3];
+      const int q_idx = q_start + row;
+      float m_ref = -INFINITY, l_sum = 0.f;
+      for (int j = 0; j <= qt && ok; ++j) {
+        const int sb = n_s & 1;
+        if (!mbar_wait(&s_full[sb], (n_s >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t s_addr = tmem_base + lane_addr + (sb ? Cfg::S_COL1 : Cfg::S_COL0);
+        float sv[FA_BN];
+#pragma unroll
+        for (int c = 0; c < FA_BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(s_addr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]) * scale_log2;
+        }
+        // S buffer may be overwritten by the MMA of tile j+2 now
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[sb]);
+        ++n_s;
+        if (j == qt) {
+          // diagonal tile: kv (column) beyond the query (row) is masked
+#pragma unroll
+          for (int c = 0; c < FA_BN; ++c)
+            if (c > row) sv[c] = -INFINITY;
+        }
+        float mx = sv[0];
+#pragma unroll
+        for (int c = 1; c < FA_BN; ++c) mx = fmaxf(mx, sv[c]);
+        // the previous PV must have retired before P is overwritten / O is rescaled
+        if (j > 0) {
+          if (!mbar_wait(pv_done, n_pv & 1, abort_flag)) { ok = false; break; }
+          ++n_pv;
+          tc_fence_after();
+        }
+        float alpha = 1.f;
+        const bool grow = mx > m_ref + FA_RESCALE_THRESHOLD;
+        if (j == 0) {
+          m_ref = mx;
+        } else if (__any_sync(0xffffffffu, grow)) {
+          if (grow) { alpha = exp2f(m_ref - mx); m_ref = mx; }
+          l_sum *= alpha;
+          const uint32_t o_addr = tmem_base + lane_addr + Cfg::O_COL;
+#pragma unroll
+          for (int c = 0; c < HD; c += 16) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(o_addr + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x16(o_addr + c, r);
+          }
+          tmem_st_wait();
+        }
+        // P = exp2(s - m_ref), packed to bf16 into the swizzled K-major tile
+        float rs = 0.f;
+        uint8_t* prow = sP + row * 128;
+#pragma unroll
+        for (int c = 0; c < FA_BN; c += 8) {
+          float p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { p[i] = exp2f(sv[c + i] - m_ref); rs += p[i]; }
+          uint4 pk;
+          pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
+          pk.z = pack_bf16x2(p[4], p[5]); pk.w = pack_bf16x2(p[6], p[7]);
+          const int sub = c >> 6, chunk = (c & 63) >> 3;
+          *reinterpret_cast<uint4*>(prow + sub * (FA_BM * 128) + ((chunk ^ (row & 7)) << 4)) = pk;
+        }
+        l_sum += rs;
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+      }
+      if (!ok) break;
+      // epilogue: wait for the last PV, normalise, store
+      if (!mbar_wait(pv_done, n_pv & 1, abort_flag)) { ok = false; break; }
+      ++n_pv;
+      tc_fence_after();
+      const float inv = 1.f / l_sum;
+      const uint32_t o_addr = tmem_base + lane_addr + Cfg::O_COL;
+      const bool valid = q_idx < doc_end && q_idx < T;
+      __nv_bfloat16* orow = out + (static_cast<size_t>(q_idx) * heads + h) * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(o_addr + c, r);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            reinterpret_cast<uint4*>(orow + c)[v] = o;
+          }
+        }
+      }
+      if (valid) lse[static_cast<size_t>(h) * T + q_idx] = m_ref + log2f(l_sum);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_empty);
+    }
+    if (!ok && lane == 0) atomicCAS(status, ST_OK, ST_TIMEOUT_EPILOGUE);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int HD>
+static int launch_fa_fwd(const void* qkv, const int* cu, int ndocs, void* out, float* lse, int* table, int max_tiles,
+                         int T, int heads, float scale, int* status, cudaStream_t st, int num_sms) {
+  using Cfg = FaCfg<HD>;
+  CUtensorMap tm;
+  if (make_tmap_bf16_2d(&tm, qkv, T, static_cast<uint64_t>(heads) * 3 * HD, static_cast<uint64_t>(heads) * 3 * HD,
+                        FA_BM, 64))
+    return -2;
+  fa_build_tiles_kernel<<<1, 32, 0, st>>>(cu, ndocs, table, max_tiles);
+  auto kern = fa_fwd_kernel<HD>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  const long work = static_cast<long>(max_tiles) * heads;
+  const int grid = static_cast<int>(work < num_sms ? work : num_sms);
+  kern<<<grid, FA_THREADS, Cfg::SMEM_BYTES, st>>>(tm, table, reinterpret_cast<__nv_bfloat16*>(out), lse, T, heads,
+                                                 scale * 1.4426950408889634f, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace hsb
+
+extern "C" int hsb_fa_max_tiles(int T, int ndocs) { return (T + hsb::FA_BM - 1) / hsb::FA_BM + ndocs; }
+
+// table: int32 scratch of 2 + 4 * hsb_fa_max_tiles(T, ndocs) entries.
+extern "C" int hsb_fa_fwd(const void* qkv, const int* cu, int ndocs, void* out, float* lse, int* table, int T,
+                          int heads, int hd, float scale, int* status, void* stream, int num_sms) {
+  if (T <= 0 || ndocs <= 0 || heads <= 0 || !status || !table) return -10;
+  if (reinterpret_cast<uintptr_t>(qkv) & 15) return -11;
+  if (num_sms <= 0) num_sms = 148;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int max_tiles = hsb_fa_max_tiles(T, ndocs);
+  if (hd == 128) return hsb::launch_fa_fwd<128>(qkv, cu, ndocs, out, lse, table, max_tiles, T, heads, scale, status, st, num_sms);
+  if (hd == 64) return hsb::launch_fa_fwd<64>(qkv, cu, ndocs, out, lse, table, max_tiles, T, heads, scale, status, st, num_sms);
+  return -12;
+}

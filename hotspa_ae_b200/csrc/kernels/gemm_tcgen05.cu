@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <mutex>
+#include <cstdio>
 
 namespace hsb {
 
@@ -262,6 +263,10 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
                       uint32_t box_rows, uint32_t box_cols) {
   auto fn = get_encode_fn();
   if (!fn) return -1;
+  // The driver entry point needs a current context on the calling thread; autograd worker threads may
+  // not have touched the runtime yet, so bind the primary context once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   cuuint64_t gdim[2] = {cols, rows};
   cuuint64_t gstride[1] = {ld * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
@@ -269,6 +274,10 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "hsb: cuTensorMapEncodeTiled failed (%d): base=%p rows=%llu cols=%llu ld=%llu box=[%u,%u]\n",
+            static_cast<int>(r), base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld,
+            box_rows, box_cols);
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 

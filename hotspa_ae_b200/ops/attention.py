@@ -79,13 +79,21 @@ class _AttnTorchFn(torch.autograd.Function):
         return dqkv.reshape(qkv.shape).to(qkv.dtype), None, None, None, None
 
 
+def _fa_available(hd: int) -> bool:
+    try:
+        from . import flash_attn
+    except ImportError:
+        return False
+    return flash_attn.supported(hd)
+
+
 def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, heads: int, hd: int, max_seqlen: int | None = None,
                      scale: float | None = None, backend: str | None = None) -> torch.Tensor:
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
     T = qkv.shape[0]
     qkv3 = qkv.reshape(T, heads, 3 * hd)
     if backend is None:
-        backend = "hsb" if (qkv.is_cuda and qkv.dtype == torch.bfloat16) else "torch"
+        backend = "hsb" if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and _fa_available(hd)) else "torch"
     if backend == "hsb":
         from .flash_attn import flash_attn_varlen
         return flash_attn_varlen(qkv3, cu_seqlens, heads, hd, max_seqlen, scale)

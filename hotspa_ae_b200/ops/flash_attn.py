@@ -1,0 +1,84 @@
+"""Python binding of the tcgen05 varlen flash-attention kernels (csrc/kernels/flash_attn_{fwd,bwd}.cu)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+c_void_p, c_int, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_declared = False
+_scratch: dict = {}
+
+
+def supported(hd: int) -> bool:
+    return hd in (64, 128)
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    _lib.declare("hsb_fa_max_tiles", [c_int, c_int])
+    _lib.declare("hsb_fa_fwd", [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int])
+    _lib.declare("hsb_fa_bwd", [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int, c_int, c_int, c_float, c_void_p,
+                                                                           c_void_p, c_int])
+    _declared = True
+
+
+def _buffer(device, key: str, numel: int, dtype) -> torch.Tensor:
+    """Grow-only scratch reused across calls on one stream (tile tables, delta, fp32 dq accumulator)."""
+    k = (device.index, key)
+    buf = _scratch.get(k)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(int(numel * 1.25) + 64, dtype=dtype, device=device)
+        _scratch[k] = buf
+    return buf
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cu, heads, hd, scale):
+        _declare()
+        T = qkv.shape[0]
+        ndocs = cu.numel() - 1
+        qkv = qkv.contiguous()
+        out = torch.empty((T, heads * hd), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((heads, T), dtype=torch.float32, device=qkv.device)
+        n_tab = 2 + 4 * _lib.lib().hsb_fa_max_tiles(T, ndocs)
+        table = _buffer(qkv.device, "fa_table_fwd", n_tab, torch.int32)
+        rc = _lib.lib().hsb_fa_fwd(qkv.data_ptr(), cu.data_ptr(), ndocs, out.data_ptr(), lse.data_ptr(),
+                                   table.data_ptr(), T, heads, hd, float(scale),
+                                   _lib.status_tensor(qkv.device).data_ptr(), _lib.stream_ptr(), 0)
+        _lib.check(rc, "hsb_fa_fwd")
+        _lib.count_launch(2)
+        ctx.save_for_backward(qkv, cu, out, lse)
+        ctx.heads, ctx.hd, ctx.scale = heads, hd, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, cu, out, lse = ctx.saved_tensors
+        heads, hd = ctx.heads, ctx.hd
+        T = qkv.shape[0]
+        ndocs = cu.numel() - 1
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        n_tab = 2 + 4 * _lib.lib().hsb_fa_max_tiles(T, ndocs)
+        table = _buffer(qkv.device, "fa_table_bwd", n_tab, torch.int32)
+        delta = _buffer(qkv.device, "fa_delta", heads * T, torch.float32)
+        dq_acc = _buffer(qkv.device, "fa_dq_acc", T * heads * hd, torch.float32)
+        rc = _lib.lib().hsb_fa_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), cu.data_ptr(),
+                                   ndocs, dqkv.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), table.data_ptr(), T,
+                                   heads, hd, float(ctx.scale), _lib.status_tensor(qkv.device).data_ptr(),
+                                   _lib.stream_ptr(), 0)
+        _lib.check(rc, "hsb_fa_bwd")
+        _lib.count_launch(4)
+        return dqkv, None, None, None, None
+
+
+def flash_attn_varlen(qkv3: torch.Tensor, cu_seqlens: torch.Tensor, heads: int, hd: int, max_seqlen, scale: float):
+    """qkv3: [T, heads, 3*hd] bf16 (per head q | k | v); cu_seqlens int32 must cover [0, T)."""
+    cu = cu_seqlens.to(device=qkv3.device, dtype=torch.int32).contiguous()
+    return _FlashAttnFn.apply(qkv3, cu, heads, hd, scale)

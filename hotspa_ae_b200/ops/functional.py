@@ -218,12 +218,13 @@ def rope_qkv(qkv, positions, heads: int, hd: int, max_pos: int | None = None, ba
         max_pos = 1 << max(12, int(math.ceil(math.log2(max(2, T + 1)))))
     cos_t, sin_t = rope_tables(max_pos, hd, qkv.device, base)
     pos = positions.to(torch.int32)
-    flat = qkv.reshape(T, heads * 3 * hd)
+    flat = qkv if qkv.dim() == 2 else qkv.reshape(T, heads * 3 * hd)
     if not flat.is_contiguous():
         flat = flat.contiguous()
-    if flat.is_leaf and flat.requires_grad:
-        flat = flat.clone()        # never rotate a leaf in place
-    return _RopeFn.apply(flat, pos, cos_t, sin_t, heads, hd).reshape(qkv.shape)
+    if (flat.is_leaf and flat.requires_grad) or flat._is_view():
+        flat = flat.clone()        # never rotate a leaf or a view of someone else's buffer in place
+    out = _RopeFn.apply(flat, pos, cos_t, sin_t, heads, hd)
+    return out if qkv.dim() == 2 else out.reshape(qkv.shape)
 
 
 # --------------------------------------------------------------------------------------------

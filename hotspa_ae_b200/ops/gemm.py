@@ -86,7 +86,7 @@ class LinearFn(torch.autograd.Function):
         ctx.main_grad = main_grad
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, w)
-        return y.reshape(*x.shape[:-1], w.shape[0])
+        return y if x.dim() == 2 else y.reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
@@ -116,7 +116,7 @@ class LinearKNFn(torch.autograd.Function):
         ctx.main_grad = main_grad
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, w, b_mn=True)           # b = W as [K=in, N=out]
-        return y.reshape(*x.shape[:-1], w.shape[1])
+        return y if x.dim() == 2 else y.reshape(*x.shape[:-1], w.shape[1])
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,0 +1,201 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _check_loaded():
+    from hotspa_ae_b200.ops import _lib
+    assert _lib.lib() is not None
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (384, 768, 192), (200, 264, 136), (1024, 2048, 1024)])
+def test_gemm_layouts(a_mn, b_mn, shape):
+    from hotspa_ae_b200.ops import _lib
+    from hotspa_ae_b200.ops.gemm import gemm
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=_dev(), dtype=torch.bfloat16)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    for tile in (128, 256):
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=tile)
+        _lib.check_status()
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    acc = torch.ones((M, N), device=_dev(), dtype=torch.float32)
+    gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True)
+    _lib.check_status()
+    assert (acc - (ref + 1)).abs().max().item() <= 1e-3 * ref.abs().max().item() + 1e-3
+
+
+def test_linear_autograd_matches_fp32():
+    from hotspa_ae_b200.ops.gemm import linear
+    torch.manual_seed(1)
+    x = torch.randn(512, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    for trans_b, wshape in ((True, (384, 256)), (False, (256, 384))):
+        w = (torch.randn(wshape, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_(True)
+        w.main_grad = torch.zeros(wshape, device=_dev(), dtype=torch.float32)
+        y = linear(x, w, w.main_grad, trans_b=trans_b)
+        dy = torch.randn_like(y)
+        (gx,) = torch.autograd.grad(y, x, dy)
+        xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        yf = xf @ (wf.t() if trans_b else wf)
+        yf.backward(dy.float())
+        assert torch.allclose(y.float(), yf, rtol=2e-2, atol=2e-2)
+        assert torch.allclose(gx.float(), xf.grad, rtol=2e-2, atol=2e-2)
+        assert torch.allclose(w.main_grad, wf.grad, rtol=2e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("is_rms", [True, False])
+@pytest.mark.parametrize("rows,H", [(37, 256), (2048, 4096), (5, 5120)])
+def test_norm_fwd_bwd(is_rms, rows, H):
+    from hotspa_ae_b200.ops import functional as Fn
+    torch.manual_seed(2)
+    x = torch.randn(rows, H, device=_dev(), dtype=torch.bfloat16)
+    r = torch.randn(rows, H, device=_dev(), dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device=_dev())).to(torch.bfloat16)
+    b = (0.1 * torch.randn(H, device=_dev())).to(torch.bfloat16)
+    dy = torch.randn(rows, H, device=_dev(), dtype=torch.bfloat16)
+    dh = torch.randn(rows, H, device=_dev(), dtype=torch.bfloat16)
+
+    def run(xx, rr, ww, bb, cuda_kernel):
+        xx, rr, ww = xx.clone().requires_grad_(True), rr.clone().requires_grad_(True), ww.clone().requires_grad_(True)
+        bb = bb.clone().requires_grad_(True)
+        if is_rms:
+            y, h = Fn.rms_norm(xx, ww, 1e-6, rr)
+        else:
+            y, h = Fn.layer_norm(xx, ww, bb, 1e-5, rr)
+        torch.autograd.backward([y, h], [dy.to(y.device, y.dtype), dh.to(h.device, h.dtype)])
+        return y, h, xx.grad, rr.grad, ww.grad, (None if is_rms else bb.grad)
+
+    got = run(x, r, w, b, True)
+    ref = run(x.float().cpu(), r.float().cpu(), w.float().cpu(), b.float().cpu(), False)
+    dy, dh = dy, dh
+    names = ["y", "h", "dx", "dres", "dw", "db"]
+    for n, g_, r_ in zip(names, got, ref):
+        if r_ is None:
+            continue
+        g_ = g_.float().cpu()
+        tol = 3e-2 * r_.abs().max().item() + 1e-2
+        assert (g_ - r_).abs().max().item() <= tol, f"{n}: {(g_ - r_).abs().max().item()} > {tol}"
+
+
+def test_norm_main_grad_accumulates():
+    from hotspa_ae_b200.ops import functional as Fn
+    x = torch.randn(64, 512, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(512, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w.main_grad = torch.full((512,), 3.0, device=_dev())
+    y = Fn.rms_norm(x, w)
+    y.backward(torch.ones_like(y))
+    xf = x.detach().float()
+    xh = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)
+    assert torch.allclose(w.main_grad, 3.0 + xh.sum(0), rtol=2e-2, atol=5e-2)
+    assert w.grad is None
+
+
+def test_rope_matches_reference_and_inverts():
+    from hotspa_ae_b200.ops import functional as Fn
+    T, heads, hd = 300, 4, 128
+    qkv = torch.randn(T, heads * 3 * hd, device=_dev(), dtype=torch.bfloat16)
+    pos = torch.arange(T, device=_dev()) % 77
+    out = Fn.rope_qkv(qkv.clone(), pos, heads, hd, 4096)
+    ref = Fn._rope_torch(qkv.float().cpu(), pos.cpu(), *[t.cpu() for t in Fn.rope_tables(4096, hd, _dev())], heads, hd, 1.0)
+    assert torch.allclose(out.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+    x = qkv.clone().requires_grad_(True)
+    y = Fn.rope_qkv(x * 1.0, pos, heads, hd, 4096)
+    (g,) = torch.autograd.grad(y, x, out)          # conj rotation of the rotated tensor gives the input back
+    assert torch.allclose(g.float(), qkv.float(), rtol=3e-2, atol=3e-2)
+
+
+def test_swiglu_fwd_bwd():
+    from hotspa_ae_b200.ops import functional as Fn
+    x = torch.randn(257, 2 * 1376, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = Fn.swiglu(x)
+    dy = torch.randn_like(y)
+    (gx,) = torch.autograd.grad(y, x, dy)
+    xf = x.detach().float().cpu().requires_grad_(True)
+    yf = torch.nn.functional.silu(xf[:, 0::2]) * xf[:, 1::2]
+    yf.backward(dy.float().cpu())
+    assert torch.allclose(y.float().cpu(), yf, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(gx.float().cpu(), xf.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("V,vocab_start", [(1000, 0), (32000, 0), (16000, 16000)])
+def test_cross_entropy_rows(V, vocab_start):
+    from hotspa_ae_b200.ops import functional as Fn
+    rows = 129
+    torch.manual_seed(3)
+    logits = (3 * torch.randn(rows, V, device=_dev())).to(torch.bfloat16)
+    labels = torch.randint(vocab_start, vocab_start + V, (rows,), device=_dev())
+    labels[5] = -1
+    lf = logits.float().cpu().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, (labels.cpu() - vocab_start).clamp(min=-1).where(labels.cpu() >= 0, torch.tensor(-1)),
+                                            ignore_index=-1, reduction="none")
+    x = logits.clone().requires_grad_(True)
+    loss = Fn.cross_entropy_rows(x * 1.0, labels, -1, vocab_start)
+    assert torch.allclose(loss.float().cpu(), ref, rtol=1e-2, atol=1e-2)
+    w = torch.rand(rows, device=_dev())
+    (g,) = torch.autograd.grad(loss, x, w)
+    ref.backward(w.cpu())
+    assert (g.float().cpu() - lf.grad).abs().max().item() < 1e-2
+
+
+def test_embedding_fwd_bwd():
+    from hotspa_ae_b200.ops import functional as Fn
+    V, H, T = 500, 256, 333
+    table = torch.randn(V, H, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    table.main_grad = torch.zeros(V, H, device=_dev())
+    ids = torch.randint(0, 2 * V, (T,), device=_dev())
+    out = Fn.embedding(table, ids, 0)
+    ok = ids < V
+    ref = table.detach()[ids.clamp(max=V - 1)] * ok[:, None]
+    assert torch.equal(out, ref)
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    want = torch.zeros(V, H, device=_dev())
+    want.index_add_(0, ids[ok], dy[ok].float())
+    assert torch.allclose(table.main_grad, want, rtol=1e-3, atol=1e-3)
+
+
+def test_adam_flat():
+    from hotspa_ae_b200.optim import AdamOptimizer
+    n = 100003
+    torch.manual_seed(4)
+    p = torch.randn(n, device=_dev()); m = torch.zeros(n, device=_dev()); v = torch.zeros(n, device=_dev())
+    g = torch.randn(n, device=_dev()); out = torch.empty(n, device=_dev(), dtype=torch.bfloat16)
+    p2, g2 = p.cpu().clone(), g.cpu().clone()
+    m2, v2, out2 = torch.zeros(n), torch.zeros(n), torch.empty(n)
+    opt = AdamOptimizer(lr=1e-2, weight_decay=0.01)
+    for step in (1, 2):
+        g.copy_(g2)
+        opt.apply_flat(p, m, v, g, out, step, 0.5)
+        gg = g2.clone()
+        opt.apply_flat(p2, m2, v2, gg, out2, step, 0.5)
+    assert torch.allclose(p.cpu(), p2, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(out.float().cpu(), p2, rtol=1e-2, atol=1e-2)
+    assert float(g.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("heads,hd,lens", [(2, 128, [5, 130, 64, 300]), (4, 128, [1024]), (1, 128, [129, 127, 1, 255])])
+def test_attention_varlen_matches_reference(heads, hd, lens):
+    from hotspa_ae_b200.ops.attention import attention_varlen
+    torch.manual_seed(5)
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=_dev())
+    qkv = torch.randn(T, heads, 3 * hd, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    out = attention_varlen(qkv, cu, heads, hd, max(lens))
+    dout = torch.randn_like(out)
+    (g,) = torch.autograd.grad(out, qkv, dout)
+    q2 = qkv.detach().float().cpu().requires_grad_(True)
+    ref = attention_varlen(q2, cu.cpu(), heads, hd, max(lens), backend="torch")
+    ref.backward(dout.float().cpu())
+    assert (out.float().cpu() - ref).abs().max().item() < 3e-2
+    assert (g.float().cpu() - q2.grad).abs().max().item() < 6e-2 * max(1.0, q2.grad.abs().max().item())

@@ -331,7 +331,7 @@ class Executor:
         sid = plan.sid
         values = dict(recv_vals)
         for seg in plan.segments:
-            if not seg.recompute or not torch.is_grad_enabled():
+            if not seg.recompute or not torch.is_grad_enabled() or not self._recompute_on(sid):
                 self._run_ops(rt, seg.ops, values, feeds, params, sid)
                 continue
             ext = [self._value(t, values, feeds, params, sid) for t in seg.ext_inputs]
@@ -347,6 +347,10 @@ class Executor:
             for i, v in zip(out_ids, outs):
                 values[i] = v
         return values
+
+    def _recompute_on(self, sid: int) -> bool:
+        rs = getattr(self.graph, "recompute_strategies", None)
+        return rs is None or sid in rs
 
     # ---- run ----------------------------------------------------------------------------------------------
     def _split_feeds(self, feed_dict, nmb):
@@ -378,15 +382,16 @@ class Executor:
             return []
         rt = Runtime(self, plan)
         params = self.store.param_views(sid)
-        feeds = self._split_feeds(feed_dict, nmb)
+        feeds = self._split_feeds(feed_dict, nmb) if nmb > 0 else []
         wants_train = any(getattr(f, "is_train_op", False) for f in fetches) or loss is not None
         loss_t = loss if loss is not None else next((f for f in fetches if not getattr(f, "is_train_op", False)), None)
         n_stage = len(plan.stages)
         stage = plan.my_stage
         if stage < 0:
             return []
-        seed = grad_scale / (nmb * plan.dp)
-        tasks = (C.schedule_1f1b if self.pipeline_schedule == "1f1b" else C.schedule_gpipe)(n_stage, stage, nmb)
+        seed = grad_scale / max(1, nmb * plan.dp)
+        tasks = [] if nmb == 0 else \
+            (C.schedule_1f1b if self.pipeline_schedule == "1f1b" else C.schedule_gpipe)(n_stage, stage, nmb)
         live: dict[int, dict] = {}
         losses: dict[int, torch.Tensor] = {}
         fetched: dict[int, list] = {f.id: [None] * nmb for f in fetches if not getattr(f, "is_train_op", False)}
@@ -454,7 +459,7 @@ class Executor:
         if wants_train and run_level == GRAD:
             self.store.hand_grads_home(sid)
         if wants_train and run_level == UPDATE:
-            if self.store.home != sid:
+            if self.store.home != self.store.canonical(sid):
                 raise RuntimeError("UPDATE must run under the home strategy (the one that was allocated first)")
             self.store.reduce_and_step(self.graph.optimizer, 1.0)
 

@@ -111,6 +111,7 @@ class ParamStore:
         self.sender_policy = 3
         self.seed = 2023
         self.symm = None
+        self._canon: dict[int, int] = {}
 
     # ---- layouts / arenas ------------------------------------------------------------------------
     @property
@@ -132,18 +133,35 @@ class ParamStore:
             return self.symm.alloc(numel, dtype)
         return torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
 
+    def canonical(self, sid: int) -> int:
+        """Strategies whose parameters have identical distributed states and device groups share arenas
+        (they may still differ in schedule or recomputation): returns the smallest such strategy id."""
+        if sid not in self._canon:
+            self._canon[sid] = sid
+            for other in range(sid):
+                same = all(p.ds_hierarchy[sid].check_equal(p.ds_hierarchy[other]) and
+                           [g.ranks() for g in p.dg_hierarchy[sid]] == [g.ranks() for g in p.dg_hierarchy[other]]
+                           for p in self.graph.parameters)
+                if same:
+                    self._canon[sid] = self.canonical(other)
+                    break
+        return self._canon[sid]
+
     def arena(self, sid: int) -> torch.Tensor:
+        sid = self.canonical(sid)
         if sid not in self.compute:
             self.compute[sid] = self._alloc(self.layout(sid).total, self.compute_dtype)
         return self.compute[sid]
 
     def grad_arena(self, sid: int) -> torch.Tensor:
+        sid = self.canonical(sid)
         if sid not in self.grads:
             self.grads[sid] = self._alloc(self.layout(sid).total, torch.float32)
         return self.grads[sid]
 
     def param_views(self, sid: int) -> dict:
         """param id -> leaf tensor viewing the compute arena, with ``.main_grad`` viewing the grad arena."""
+        sid = self.canonical(sid)
         if sid not in self.views:
             lay, arena, garena = self.layout(sid), self.arena(sid), self.grad_arena(sid)
             out = {}
@@ -167,6 +185,7 @@ class ParamStore:
     def materialize_home(self, sid: int) -> None:
         if self.home is not None:
             return
+        sid = self.canonical(sid)
         self.home = sid
         lay, arena = self.layout(sid), self.arena(sid)
         self.grad_arena(sid)
@@ -194,6 +213,7 @@ class ParamStore:
 
     def ensure_compute(self, sid: int) -> None:
         """Make strategy `sid`'s compute arena hold the current weights (hot switch when needed)."""
+        sid = self.canonical(sid)
         if self.home is None:
             self.materialize_home(sid)
             return
@@ -297,6 +317,7 @@ class ParamStore:
 
     def hand_grads_home(self, sid: int) -> None:
         """Add strategy `sid`'s accumulated gradients into the home strategy's grad arena and clear them."""
+        sid = self.canonical(sid)
         if sid == self.home:
             return
         self.switch(sid, self.home, "grad")

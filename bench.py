@@ -1,0 +1,232 @@
+"""Headline benchmark: Llama-7B variable-length training with parallelism hot switching, tokens/s.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 5 --warmup 3
+
+Every step trains on one synthetic global batch of ~32K tokens per GPU (weak scaling: 256K at 8 GPUs): sequence
+lengths lognormal (median ~800, ~90 % <= 4K, clipped at 32K), token ids uniform, weights random N(0, 0.02),
+bf16 compute with fp32 master weights and Adam.  The batch is bucketed by length; every bucket runs under its
+own (dp, tp, pp) strategy inside the same optimizer step, parameters and gradients hot-switch between layouts.
+
+Two timed regions of K steps each, both bracketed by a barrier + ``torch.cuda.synchronize()`` and timed with
+CUDA events, max over ranks:
+  * ``value``      device-resident inputs (packed and uploaded before the region), no loss read-back;
+  * ``e2e.value``  ``HotSwitchTrainer.step(sequences)``: host bucketing/packing, upload from pinned host
+                   memory, the device step, and the device->host read of the loss, every step.
+``--impl reference`` reports why the reference implementation cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOKENS_PER_GPU = 32768
+
+# (bucket bounds, [(dp, tp, pp, zero) per bucket, longest bucket first]) per world size, Llama-7B
+PLANS = {
+    1: ((32768, 0), [(1, 1, 1, False)]),
+    2: ((32768, 4096, 0), [(1, 2, 1, False), (2, 1, 1, True)]),
+    4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)]),
+    8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)]),
+}
+
+REFERENCE_UNAVAILABLE = (
+    "reference is not pip-installable (no setup.py/pyproject.toml; its CMake build needs MPI, the missing "
+    "cutlass/oneDNN tarballs and compiles sm_80/86 only, and its FlashAttention wrapper asserts sm8x/sm90)")
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="7b")
+    ap.add_argument("--tokens_per_gpu", type=int, default=TOKENS_PER_GPU)
+    ap.add_argument("--switch_mode", default="auto")
+    ap.add_argument("--no_e2e", action="store_true", help="skip the end-to-end region (profiling runs)")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling runs only; the "
+                                                           "result is then marked as not the headline config)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [c for c, p in zip(sm, power) if p > 300.0] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from hotspa_ae_b200.ops import _lib
+    from hotspa_ae_b200.train.trainer import HotSwitchTrainer
+    from hotspa_ae_b200.utils import data as D
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU")
+    bounds, strategies = PLANS[world]
+    overrides = {"vocab_size": 32000}
+    if args.layers:
+        overrides["num_layers"] = args.layers
+    trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=True,
+                               switch_mode=args.switch_mode, **overrides)
+    vocab = trainer.config.vocab_size
+    tokens = args.tokens_per_gpu * world
+    K, W = args.steps, args.warmup
+
+    def batch(i):
+        lens = D.lognormal_lengths(tokens, seed=1000 + i, max_len=bounds[0])
+        return D.synthetic_sequences(lens, vocab, seed=1000 + i)
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: int) -> int:
+        t = torch.tensor([x], dtype=torch.int64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t)
+        return int(t.item())
+
+    # ---- region A: device-resident inputs ------------------------------------------------------------
+    seqs = [batch(i) for i in range(W + K)]
+    for i in range(W):
+        trainer.run_prepared(trainer.prepare(seqs[i]), read_loss=False)
+    prepared = []
+    for i in range(W, W + K):
+        # one staging buffer set per prepared batch so that all K uploads can be in flight before the region
+        trainer._pinned = {}
+        prepared.append(trainer.prepare(seqs[i]))
+    sampler = ClockSampler()
+    fence()
+    if rank == 0:
+        sampler.start()
+    l0 = _lib.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for pb in prepared:
+        trainer.run_prepared(pb, read_loss=False)
+    e1.record()
+    fence()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = sum_over_ranks(_lib.launches() - l0)
+    ms_a = max_over_ranks(e0.elapsed_time(e1))
+    tok_a = sum(p["tokens"] for p in prepared)
+    _lib.check_status()
+
+    # ---- region B: end to end through the public API -------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        seqs_b = [batch(100 + i) for i in range(K)]
+        trainer.step(batch(99))
+        fence()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        h2d = d2h = 0
+        last_loss = None
+        for s in seqs_b:
+            r = trainer.step(s)
+            h2d += r.h2d_bytes
+            d2h += r.d2h_bytes
+            last_loss = r.loss
+        e1.record()
+        fence()
+        ms_b = max_over_ranks(e0.elapsed_time(e1))
+        tok_b = sum(sum(len(x) for x in s) for s in seqs_b)
+        e2e = {"value": tok_b / (ms_b / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d // K,
+               "d2h_bytes_per_step": d2h // K, "ms_per_step": ms_b / K, "last_loss": last_loss}
+        _lib.check_status()
+
+    if rank == 0:
+        par = "+".join(f"dp{dp}tp{tp}pp{pp}" + ("z" if z else "") for dp, tp, pp, z in strategies)
+        out = {
+            "metric": "Llama-7B varlen hot-switch training throughput", "value": tok_a / (ms_a / 1e3),
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_a / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (lognormal lengths median 800 clipped at 32K, uniform token ids, random-init weights)",
+            "impl": "ours",
+            "config": {"model": f"llama-{args.model}" + (f"-{args.layers}layers(not headline)" if args.layers else ""),
+                       "global_batch": f"{tokens} tokens/step", "seq_len": f"varlen<= {bounds[0]}",
+                       "parallelism": par, "buckets": list(bounds), "optimizer": "Adam fp32 master",
+                       "recompute": "per block", "switch_mode": trainer.switch_mode,
+                       "l2": "inputs larger than L2 (weights and activations of several GB stream every step)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -133,6 +133,20 @@ class Executor:
         self.stats: dict = {"runs": 0}
         self.pipeline_schedule = "1f1b"
 
+    def configure_switch(self, mode: str):
+        """'nccl': pack -> grouped send/recv -> unpack.  'fused': one pull kernel over peer-mapped arenas
+        (needs CUDA and more than one rank; arenas are then allocated from the symmetric heap)."""
+        if mode not in ("nccl", "fused"):
+            raise ValueError(f"unknown switch mode {mode}")
+        if mode == "fused":
+            if self.mesh.torch_device.type != "cuda" or self.mesh.world_size == 1:
+                mode = "nccl"
+            else:
+                from ..parallel import symm
+                self.store.symm = symm.heap()
+        self.store.switch_mode = mode
+        return mode
+
     def on_strategies_added(self):
         self.plans.clear()
         return self

@@ -1,0 +1,110 @@
+"""Command-line training entry: Llama with parallelism hot switching (or one static strategy).
+
+    torchrun --nproc-per-node 8 -m hotspa_ae_b200.train.llama_hot_switch --model_size 7b \\
+        --bucket_sizes "32768 16384 4096 0" --strategies "1,4,2 2,2,2 8,1,1" --zero --bf16 \\
+        --global_tokens 262144 --steps 10
+
+``--strategies`` lists one "dp,tp,pp" per bucket, longest bucket first (the first one is the home strategy).
+``--ds_parallel_config`` takes strategy JSON files instead, in the reference's order (home first, then the
+strategy of the shortest bucket ... the strategy of the second-longest bucket).  One strategy and two bounds
+give static-parallel training.  Data is synthetic (lognormal lengths, uniform token ids) unless ``--json_file``
+names a jsonl file with a ``--json_key`` text field and a vocab/merges pair for the GPT-2 BPE tokenizer.
+Reference entry points: hotspa/llama_hot_switch.py:489-594, hotspa/scripts/llama_hot_switch.sh,
+hotspa/scripts/llama_static_parallel.sh.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+from ..parallel import mesh as M
+from ..utils import data as D
+from .trainer import build_trainer_from_args, timed_steps
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--model_size", default="7b", help="tiny | 3b | 7b | 13b | 32b")
+    ap.add_argument("--hot_switch", action="store_true", help="accepted for compatibility: several strategies switch")
+    ap.add_argument("--strategies", default="1,1,1", help='"dp,tp,pp" per bucket, longest bucket first')
+    ap.add_argument("--reference_order", action="store_true",
+                    help="--strategies is in the reference's order (home, shortest ... second longest)")
+    ap.add_argument("--ds_parallel_config", default="", help="comma/space separated strategy JSON files")
+    ap.add_argument("--num_strategy", type=int, default=0, help="accepted for compatibility")
+    ap.add_argument("--bucket_sizes", default="32768 0")
+    ap.add_argument("--zero", action="store_true", help="shard optimizer state over data-parallel ranks (ZeRO-1)")
+    ap.add_argument("--global_tokens", type=int, default=0, help="synthetic tokens per step (whole job)")
+    ap.add_argument("--global_batch_size", type=int, default=64, help="sequences per step when reading a dataset")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("-e", "--epochs", type=int, default=1)
+    ap.add_argument("--lr", type=float, default=1e-5)
+    ap.add_argument("--adam_weight_decay", type=float, default=0.0)
+    ap.add_argument("--bf16", action="store_true")
+    ap.add_argument("--no_recompute", action="store_true")
+    ap.add_argument("--switch_mode", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--vocab_size", type=int, default=0)
+    ap.add_argument("--hidden_size", type=int, default=0)
+    ap.add_argument("--ffn_hidden_size", type=int, default=0)
+    ap.add_argument("--num_hidden_layers", type=int, default=0)
+    ap.add_argument("-a", "--num_attention_heads", type=int, default=0)
+    ap.add_argument("-s", "--seq_length", type=int, default=0, help="maximum sequence length (default: first bucket)")
+    ap.add_argument("--json_file", default="")
+    ap.add_argument("--json_key", default="content")
+    ap.add_argument("--vocab_file", default="")
+    ap.add_argument("--merge_file", default="")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--log_file", default="", help="append one JSON line per step (rank 0)")
+    ap.add_argument("--save_checkpoint", default="", help="directory to write a checkpoint into after training")
+    ap.add_argument("--load_checkpoint", default="", help="directory (or .bin file) to load weights from")
+    ap.add_argument("--use_flash_attn", action="store_true", help="accepted for compatibility (always on)")
+    return ap.parse_args(argv)
+
+
+def batches(args, trainer):
+    bounds = [int(x) for x in args.bucket_sizes.split()]
+    max_len = args.seq_length or bounds[0]
+    vocab = trainer.config.vocab_size
+    if args.json_file:
+        from ..utils.dataset import LlamaJsonDataset, global_batches
+        ds = LlamaJsonDataset(args.json_file, args.json_key, max_len, args.vocab_file, args.merge_file)
+        yield from global_batches(ds, args.global_batch_size, args.steps * args.epochs, seed=args.seed)
+        return
+    world = M.mesh().world_size
+    tokens = args.global_tokens or 32768 * world
+    for i in range(args.steps * args.epochs):
+        lens = D.lognormal_lengths(tokens, seed=args.seed + i, max_len=max_len)
+        yield D.synthetic_sequences(lens, vocab, seed=args.seed + i)
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    trainer = build_trainer_from_args(args)
+    rank = M.mesh().rank
+    if args.load_checkpoint:
+        from ..utils.checkpoint import load_checkpoint
+        load_checkpoint(trainer.model, args.load_checkpoint, graph=trainer.graph)
+    logf = open(args.log_file, "a") if (args.log_file and rank == 0) else None
+
+    def log(msg):
+        print(msg, flush=True)
+
+    for i, (res, dt) in enumerate(timed_steps(trainer, batches(args, trainer), log)):
+        if logf is not None:
+            logf.write(json.dumps({"step": i, "loss": res.loss, "time_s": dt, "tokens": res.tokens,
+                                   "tokens_per_s": res.tokens / dt, "buckets": res.buckets}) + "\n")
+            logf.flush()
+    if args.save_checkpoint:
+        from ..utils.checkpoint import save_checkpoint
+        save_checkpoint(trainer.model, args.save_checkpoint, graph=trainer.graph)
+    if logf is not None:
+        logf.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

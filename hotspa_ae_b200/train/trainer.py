@@ -1,0 +1,270 @@
+"""Hot-switch / static-parallel Llama trainer: the call a user of the framework makes.
+
+``HotSwitchTrainer(model, strategies, bucket_bounds)`` defines one Llama over every strategy
+(``strategies[i]`` runs bucket ``i``; bucket 0 is the longest and its strategy is the *home*
+strategy that owns the fp32 master weights and the optimizer state).  ``step(sequences)`` takes one
+global batch of token sequences, buckets them by length, packs every bucket first-fit into rows,
+and runs, inside one optimizer step,
+
+    GRAD   strategy n-1 on bucket n-1 (shortest) ... GRAD strategy 1 on bucket 1
+    UPDATE strategy 0 on bucket 0 (longest)
+
+hot-switching parameters (copy) and accumulated gradients (add) between the strategies' layouts.
+A single strategy with a single bucket is the static-parallel mode.
+
+Reference application: hotspa/llama_hot_switch.py (pretrain :244-311, run_plan :313-487, buckets
+:125-208).  Divergences on purpose: every token weighs the same in the loss (the reference averages
+each bucket separately), padding and cross-document targets are masked, attention is per document,
+rows are balanced over data-parallel ranks instead of being dropped.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+import hetu as ht
+
+from ..models.llama import LlamaConfig, LlamaLMHeadModel, llama_config
+from ..parallel import mesh as M
+from ..parallel.strategy_config import generate_llama_3d_config, propagate_zero, read_ds_parallel_config
+from ..utils import data as D
+
+
+@dataclass
+class StepResult:
+    loss: float                    # mean loss per target token of the whole global batch
+    tokens: int                    # real (non-padding) tokens consumed by the step
+    target_tokens: int             # tokens that had a target
+    h2d_bytes: int                 # bytes this rank copied host -> device for the step's inputs
+    d2h_bytes: int                 # bytes this rank read back (loss statistics)
+    buckets: list = field(default_factory=list)     # per bucket: dict(strategy, rows, tokens, micro_batches)
+
+
+class HotSwitchTrainer:
+    def __init__(self, model: str | LlamaConfig = "7b", strategies=((1, 1, 1, False),), bucket_bounds=(32768, 0),
+                 lr: float = 1e-4, dtype=torch.bfloat16, recompute: bool | list = True, switch_mode: str = "auto",
+                 weight_decay: float = 0.0, ds_parallel_configs: list | None = None, gpus_per_node: int = 8,
+                 pad_id: int = 0, seed: int = 2023, **config_overrides):
+        self.mesh = ht.init_comm_group(gpus_per_node)
+        world = self.mesh.world_size
+        self.config = model if isinstance(model, LlamaConfig) else llama_config(model, **config_overrides)
+        bounds = [int(b) for b in bucket_bounds]
+        if sorted(bounds, reverse=True) != bounds or len(bounds) < 2:
+            raise ValueError("bucket_bounds must be descending, e.g. (32768, 16384, 4096, 0)")
+        self.bounds = bounds
+        n_buckets = len(bounds) - 1
+        if ds_parallel_configs is not None:
+            cfgs = [propagate_zero(c) for c in ds_parallel_configs]
+        else:
+            cfgs = [propagate_zero(generate_llama_3d_config(self.config.num_layers, world, dp, tp, pp, zero))
+                    for dp, tp, pp, zero in strategies]
+        if len(cfgs) != n_buckets:
+            raise ValueError(f"{len(cfgs)} strategies for {n_buckets} buckets")
+        self.cfgs = cfgs
+        self.config.max_seq_len = max(self.config.max_seq_len, bounds[0])
+        self.config.recompute = bool(recompute)
+        self.pad_id = pad_id
+        self.device = self.mesh.torch_device
+        self.step_count = 0
+
+        with ht.graph("define_and_run", num_strategy=len(cfgs)) as g:
+            ac = ht.autocast(dtype) if dtype != torch.float32 else None
+            if ac is not None:
+                ac.__enter__()
+            try:
+                self.model = LlamaLMHeadModel(self.config, cfgs)
+                in_ds, in_dg, lab_ds, lab_dg = [], [], [], []
+                for c in cfgs:
+                    u, dg = ht.nn.config2ds(c["input"]); in_ds.append(u); in_dg.append(dg)
+                    u, dg = ht.nn.config2ds(c["label"]); lab_ds.append(u); lab_dg.append(dg)
+                self.config.mbs_times_dp_symbol = ht.IntSymbol(1)
+                self.config.seq_len_symbol = ht.IntSymbol(bounds[0])
+                self.docs_symbol = ht.IntSymbol(2)
+                shape = [self.config.mbs_times_dp_symbol, self.config.seq_len_symbol]
+                self.input_ids = ht.parallel_placeholder(ht.int64, shape, in_ds, in_dg, name="input_ids")
+                self.position_ids = ht.parallel_placeholder(ht.int64, shape, in_ds, in_dg, name="position_ids")
+                self.cu_seqlens = ht.parallel_placeholder(ht.int32, [self.config.mbs_times_dp_symbol, self.docs_symbol],
+                                                          in_ds, in_dg, name="cu_seqlens")
+                self.labels = ht.parallel_placeholder(ht.int64, shape, lab_ds, lab_dg, name="labels")
+                self.loss = self.model(self.input_ids, self.position_ids, self.cu_seqlens, self.labels,
+                                       reduction="sum")
+                self.optimizer = ht.AdamOptimizer(lr=lr, weight_decay=weight_decay)
+                self.train_op = self.optimizer.minimize(self.loss)
+            finally:
+                if ac is not None:
+                    ac.__exit__(None, None, None)
+        self.graph = g
+        if isinstance(recompute, (list, tuple, set)):
+            g.recompute_strategies = set(recompute)
+        store = g.executor.store
+        store.seed = seed
+        if switch_mode == "auto":
+            switch_mode = "nccl"
+        self.switch_mode = switch_mode
+        g.executor.configure_switch(switch_mode)
+        self.in_ds = in_ds
+        self._dp_index = [self._my_dp_index(s) for s in range(len(cfgs))]
+        self._pinned: dict = {}
+        self._stat_dev = None
+        self._upload_done = None
+        # materialise the home strategy (fp32 master + optimizer state) before the first step
+        g.run(self.loss, [self.loss, self.train_op], {}, 0, 0, ht.run_level("alloc"))
+
+    # ---- topology helpers ---------------------------------------------------------------------------
+    def dp_of(self, sid: int) -> int:
+        return self.in_ds[sid].get(0).get_dim(0)
+
+    def tp_of(self, sid: int) -> int:
+        return self.in_ds[sid].get(0).get_dim(-1)
+
+    def _my_dp_index(self, sid: int) -> int:
+        rank = self.mesh.rank
+        for st in self.graph.executor.plan(sid).stages:
+            if rank in st:
+                return int(self.input_ids.ds(sid).get_dup_group_index(list(st).index(rank)))
+        return 0
+
+    # ---- host -> device staging -----------------------------------------------------------------------
+    def _stage(self, key, arr: np.ndarray) -> torch.Tensor:
+        """Copy `arr` into a (grow-only) pinned host buffer and return the pinned view the executor uploads."""
+        t = torch.from_numpy(np.ascontiguousarray(arr))
+        if self.device.type != "cuda":
+            return t
+        buf = self._pinned.get(key)
+        if buf is None or buf.numel() < t.numel() or buf.dtype != t.dtype:
+            buf = torch.empty(int(t.numel() * 1.5) + 16, dtype=t.dtype).pin_memory()
+            self._pinned[key] = buf
+        view = buf[:t.numel()].view(t.shape)
+        view.copy_(t)
+        return view
+
+    # ---- one optimizer step ----------------------------------------------------------------------------
+    def plan_batch(self, sequences) -> list:
+        lengths = [len(s) for s in sequences]
+        return D.bucket_and_pack(lengths, self.bounds, 1, False)
+
+    def prepare(self, sequences) -> dict:
+        """Host side of a step: bucket, pack, build this rank's micro-batches, stage them in pinned memory and
+        start their upload.  The result can be run later (and more than once) with :meth:`run_prepared`."""
+        packed = self.plan_batch(sequences)
+        if self._upload_done is not None:
+            self._upload_done.synchronize()        # the pinned staging buffers are reused: previous upload first
+        # every rank can count the global number of targets: one per token except the last of each document
+        total_targets = max(int(sum(max(len(s) - 1, 0) for s in sequences)), 1)
+        h2d, buckets = 0, []
+        for b, pk in enumerate(packed):
+            if not pk.rows:
+                buckets.append(None)
+                continue
+            mb = D.micro_batches_for_rank(sequences, pk, self.dp_of(b), self._dp_index[b], self.pad_id)
+            feed = {}
+            for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"),
+                            (self.position_ids, "position_ids"), (self.cu_seqlens, "cu_seqlens")):
+                t = self._stage((b, key), mb[key])
+                h2d += t.numel() * t.element_size()
+                feed[ph] = t.to(self.device, non_blocking=True)
+            buckets.append(dict(feed=feed, nmb=mb["num_micro_batches"], max_len=pk.max_len,
+                                docs=mb["cu_seqlens"].shape[1], rows=len(pk.rows), tokens=pk.tokens))
+        if self.device.type == "cuda":
+            self._upload_done = torch.cuda.Event()
+            self._upload_done.record()
+        return dict(buckets=buckets, total_targets=total_targets, h2d_bytes=h2d,
+                    tokens=int(sum(len(s) for s in sequences)))
+
+    def run_prepared(self, batch: dict, read_loss: bool = True) -> StepResult:
+        """Device side of a step: GRAD runs for buckets n-1 .. 1, UPDATE for bucket 0.  With ``read_loss`` the
+        global mean loss is all-reduced and read back to the host (the only synchronisation of the step)."""
+        n = len(batch["buckets"])
+        total_targets = batch["total_targets"]
+        if self._stat_dev is None:
+            self._stat_dev = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._stat_dev.zero_()
+        info = []
+        for b in list(range(n - 1, 0, -1)) + [0]:
+            bk = batch["buckets"][b]
+            level = ht.run_level("update" if b == 0 else "grad")
+            if bk is None:
+                if b == 0:
+                    self.graph.run(self.loss, [self.loss, self.train_op], {}, 0, 0, level)
+                info.append(dict(strategy=b, rows=0, tokens=0, micro_batches=0))
+                continue
+            nmb, dp = bk["nmb"], self.dp_of(b)
+            self.config.mbs_times_dp_symbol.set_data(dp)
+            self.config.seq_len_symbol.set_data(bk["max_len"])
+            self.docs_symbol.set_data(bk["docs"])
+            out = self.graph.run(self.loss, [self.loss, self.train_op], bk["feed"], nmb, b, level,
+                                 grad_scale=float(nmb * dp) / total_targets)
+            if out and out[0] is not None:
+                # tensor-parallel peers of the last stage hold the same loss: count it once
+                self._stat_dev += out[0].float().sum() / self.tp_of(b)
+            info.append(dict(strategy=b, rows=bk["rows"], tokens=bk["tokens"], micro_batches=nmb))
+        self.step_count += 1
+        loss = self._collect_loss(total_targets) if read_loss else float("nan")
+        return StepResult(loss, batch["tokens"], total_targets, batch["h2d_bytes"], 4 if read_loss else 0, info)
+
+    def step(self, sequences) -> StepResult:
+        """One optimizer step over the global batch `sequences` (list of 1-D integer token arrays; every rank
+        passes the same list): host-side packing, upload from pinned memory, the device step, loss read-back."""
+        return self.run_prepared(self.prepare(sequences), read_loss=True)
+
+    def _collect_loss(self, total_targets: int) -> float:
+        """Global mean loss per target token: per-rank loss sums, all-reduced, read back to the host."""
+        stat = self._stat_dev.clone()
+        if self.mesh.world_size > 1:
+            dist.all_reduce(stat)
+        return float(stat.item()) / total_targets          # the step's device -> host read
+
+    # ---- conveniences ------------------------------------------------------------------------------------
+    def switch_log(self) -> list:
+        return self.graph.executor.store.switch_log
+
+    def state_dict(self):
+        return self.model.state_dict()
+
+
+def build_trainer_from_args(args) -> HotSwitchTrainer:
+    bounds = [int(x) for x in str(args.bucket_sizes).split()]
+    if args.ds_parallel_config:
+        cfgs = read_ds_parallel_config(args.ds_parallel_config)
+        strategies = None
+    else:
+        cfgs = None
+        strategies = []
+        for s in args.strategies.split():
+            dp, tp, pp = (int(x) for x in s.split(","))
+            strategies.append((dp, tp, pp, bool(args.zero)))
+    overrides = {}
+    for key, attr in (("hidden_size", "hidden_size"), ("ffn_hidden_size", "ffn_hidden_size"),
+                      ("num_layers", "num_hidden_layers"), ("num_heads", "num_attention_heads"),
+                      ("vocab_size", "vocab_size")):
+        v = getattr(args, attr, None)
+        if v is not None and v > 0:
+            overrides[key] = v
+    if cfgs is not None:
+        # the reference convention lists strategies as: longest bucket first, then shortest ... second longest
+        cfgs = [cfgs[0]] + list(reversed(cfgs[1:]))
+    elif getattr(args, "reference_order", False):
+        strategies = [strategies[0]] + list(reversed(strategies[1:]))
+    return HotSwitchTrainer(args.model_size, strategies or (), bounds, lr=args.lr,
+                            dtype=torch.bfloat16 if args.bf16 else torch.float32, recompute=not args.no_recompute,
+                            switch_mode=args.switch_mode, weight_decay=args.adam_weight_decay,
+                            ds_parallel_configs=cfgs, **overrides)
+
+
+def timed_steps(trainer: HotSwitchTrainer, batches, log=None):
+    out = []
+    for i, seqs in enumerate(batches):
+        t0 = time.perf_counter()
+        res = trainer.step(seqs)
+        if trainer.device.type == "cuda":
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        out.append((res, dt))
+        if log is not None and M.mesh().rank == 0:
+            log(f"step {i}: loss = {res.loss:.4f}, time = {dt:.3f} s, tokens = {res.tokens}, "
+                f"tokens/s = {res.tokens / dt:.0f}")
+    return out

@@ -1,0 +1,203 @@
+"""Micro-benchmarks of the kernel library against the measured roofline of the GPU they run on.
+
+    python -m hotspa_ae_b200.ops.bench_kernels gemm                       # the Llama-7B GEMM shapes
+    python -m hotspa_ae_b200.ops.bench_kernels gemm --m 8192 --n 8192 --k 8192 --iters 3 --no_torch
+    python -m hotspa_ae_b200.ops.bench_kernels attn --tokens 32768
+    python -m hotspa_ae_b200.ops.bench_kernels bandwidth                  # norm / swiglu / adam / cross-entropy
+
+Timing: CUDA events on the launching stream after warm-up, an L2-sized buffer is rewritten between timed
+iterations, the median of the iterations is reported.  Peaks come from ``MEASURED_PEAKS.json`` at the
+repository root when present (copy bandwidth and library bf16 GEMM throughput measured on this machine),
+else from the nominal figures.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+from . import _lib
+from . import functional as Fn
+from .attention import attention_varlen
+from .gemm import gemm
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> dict:
+    path = os.path.join(_ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"tflops": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "gbs": p["hbm_gbs"], "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "gbs": 6650.0, "source": "fallback"}
+
+
+_flush_buf = None
+
+
+def flush_l2():
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush_buf.zero_()
+
+
+def time_ms(fn, iters: int = 10, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return statistics.median(out)
+
+
+LLAMA7B_GEMMS = [
+    # (name, M, N, K, a_mn, b_mn)  for T = 8192 tokens, h = 4096, ffn = 11008
+    ("qkv fwd", 8192, 12288, 4096, False, False),
+    ("o-proj fwd", 8192, 4096, 4096, False, True),
+    ("fc1 fwd", 8192, 22016, 4096, False, False),
+    ("fc2 fwd", 8192, 4096, 11008, False, True),
+    ("lm-head fwd", 8192, 32000, 4096, False, False),
+    ("qkv dgrad", 8192, 4096, 12288, False, True),
+    ("fc1 dgrad", 8192, 4096, 22016, False, True),
+    ("fc2 dgrad", 8192, 11008, 4096, False, False),
+    ("qkv wgrad", 12288, 4096, 8192, True, True),
+    ("fc1 wgrad", 22016, 4096, 8192, True, True),
+    ("fc2 wgrad", 4096, 11008, 8192, True, True),
+]
+
+
+def bench_gemm(args):
+    pk = peaks()
+    shapes = LLAMA7B_GEMMS
+    if args.m:
+        shapes = [("custom", args.m, args.n, args.k, bool(args.a_mn), bool(args.b_mn))]
+    for name, M, N, K, a_mn, b_mn in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+        wgrad = a_mn and b_mn
+        out = torch.zeros((M, N), device="cuda", dtype=torch.float32 if wgrad else torch.bfloat16)
+        ms = time_ms(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=wgrad, tile_n=args.tile_n),
+                     args.iters, args.warmup)
+        _lib.check_status()
+        tf = 2.0 * M * N * K / ms / 1e9
+        line = f"gemm {name:12s} M={M} N={N} K={K} a_mn={int(a_mn)} b_mn={int(b_mn)}: {ms * 1e3:8.1f} us " \
+               f"{tf:7.1f} TFLOP/s = {tf / pk['tflops']:.2f} of {pk['source']} library peak"
+        if not args.no_torch:
+            A = a.t() if a_mn else a
+            B = b if b_mn else b.t()
+            ms_t = time_ms(lambda: torch.matmul(A, B), args.iters, args.warmup)
+            line += f" | torch.matmul {ms_t * 1e3:8.1f} us {2.0 * M * N * K / ms_t / 1e9:7.1f} TFLOP/s"
+        print(line, flush=True)
+
+
+def _varlen_batch(tokens: int, seed: int):
+    from ..utils import data as D
+    lens = D.lognormal_lengths(tokens, seed=seed)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + int(n))
+    return lens, torch.tensor(cu, dtype=torch.int32, device="cuda")
+
+
+def bench_attn(args):
+    pk = peaks()
+    heads, hd, T = args.heads, args.head_dim, args.tokens
+    if args.doc_len:
+        n = T // args.doc_len
+        lens = [args.doc_len] * n
+        cu = torch.arange(0, n + 1, dtype=torch.int32, device="cuda") * args.doc_len
+        T = n * args.doc_len
+    else:
+        lens, cu = _varlen_batch(T, args.seed)
+    flops_fwd = sum(4.0 * heads * hd * (float(n) * (float(n) + 1) / 2) for n in lens)
+    qkv = torch.randn(T, heads, 3 * hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    dout = torch.randn(T, heads * hd, device="cuda", dtype=torch.bfloat16)
+    ms_f = time_ms(lambda: attention_varlen(qkv.detach(), cu, heads, hd), args.iters, args.warmup)
+    out = attention_varlen(qkv, cu, heads, hd)
+    ms_b = time_ms(lambda: torch.autograd.grad(out, qkv, dout, retain_graph=True), args.iters, args.warmup)
+    _lib.check_status()
+    print(f"attn T={T} docs={len(lens)} heads={heads} hd={hd}: fwd {ms_f:.3f} ms {flops_fwd / ms_f / 1e9:.1f} TFLOP/s "
+          f"({flops_fwd / ms_f / 1e9 / pk['tflops']:.2f} of {pk['source']} peak) | bwd {ms_b:.3f} ms "
+          f"{2.5 * flops_fwd / ms_b / 1e9:.1f} TFLOP/s ({2.5 * flops_fwd / ms_b / 1e9 / pk['tflops']:.2f})", flush=True)
+    if not args.no_torch and args.doc_len:
+        q, k, v = (qkv.detach().reshape(-1, args.doc_len, heads, 3, hd)[:, :, :, i].transpose(1, 2) for i in range(3))
+        ms_t = time_ms(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True), args.iters,
+                       args.warmup)
+        print(f"  torch SDPA fwd {ms_t:.3f} ms {flops_fwd / ms_t / 1e9:.1f} TFLOP/s", flush=True)
+
+
+def bench_bandwidth(args):
+    pk = peaks()
+    rows, H, F_ = args.tokens, 4096, 11008
+
+    def report(name, ms, nbytes):
+        gbs = nbytes / ms / 1e6
+        print(f"{name:22s} {ms * 1e3:8.1f} us {gbs:7.0f} GB/s = {gbs / pk['gbs']:.2f} of {pk['source']} copy bandwidth",
+              flush=True)
+
+    x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn_like(x)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w.main_grad = torch.zeros(H, device="cuda", dtype=torch.float32)
+    report("rmsnorm+residual fwd", time_ms(lambda: Fn.rms_norm(x, w, 1e-6, res), args.iters), 4 * x.numel() * 2)
+    xr = x.clone().requires_grad_(True)
+    y = Fn.rms_norm(xr, w, 1e-6)
+    dy = torch.randn_like(y)
+    report("rmsnorm bwd", time_ms(lambda: torch.autograd.grad(y, xr, dy, retain_graph=True), args.iters),
+           3 * x.numel() * 2)
+    gu = torch.randn(rows, 2 * F_, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    report("swiglu fwd", time_ms(lambda: Fn.swiglu(gu.detach()), args.iters), 3 * rows * F_ * 2)
+    so = Fn.swiglu(gu)
+    dso = torch.randn_like(so)
+    report("swiglu bwd", time_ms(lambda: torch.autograd.grad(so, gu, dso, retain_graph=True), args.iters),
+           5 * rows * F_ * 2)
+    n = 512 << 20
+    p, m, v, g = (torch.zeros(n, device="cuda", dtype=torch.float32) for _ in range(4))
+    pb = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    from ..optim.optimizer import AdamOptimizer
+    opt = AdamOptimizer()
+    report("adam (fp32 p,m,v,g)", time_ms(lambda: opt.apply_flat(p, m, v, g, pb, 1), args.iters), n * (4 * 7 + 2 + 4))
+    del p, m, v, g, pb
+    V = 32000
+    logits = torch.randn(rows, V, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    report("cross-entropy fwd", time_ms(lambda: Fn.cross_entropy_rows(logits.detach(), labels, -1), args.iters),
+           rows * V * 2)
+    _lib.check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "bandwidth"])
+    ap.add_argument("--m", type=int, default=0)
+    ap.add_argument("--n", type=int, default=0)
+    ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--a_mn", type=int, default=0)
+    ap.add_argument("--b_mn", type=int, default=0)
+    ap.add_argument("--tile_n", type=int, default=0)
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--doc_len", type=int, default=0, help="attn: equal documents of this length instead of lognormal")
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--head_dim", type=int, default=128)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no_torch", action="store_true", help="skip the library comparison (profiling runs)")
+    args = ap.parse_args()
+    {"gemm": bench_gemm, "attn": bench_attn, "bandwidth": bench_bandwidth}[args.what](args)
+
+
+if __name__ == "__main__":
+    main()

@@ -245,3 +245,66 @@ extern "C" int hsb_norm_bwd(const void* dy, const void* x, const void* w, const 
   norm_bwd_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, is_rms ? nullptr : db, parts, H, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ----------------------------------------------------------------------------------------------
+// Allocation-free variant of hsb_norm_bwd (declared and documented in norm_noalloc_api.h).
+// The stage-one partial sums go to a scratch array that is part of the library image instead of a
+// buffer the caller allocates.
+// ----------------------------------------------------------------------------------------------
+#include "norm_noalloc_api.h"
+#include <cstdio>
+#include <mutex>
+
+namespace hsb {
+
+// One copy per GPU that loads the library, resident until the process exits.
+static __device__ __align__(256) float g_norm_bwd_scratch[HSB_NORM_BWD_NOALLOC_MAX_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_norm_bwd_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_norm_bwd_scratch_mutex;
+
+// Device address of the array on the current device.  `g_norm_bwd_scratch` in host code is only a
+// handle for the runtime, not something a kernel may dereference, so the address is looked up once
+// per device (with that device current) and cached.
+static int norm_bwd_scratch_address(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -21;
+  std::lock_guard<std::mutex> lock(g_norm_bwd_scratch_mutex);
+  if (g_norm_bwd_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_norm_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "hsb_norm_bwd_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return -22;
+    }
+    g_norm_bwd_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_norm_bwd_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace hsb
+
+extern "C" long hsb_norm_bwd_noalloc_max_floats(void) { return HSB_NORM_BWD_NOALLOC_MAX_FLOATS; }
+
+extern "C" int hsb_norm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* mean,
+                                    const float* rstd, const void* dres, void* dx, float* dw, float* db, int rows,
+                                    int H, int is_rms, int accumulate, int num_sms, void* stream) {
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAX_VEC * 8 || rows <= 0) return -10;
+  const long need = static_cast<long>(hsb_norm_bwd_parts(rows, num_sms)) * 2 * H;
+  if (need > HSB_NORM_BWD_NOALLOC_MAX_FLOATS) {
+    fprintf(stderr,
+            "hsb_norm_bwd_noalloc: rows=%d H=%d num_sms=%d needs %ld scratch floats, the built-in scratch holds %ld; "
+            "use hsb_norm_bwd with a caller-allocated scratch for this size\n",
+            rows, H, num_sms, need, static_cast<long>(HSB_NORM_BWD_NOALLOC_MAX_FLOATS));
+    return -20;
+  }
+  float* scratch = nullptr;
+  const int rc = norm_bwd_scratch_address(&scratch);
+  if (rc != 0) return rc;
+  // Every float of the scratch that stage two reads is written by stage one of the same call, so
+  // nothing has to be cleared even though the array still holds the previous call's partial sums.
+  return hsb_norm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, scratch, rows, H, is_rms, accumulate, num_sms, stream);
+}

@@ -1,0 +1,45 @@
+// Allocation-free entry point for the RMSNorm / LayerNorm backward pass.
+//
+// This entry point has no counterpart in the reference implementation; it exists for callers that
+// are not allowed to allocate GPU memory: plugins that are handed device buffers by a host
+// application which owns the whole memory budget and forbids cudaMalloc in plugin code, processes
+// whose device memory was reserved up front by an arena manager so that a later cudaMalloc fails,
+// and latency-critical loops in which an allocation (which may synchronise the device) would break
+// their time budget.
+//
+// hsb_norm_bwd needs a scratch buffer for the per-CTA partial weight gradients
+// (hsb_norm_bwd_parts(rows, num_sms) * 2 * H floats) and leaves its allocation to the caller.
+// hsb_norm_bwd_noalloc does the same computation with the same kernels, but keeps that scratch in
+// a file-scope device array inside the library:
+//
+//   * size: HSB_NORM_BWD_NOALLOC_MAX_FLOATS floats (18.5 MiB), enough for hidden sizes up to 8192 on a
+//     148-SM part.  Each GPU on which the library is loaded holds this memory until the process ends.
+//   * a call whose scratch need exceeds that size is refused: it prints the sizes to stderr, returns -20
+//     and launches nothing.  Other return codes are those of hsb_norm_bwd, plus -21 (no usable current
+//     device) and -22 (the address of the array could not be obtained).
+//   * the function calls no cudaMalloc / cudaFree and no allocating library routine.  The caller passes
+//     every input and output buffer.
+//   * the first call on each device looks up the array's device address (cudaGetSymbolAddress) and caches
+//     it.  Make that first call outside of any stream capture, with the device it should run on current.
+//   * all calls on one device share the one array.  Two calls whose kernels may run at the same time
+//     (different streams without an ordering between them, or different host threads) overwrite each
+//     other's partial sums: order them.  The array keeps the previous call's contents; that is harmless
+//     because every value that the second stage reads is rewritten by the first stage of the same call,
+//     so nothing is cleared between calls.
+#pragma once
+#include <stdint.h>
+
+#define HSB_NORM_BWD_NOALLOC_MAX_FLOATS (296L * 2L * 8192L)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// Same arguments as hsb_norm_bwd without the scratch pointer.
+int hsb_norm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                         const void* dres, void* dx, float* dw, float* db, int rows, int H, int is_rms,
+                         int accumulate, int num_sms, void* stream);
+// Capacity of the built-in scratch, in floats.
+long hsb_norm_bwd_noalloc_max_floats(void);
+#ifdef __cplusplus
+}
+#endif

@@ -327,6 +327,8 @@ extern "C" int hsb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     return -11;
   if (num_sms <= 0) num_sms = 148;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (tile_n == 2 || (tile_n == 0 && M > 128 && N > 128))
+    return hsb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, epi, status, stream, num_sms);
   if (tile_n == 0) {
     // Pick the tile width with the fewer waves-times-width (ties -> the wider tile).
     auto cost = [&](int bn) {

@@ -26,7 +26,7 @@ def test_gemm_layouts(a_mn, b_mn, shape):
     a = torch.randn((K, M) if a_mn else (M, K), device=_dev(), dtype=torch.bfloat16)
     b = torch.randn((K, N) if b_mn else (N, K), device=_dev(), dtype=torch.bfloat16)
     ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
-    for tile in (128, 256):
+    for tile in (128, 256, 2):
         out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=tile)
         _lib.check_status()
         assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()

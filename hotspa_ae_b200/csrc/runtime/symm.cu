@@ -1,0 +1,280 @@
+// Peer-memory runtime: symmetric buffers shared between the GPUs of one node through CUDA IPC, a
+// stream-ordered flag barrier, the hot-switch reshard kernel and the fused data-parallel gradient
+// reduce-scatter + Adam + parameter all-gather kernel.  All inter-GPU traffic of these kernels is plain
+// loads and stores on peer-mapped addresses (NVLink 5 through NVSwitch); there is no TMA on this path.
+//
+// Replaces, in the reference: the pack -> ncclSend/ncclRecv group -> concat hot switch
+// (hetu/graph/switch_exec_graph.cc:1294-1435), the per-tensor gradient ncclReduceScatter / ncclAllReduce
+// (hetu/graph/executable_graph.cc:755-813), and Adam + in-place ncclAllGather of the updated shard
+// (hetu/graph/ops/optimizer_update.cc:73-116, hetu/impl/kernel/Optimizers.cu).
+#include "signals.cuh"
+#include "symm_api.h"
+#include <cstdio>
+
+namespace hsb {
+
+// ---------------------------------------------------------------------------------------------
+// barrier
+// ---------------------------------------------------------------------------------------------
+__global__ void symm_barrier_kernel(PeerPtrs pads, int n, int my_pos, int slot, uint32_t epoch, uint64_t timeout_ns,
+                                    int* status) {
+  const int t = threadIdx.x;
+  if (t < n) {
+    __threadfence_system();
+    uint32_t* theirs = reinterpret_cast<uint32_t*>(pads.p[t]) + slot * SYMM_MAX_RANKS + my_pos;
+    st_release_sys(theirs, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(pads.p[my_pos]) + slot * SYMM_MAX_RANKS + t;
+    wait_flag_sys(mine, epoch, timeout_ns, status);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// reshard: dst (=|+=) src over rectangles, sources may be peer memory
+// ---------------------------------------------------------------------------------------------
+constexpr int RESHARD_THREADS = 512;
+
+template <int OP>
+__global__ void __launch_bounds__(RESHARD_THREADS)
+reshard_kernel(const HsbReshardDesc* __restrict__ descs, const int32_t* __restrict__ unit_prefix,
+               const int32_t* __restrict__ unit_rows, int n_desc, int n_units) {
+  __shared__ int s_desc;
+  for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+    // binary search: the descriptor that owns unit u
+    if (threadIdx.x == 0) {
+      int lo = 0, hi = n_desc;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
+      }
+      s_desc = lo;
+    }
+    __syncthreads();
+    const int d = s_desc;
+    const HsbReshardDesc desc = descs[d];
+    const int64_t r0 = static_cast<int64_t>(u - unit_prefix[d]) * unit_rows[d];
+    const int64_t r1 = min(desc.rows, r0 + unit_rows[d]);
+    const char* src = reinterpret_cast<const char*>(desc.src);
+    char* dst = reinterpret_cast<char*>(desc.dst);
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
+                          static_cast<uintptr_t>(desc.src_ld_bytes) | static_cast<uintptr_t>(desc.dst_ld_bytes) |
+                          static_cast<uintptr_t>(desc.row_bytes)) & 15) == 0;
+    if (vec_ok) {
+      const int64_t vec_per_row = desc.row_bytes >> 4;
+      const int64_t total = (r1 - r0) * vec_per_row;
+      for (int64_t i = threadIdx.x; i < total; i += 4 * RESHARD_THREADS) {
+        // four independent 16-byte transfers per thread keep enough bytes in flight over NVLink
+        uint4 v[4];
+        int64_t so[4], dof[4];
+        bool on[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int64_t idx = i + static_cast<int64_t>(k) * RESHARD_THREADS;
+          on[k] = idx < total;
+          const int64_t r = on[k] ? r0 + idx / vec_per_row : r0;
+          const int64_t c = on[k] ? (idx % vec_per_row) << 4 : 0;
+          so[k] = r * desc.src_ld_bytes + c;
+          dof[k] = r * desc.dst_ld_bytes + c;
+          if (on[k]) v[k] = ld_peer_v4(src + so[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (!on[k]) continue;
+          if (OP == 1) {
+            float4 a = *reinterpret_cast<float4*>(dst + dof[k]);
+            a.x += __uint_as_float(v[k].x); a.y += __uint_as_float(v[k].y);
+            a.z += __uint_as_float(v[k].z); a.w += __uint_as_float(v[k].w);
+            *reinterpret_cast<float4*>(dst + dof[k]) = a;
+          } else {
+            *reinterpret_cast<uint4*>(dst + dof[k]) = v[k];
+          }
+        }
+      }
+    } else {
+      // ragged rectangle: element-wise (2-byte granules for copies, 4-byte for adds)
+      constexpr int G = OP == 1 ? 4 : 2;
+      const int64_t g_per_row = desc.row_bytes / G;
+      const int64_t total = (r1 - r0) * g_per_row;
+      for (int64_t i = threadIdx.x; i < total; i += RESHARD_THREADS) {
+        const int64_t r = r0 + i / g_per_row, c = (i % g_per_row) * G;
+        if (OP == 1) {
+          const float s = *reinterpret_cast<const volatile float*>(src + r * desc.src_ld_bytes + c);
+          *reinterpret_cast<float*>(dst + r * desc.dst_ld_bytes + c) += s;
+        } else {
+          const unsigned short s = *reinterpret_cast<const volatile unsigned short*>(src + r * desc.src_ld_bytes + c);
+          *reinterpret_cast<unsigned short*>(dst + r * desc.dst_ld_bytes + c) = s;
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// data-parallel gradient reduce (+ Adam + bf16 all-gather)
+// ---------------------------------------------------------------------------------------------
+constexpr int DPR_THREADS = 512;
+
+// MODE 0: out = scale * sum;  MODE 1: every member's gradient chunk = scale * sum (all-reduce);
+// MODE 2: Adam on the owner's shard, bf16 result written to every member's parameter range.
+template <int MODE>
+__global__ void __launch_bounds__(DPR_THREADS)
+dp_reduce_kernel(PeerPtrs grads, PeerPtrs params, int n, int my_pos, int64_t chunk, float* __restrict__ out,
+                 float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, float lr, float b1,
+                 float b2, float eps, float wd, float bc1, float bc2, float gscale) {
+  const int64_t base = static_cast<int64_t>(my_pos) * chunk;
+  const int64_t nvec = chunk >> 2;
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(DPR_THREADS) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * DPR_THREADS) {
+    const int64_t e = base + (i << 2);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint4 part[SYMM_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < SYMM_MAX_RANKS; ++r)
+      if (r < n) part[r] = ld_peer_v4(reinterpret_cast<const float*>(grads.p[r]) + e);
+#pragma unroll
+    for (int r = 0; r < SYMM_MAX_RANKS; ++r)
+      if (r < n) {
+        acc.x += __uint_as_float(part[r].x); acc.y += __uint_as_float(part[r].y);
+        acc.z += __uint_as_float(part[r].z); acc.w += __uint_as_float(part[r].w);
+      }
+    acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
+    if (MODE == 0) {
+      reinterpret_cast<float4*>(out)[i] = acc;
+    } else if (MODE == 1) {
+      uint4 o = make_uint4(__float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z),
+                           __float_as_uint(acc.w));
+#pragma unroll
+      for (int r = 0; r < SYMM_MAX_RANKS; ++r)
+        if (r < n) st_peer_v4(reinterpret_cast<float*>(grads.p[r]) + e, o);
+    } else {
+      float4 p = reinterpret_cast<float4*>(master)[i];
+      float4 mm = reinterpret_cast<float4*>(m)[i];
+      float4 vv = reinterpret_cast<float4*>(v)[i];
+      float* pp = reinterpret_cast<float*>(&p);
+      float* pm = reinterpret_cast<float*>(&mm);
+      float* pv = reinterpret_cast<float*>(&vv);
+      const float* g = reinterpret_cast<const float*>(&acc);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        pm[k] = b1 * pm[k] + (1.f - b1) * g[k];
+        pv[k] = b2 * pv[k] + (1.f - b2) * g[k] * g[k];
+        float upd = (pm[k] * inv_bc1) / (sqrtf(pv[k] * inv_bc2) + eps);
+        if (wd != 0.f) upd += wd * pp[k];
+        pp[k] -= lr * upd;
+      }
+      reinterpret_cast<float4*>(master)[i] = p;
+      reinterpret_cast<float4*>(m)[i] = mm;
+      reinterpret_cast<float4*>(v)[i] = vv;
+      uint2 o;
+      o.x = pack_bf16x2(pp[0], pp[1]);
+      o.y = pack_bf16x2(pp[2], pp[3]);
+#pragma unroll
+      for (int r = 0; r < SYMM_MAX_RANKS; ++r)
+        if (r < n) {
+          __nv_bfloat16* dstp = reinterpret_cast<__nv_bfloat16*>(params.p[r]) + e;
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dstp), "r"(o.x), "r"(o.y) : "memory");
+        }
+      // the owner's gradient chunk starts the next step at zero
+      reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[my_pos]) + base)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+}
+
+static bool fill_ptrs(PeerPtrs* dst, void* const* src, int n) {
+  if (n < 1 || n > SYMM_MAX_RANKS) return false;
+  for (int i = 0; i < SYMM_MAX_RANKS; ++i) dst->p[i] = i < n ? src[i] : nullptr;
+  return true;
+}
+
+}  // namespace hsb
+
+using namespace hsb;
+
+extern "C" int hsb_symm_malloc(uint64_t bytes, void** out) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "hsb_symm_malloc(%llu bytes): %s\n", (unsigned long long)bytes, cudaGetErrorString(e));
+    cudaGetLastError();
+    return -1;
+  }
+  e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) return -2;
+  *out = p;
+  return 0;
+}
+extern "C" int hsb_symm_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : -1; }
+extern "C" int hsb_ipc_get_handle(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "cudaIpcGetMemHandle: %s\n", cudaGetErrorString(e));
+    return -1;
+  }
+  static_assert(sizeof(h) == 64, "unexpected IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+extern "C" int hsb_ipc_open_handle(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  const cudaError_t e = cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "cudaIpcOpenMemHandle: %s\n", cudaGetErrorString(e));
+    cudaGetLastError();
+    return -1;
+  }
+  return 0;
+}
+extern "C" int hsb_ipc_close_handle(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : -1; }
+
+extern "C" int hsb_symm_barrier(void* const* pads, int n, int my_pos, int slot, uint32_t epoch, uint64_t timeout_ns,
+                                int* status, void* stream) {
+  PeerPtrs pp;
+  if (!fill_ptrs(&pp, pads, n) || my_pos < 0 || my_pos >= n || !status) return -10;
+  symm_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, n, my_pos, slot, epoch, timeout_ns,
+                                                                            status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int hsb_reshard(const HsbReshardDesc* descs, const int32_t* unit_prefix, const int32_t* unit_rows,
+                           int n_desc, int n_units, int op, void* stream) {
+  if (n_desc <= 0 || n_units <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = n_units < 148 * 4 ? n_units : 148 * 4;
+  if (op == 0) reshard_kernel<0><<<grid, RESHARD_THREADS, 0, st>>>(descs, unit_prefix, unit_rows, n_desc, n_units);
+  else if (op == 1) reshard_kernel<1><<<grid, RESHARD_THREADS, 0, st>>>(descs, unit_prefix, unit_rows, n_desc, n_units);
+  else return -12;
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static int dp_grid(int64_t chunk) {
+  const int64_t blocks = ((chunk >> 2) + DPR_THREADS - 1) / DPR_THREADS;
+  return static_cast<int>(blocks < 148 * 4 ? (blocks < 1 ? 1 : blocks) : 148 * 4);
+}
+
+extern "C" int hsb_dp_reduce_adam(void* const* grads, void* const* params, int n, int my_pos, int64_t chunk,
+                                  float* master, float* m, float* v, float lr, float b1, float b2, float eps,
+                                  float wd, float bc1, float bc2, float gscale, void* stream) {
+  PeerPtrs g, p;
+  if (!fill_ptrs(&g, grads, n) || !fill_ptrs(&p, params, n) || chunk <= 0 || (chunk & 3)) return -10;
+  dp_reduce_kernel<2><<<dp_grid(chunk), DPR_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      g, p, n, my_pos, chunk, nullptr, master, m, v, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int hsb_dp_reduce_scatter(void* const* grads, int n, int my_pos, int64_t chunk, float* out, float scale,
+                                     void* stream) {
+  PeerPtrs g, p;
+  if (!fill_ptrs(&g, grads, n) || chunk <= 0 || (chunk & 3)) return -10;
+  fill_ptrs(&p, grads, n);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (out)
+    dp_reduce_kernel<0><<<dp_grid(chunk), DPR_THREADS, 0, st>>>(g, p, n, my_pos, chunk, out, nullptr, nullptr, nullptr,
+                                                               0, 0, 0, 0, 0, 1, 1, scale);
+  else
+    dp_reduce_kernel<1><<<dp_grid(chunk), DPR_THREADS, 0, st>>>(g, p, n, my_pos, chunk, nullptr, nullptr, nullptr,
+                                                               nullptr, 0, 0, 0, 0, 0, 1, 1, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,52 @@
+// C entry points of the peer-memory runtime: allocation + CUDA IPC mapping of symmetric buffers, the
+// stream-ordered flag barrier, and the kernels that move or reduce data straight between GPUs' HBM.
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- memory -------------------------------------------------------------------------------------------
+int hsb_symm_malloc(uint64_t bytes, void** out);                 // cudaMalloc + zero fill
+int hsb_symm_free(void* p);
+int hsb_ipc_get_handle(void* p, void* handle64);                 // 64-byte cudaIpcMemHandle_t
+int hsb_ipc_open_handle(const void* handle64, void** out);       // maps a peer's allocation
+int hsb_ipc_close_handle(void* p);
+
+// ---- stream-ordered barrier over flag pads ----------------------------------------------------------
+// pads[i] = flag pad (uint32[]) of group member i as mapped in this process.  Every member writes `epoch`
+// into word [slot * 16 + my_pos] of every member's pad, then waits until its own pad shows `epoch` from
+// everybody.  All work enqueued before the barrier on every member's stream is visible afterwards.
+int hsb_symm_barrier(void* const* pads, int n, int my_pos, int slot, uint32_t epoch, uint64_t timeout_ns,
+                     int* status, void* stream);
+
+// ---- reshard (hot switch) -----------------------------------------------------------------------------
+// One descriptor = a [rows, row_bytes] rectangle: dst (this GPU) (=|+=) src (this or a peer GPU).
+struct HsbReshardDesc {
+  const void* src;       // already points at the first byte of the rectangle (peer-mapped address if remote)
+  void* dst;
+  int64_t rows;
+  int64_t row_bytes;     // multiple of 4 (fp32 add) or 2 (bf16 copy)
+  int64_t src_ld_bytes;
+  int64_t dst_ld_bytes;
+};
+// op: 0 = copy bytes, 1 = fp32 add (dst += src).  descs/unit_prefix are device arrays; unit_prefix has
+// n_desc + 1 entries: descriptor d owns work units [unit_prefix[d], unit_prefix[d+1]) of `unit_rows[d]` rows.
+int hsb_reshard(const struct HsbReshardDesc* descs, const int32_t* unit_prefix, const int32_t* unit_rows, int n_desc,
+                int n_units, int op, void* stream);
+
+// ---- data-parallel gradient reduce-scatter + Adam + parameter all-gather --------------------------------
+// grads[i] / params[i]: the fp32 gradient range / bf16 parameter range of one reduce class on member i
+// (peer-mapped).  Member my_pos owns elements [my_pos * chunk, (my_pos + 1) * chunk): it sums that chunk over
+// all members' gradients (fp32), applies Adam to its fp32 master/moment shards and writes the bf16 result into
+// every member's parameter range.  zero_grad clears the owner's gradient chunk afterwards.
+int hsb_dp_reduce_adam(void* const* grads, void* const* params, int n, int my_pos, int64_t chunk, float* master,
+                       float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                       float gscale, void* stream);
+// Same reduction without the optimizer: out[chunk] = scale * sum_i grads[i][my chunk]  (fp32).
+int hsb_dp_reduce_scatter(void* const* grads, int n, int my_pos, int64_t chunk, float* out, float scale,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -329,11 +329,30 @@ class ParamStore:
         lay, arena, garena = self.layout(sid), self.arena(sid), self.grad_arena(sid)
         zero = self.zero_enabled(sid)
         self.step_count += 1
+        fused = self.symm is not None and self.switch_mode == "fused" and arena.dtype == torch.bfloat16 \
+            and hasattr(opt, "beta1")
         for ci, c in enumerate(lay.classes):
             group = self.mesh.group(c.ranks)
             seg = garena[c.start:c.end]
             lo, hi = self._owned_range(c, zero)
-            if len(c.ranks) > 1 and group is not None:
+            n = hi - lo
+            if self.exp_avg[ci] is None:
+                self.exp_avg[ci] = torch.zeros(n, dtype=torch.float32, device=self.device)
+                self.exp_avg_sq[ci] = torch.zeros(n, dtype=torch.float32, device=self.device)
+            multi = len(c.ranks) > 1 and group is not None
+            if multi and fused:
+                # one kernel over peer memory: reduce-scatter (+ Adam + bf16 all-gather when ZeRO shards the state)
+                self.symm.barrier(c.ranks)
+                if zero:
+                    self.symm.dp_reduce_adam(c.ranks, garena, arena, c.start, c.chunk, self.master[ci],
+                                             self.exp_avg[ci], self.exp_avg_sq[ci], opt, self.step_count, grad_scale)
+                else:
+                    self.symm.dp_all_reduce(c.ranks, garena, c.start, c.chunk)
+                self.symm.barrier(c.ranks)
+                if zero:
+                    seg.zero_()
+                    continue
+            elif multi:
                 if zero:
                     own = garena[lo:hi]
                     if self.device.type == "cuda":
@@ -342,15 +361,12 @@ class ParamStore:
                         dist.all_reduce(seg, group=group)
                 else:
                     dist.all_reduce(seg, group=group)
-            n = hi - lo
-            if self.exp_avg[ci] is None:
-                self.exp_avg[ci] = torch.zeros(n, dtype=torch.float32, device=self.device)
-                self.exp_avg_sq[ci] = torch.zeros(n, dtype=torch.float32, device=self.device)
             opt.apply_flat(self.master[ci], self.exp_avg[ci], self.exp_avg_sq[ci], garena[lo:hi], arena[lo:hi],
                            self.step_count, grad_scale)
-            if zero and len(c.ranks) > 1 and group is not None:
+            if zero and multi:
                 dist.all_gather_into_tensor(arena[c.start:c.end], arena[lo:hi], group=group) \
                     if self.device.type == "cuda" else self._gloo_all_gather(arena, c, lo, hi, group)
+                seg.zero_()       # the chunks owned by other ranks still hold this rank's partial sums
         self.valid = {sid}
 
     def _gloo_all_gather(self, arena, c, lo, hi, group):

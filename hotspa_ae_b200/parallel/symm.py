@@ -1,0 +1,241 @@
+"""Symmetric heap: buffers of every GPU of the node mapped into every process (CUDA IPC), flag pads,
+a stream-ordered barrier, and the executors of the fused peer-memory paths:
+
+* :meth:`SymmHeap.reshard`      hot switch: every rank pulls the rectangles it needs straight out of the
+                                old owners' arenas into its new arena (copy for parameters, fp32 add for
+                                gradients) in one kernel, no pack / send / unpack passes;
+* :meth:`SymmHeap.dp_reduce_adam`  data-parallel gradient reduce-scatter fused with Adam and the bf16
+                                parameter all-gather: each rank sums its chunk over its peers' gradient
+                                arenas, updates its fp32 master/moment shards and writes the new bf16
+                                weights into every peer's parameter arena.
+
+Allocation is collective: every rank must call :meth:`alloc` in the same order (sizes may differ).
+Replaces the NCCL communicator + ParamBuffer machinery of the reference's hot switch
+(hetu/graph/switch_exec_graph.cc:169-200, 1294-1435) and its per-tensor gradient collectives.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from . import mesh as M
+
+c_void_p, c_int, c_u32, c_u64, c_i64, c_float = (ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64,
+                                                  ctypes.c_int64, ctypes.c_float)
+
+PAD_WORDS = 16 * 256          # 256 barrier slots of 16 ranks
+BARRIER_TIMEOUT_NS = 20_000_000_000
+UNIT_BYTES = 256 * 1024       # reshard work unit
+
+
+class _RawCuda:
+    """Exposes a raw device allocation to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+_declared = False
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    L = _lib
+    L.declare("hsb_symm_malloc", [c_u64, ctypes.POINTER(c_void_p)])
+    L.declare("hsb_symm_free", [c_void_p])
+    L.declare("hsb_ipc_get_handle", [c_void_p, c_void_p])
+    L.declare("hsb_ipc_open_handle", [c_void_p, ctypes.POINTER(c_void_p)])
+    L.declare("hsb_ipc_close_handle", [c_void_p])
+    L.declare("hsb_symm_barrier", [ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_u32, c_u64, c_void_p, c_void_p])
+    L.declare("hsb_reshard", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    L.declare("hsb_dp_reduce_adam", [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int, c_i64,
+                                     c_void_p, c_void_p, c_void_p] + [c_float] * 8 + [c_void_p])
+    L.declare("hsb_dp_reduce_scatter", [ctypes.POINTER(c_void_p), c_int, c_int, c_i64, c_void_p, c_float, c_void_p])
+    _declared = True
+
+
+class SymmBuffer:
+    """One symmetric allocation: the local tensor plus every rank's base address as mapped here."""
+
+    def __init__(self, tensor: torch.Tensor, base: int, nbytes: int, peer_bases: list, sizes: list):
+        self.tensor, self.base, self.nbytes, self.peer_bases, self.sizes = tensor, base, nbytes, peer_bases, sizes
+
+
+class SymmHeap:
+    def __init__(self):
+        _declare()
+        self.mesh = M.mesh()
+        if self.mesh.torch_device.type != "cuda":
+            raise RuntimeError("the symmetric heap needs CUDA devices")
+        self.rank, self.world = self.mesh.rank, self.mesh.world_size
+        self.device = self.mesh.torch_device
+        self.buffers: list[SymmBuffer] = []
+        self._by_ptr: dict[int, SymmBuffer] = {}
+        self._epoch: dict[tuple, int] = {}
+        self._slots: dict[tuple, int] = {}
+        self.pad = self._alloc_bytes(PAD_WORDS * 4)
+        self._desc_cache: dict = {}
+
+    # ---- allocation ----------------------------------------------------------------------------------
+    def _alloc_bytes(self, nbytes: int) -> SymmBuffer:
+        nbytes = max(int(nbytes), 256)
+        nbytes = (nbytes + 255) // 256 * 256
+        ptr = c_void_p()
+        _lib.check(_lib.lib().hsb_symm_malloc(nbytes, ctypes.byref(ptr)), "hsb_symm_malloc")
+        handle = (ctypes.c_ubyte * 64)()
+        _lib.check(_lib.lib().hsb_ipc_get_handle(ptr, handle), "hsb_ipc_get_handle")
+        mine = (bytes(handle), nbytes)
+        if self.world > 1:
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine)
+        else:
+            everyone = [mine]
+        bases, sizes = [], []
+        for r, (h, n) in enumerate(everyone):
+            sizes.append(n)
+            if r == self.rank:
+                bases.append(ptr.value)
+                continue
+            out = c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            _lib.check(_lib.lib().hsb_ipc_open_handle(buf, ctypes.byref(out)), "hsb_ipc_open_handle")
+            bases.append(out.value)
+        t = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=self.device)
+        sb = SymmBuffer(t, ptr.value, nbytes, bases, sizes)
+        self.buffers.append(sb)
+        self._by_ptr[ptr.value] = sb
+        return sb
+
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Collective.  Returns a zero-filled tensor of `numel` elements in peer-visible memory."""
+        esz = torch.empty((), dtype=dtype).element_size()
+        sb = self._alloc_bytes(max(numel, 1) * esz)
+        return sb.tensor[:max(numel, 1) * esz].view(dtype)
+
+    def buffer_of(self, t: torch.Tensor) -> SymmBuffer:
+        ptr = t.untyped_storage().data_ptr()
+        sb = self._by_ptr.get(ptr)
+        if sb is None:
+            raise KeyError("tensor was not allocated from the symmetric heap")
+        return sb
+
+    def peer_ptr(self, t: torch.Tensor, rank: int, byte_offset: int = 0) -> int:
+        """Address, in this process, of byte `byte_offset` of rank `rank`'s copy of the buffer behind `t`."""
+        return self.buffer_of(t).peer_bases[rank] + byte_offset
+
+    # ---- barrier -------------------------------------------------------------------------------------
+    def barrier(self, ranks=None) -> None:
+        """Stream-ordered barrier over `ranks` (default: everyone): work enqueued before it on every member's
+        current stream has completed and is visible when work enqueued after it starts."""
+        ranks = tuple(range(self.world)) if ranks is None else tuple(ranks)
+        if len(ranks) <= 1:
+            return
+        slot = self._slots.setdefault(ranks, len(self._slots))
+        if slot >= PAD_WORDS // 16:
+            raise RuntimeError("too many distinct barrier groups")
+        epoch = self._epoch.get(ranks, 0) + 1
+        self._epoch[ranks] = epoch
+        arr = (c_void_p * len(ranks))(*[self.pad.peer_bases[r] for r in ranks])
+        _lib.check(_lib.lib().hsb_symm_barrier(arr, len(ranks), ranks.index(self.rank), slot, epoch & 0xFFFFFFFF,
+                                               BARRIER_TIMEOUT_NS, _lib.status_tensor(self.device).data_ptr(),
+                                               _lib.stream_ptr()), "hsb_symm_barrier")
+        _lib.count_launch()
+
+    # ---- hot switch ------------------------------------------------------------------------------------
+    def _descriptors(self, store, plan, src: int, dst: int, kind: str):
+        key = (src, dst, kind)
+        if key in self._desc_cache:
+            return self._desc_cache[key]
+        if kind == "param":
+            s_arena, d_arena = store.arena(src), store.arena(dst)
+        else:
+            s_arena, d_arena = store.grad_arena(src), store.grad_arena(dst)
+        esz = s_arena.element_size()
+        d_lay = store.layout(dst)
+        rows = []
+        for c in list(plan["local"]) + [c for peer in sorted(plan["recvs"]) for c in plan["recvs"][peer]]:
+            p = store.graph.parameters[c.tensor_id]
+            s_entry = store.layout(src, c.src_rank).entries[p.id]
+            d_entry = d_lay.entries[p.id]
+            s_ptr = self.peer_ptr(s_arena, c.src_rank, (s_entry.offset + c.src_off) * esz)
+            d_ptr = d_arena.data_ptr() + (d_entry.offset + c.dst_off) * esz
+            row_bytes = c.row_elems * esz
+            # full-width rectangles are one long row: fewer, larger units
+            r, rb, sld, dld = c.rows, row_bytes, c.src_ld * esz, c.dst_ld * esz
+            if sld == rb and dld == rb:
+                r, rb, sld, dld = 1, rb * c.rows, rb * c.rows, rb * c.rows
+            rows.append((s_ptr, d_ptr, r, rb, sld, dld))
+        n = len(rows)
+        if n == 0:
+            self._desc_cache[key] = None
+            return None
+        # split single-row rectangles into units by bytes, multi-row ones by rows
+        descs = []
+        for s_ptr, d_ptr, r, rb, sld, dld in rows:
+            if r == 1 and rb > UNIT_BYTES:
+                nchunk = (rb + UNIT_BYTES - 1) // UNIT_BYTES
+                for k in range(nchunk):
+                    b0 = k * UNIT_BYTES
+                    descs.append((s_ptr + b0, d_ptr + b0, 1, min(UNIT_BYTES, rb - b0), 0, 0, 1))
+            else:
+                unit_rows = max(1, UNIT_BYTES // max(rb, 1))
+                descs.append((s_ptr, d_ptr, r, rb, sld, dld, unit_rows))
+        nd = len(descs)
+        arr = np.zeros((nd, 6), dtype=np.int64)
+        unit_rows = np.zeros(nd, dtype=np.int32)
+        prefix = np.zeros(nd + 1, dtype=np.int32)
+        for i, (s_ptr, d_ptr, r, rb, sld, dld, ur) in enumerate(descs):
+            arr[i] = (s_ptr, d_ptr, r, rb, sld, dld)
+            unit_rows[i] = ur
+            prefix[i + 1] = prefix[i] + (r + ur - 1) // ur
+        out = dict(descs=torch.from_numpy(arr).to(self.device), prefix=torch.from_numpy(prefix).to(self.device),
+                   unit_rows=torch.from_numpy(unit_rows).to(self.device), n_desc=nd, n_units=int(prefix[-1]))
+        self._desc_cache[key] = out
+        return out
+
+    def reshard(self, store, plan, src: int, dst: int, kind: str) -> None:
+        d = self._descriptors(store, plan, src, dst, kind)
+        self.barrier()                       # every rank's source arena is final
+        if d is not None:
+            _lib.check(_lib.lib().hsb_reshard(d["descs"].data_ptr(), d["prefix"].data_ptr(), d["unit_rows"].data_ptr(),
+                                              d["n_desc"], d["n_units"], 1 if kind == "grad" else 0,
+                                              _lib.stream_ptr()), "hsb_reshard")
+            _lib.count_launch()
+        self.barrier()                       # every rank is done reading: sources may be overwritten
+
+    # ---- data-parallel reduce + optimizer ----------------------------------------------------------------
+    def dp_reduce_adam(self, ranks, garena, parena, start: int, chunk: int, master, m, v, opt, step: int,
+                       grad_scale: float) -> None:
+        """Reduce class [start, start + len(ranks) * chunk) over `ranks`; this rank owns chunk ranks.index(rank)."""
+        n, pos = len(ranks), list(ranks).index(self.rank)
+        g = (c_void_p * n)(*[self.peer_ptr(garena, r, start * 4) for r in ranks])
+        p = (c_void_p * n)(*[self.peer_ptr(parena, r, start * 2) for r in ranks])
+        bc1, bc2 = 1.0 - opt.beta1 ** step, 1.0 - opt.beta2 ** step
+        _lib.check(_lib.lib().hsb_dp_reduce_adam(g, p, n, pos, chunk, master.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                                 opt.lr, opt.beta1, opt.beta2, opt.eps, opt.weight_decay, bc1, bc2,
+                                                 grad_scale, _lib.stream_ptr()), "hsb_dp_reduce_adam")
+        _lib.count_launch()
+
+    def dp_all_reduce(self, ranks, garena, start: int, chunk: int, scale: float = 1.0) -> None:
+        n, pos = len(ranks), list(ranks).index(self.rank)
+        g = (c_void_p * n)(*[self.peer_ptr(garena, r, start * 4) for r in ranks])
+        _lib.check(_lib.lib().hsb_dp_reduce_scatter(g, n, pos, chunk, None, scale, _lib.stream_ptr()),
+                   "hsb_dp_reduce_scatter")
+        _lib.count_launch()
+
+
+_HEAP: SymmHeap | None = None
+
+
+def heap() -> SymmHeap:
+    global _HEAP
+    if _HEAP is None or _HEAP.mesh is not M.mesh():
+        _HEAP = SymmHeap()
+    return _HEAP

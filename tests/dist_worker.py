@@ -37,7 +37,7 @@ def main():
     cfg = llama_config("tiny", max_seq_len=256, num_layers=4)
     b = build_llama_graph(cfg, strategies, world, lr=1e-3)
     g = b["graph"]
-    g.executor.store.switch_mode = args.switch_mode
+    g.executor.configure_switch(args.switch_mode)
     rng = np.random.default_rng(1234)
     weights = None
     ref_loss_terms = []

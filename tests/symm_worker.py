@@ -1,0 +1,115 @@
+"""Worker for the multi-GPU peer-memory tests (launched by torch.distributed.run, one rank per GPU)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.ops import _lib  # noqa: E402
+from hotspa_ae_b200.optim.optimizer import AdamOptimizer  # noqa: E402
+from hotspa_ae_b200.parallel import symm  # noqa: E402
+
+
+def main():
+    ht.init_comm_group(8)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    heap = symm.heap()
+    ranks = list(range(world))
+    ok = True
+
+    # ---- barrier + peer visibility: everyone writes its rank, peers read it after the barrier ------------
+    buf = heap.alloc(1024, torch.float32)
+    for it in range(3):
+        buf.fill_(float(rank * 10 + it))
+        heap.barrier()
+        for r in ranks:
+            sb = heap.buffer_of(buf)
+            peer = torch.as_tensor(symm._RawCuda(sb.peer_bases[r], sb.nbytes), device=dev)[:4096].view(torch.float32)
+            got = float(peer[5].item())
+            if got != float(r * 10 + it):
+                print(f"rank {rank}: barrier/peer read mismatch from {r}: {got}", flush=True)
+                ok = False
+        heap.barrier()
+
+    # ---- fused reduce-scatter + Adam + all-gather against all_reduce + the same Adam in torch ------------
+    torch.manual_seed(100 + rank)
+    chunk = 256 * 37
+    n = chunk * world
+    garena = heap.alloc(n + 512, torch.float32)
+    parena = heap.alloc(n + 512, torch.bfloat16)
+    start = 256
+    g_local = torch.randn(n, device=dev)
+    garena[start:start + n].copy_(g_local)
+    torch.manual_seed(7)
+    master_full = torch.randn(n, device=dev) * 0.02
+    m_full = torch.randn(n, device=dev) * 0.01
+    v_full = torch.rand(n, device=dev) * 0.01
+    lo, hi = rank * chunk, (rank + 1) * chunk
+    master, m, v = master_full[lo:hi].clone(), m_full[lo:hi].clone(), v_full[lo:hi].clone()
+    opt = AdamOptimizer(lr=1e-2, weight_decay=0.01)
+    step, gscale = 3, 0.5
+    g_sum = g_local.clone()
+    dist.all_reduce(g_sum)
+    heap.barrier()
+    heap.dp_reduce_adam(ranks, garena, parena, start, chunk, master, m, v, opt, step, gscale)
+    heap.barrier()
+    gs = g_sum * gscale
+    m_ref = 0.9 * m_full + 0.1 * gs
+    v_ref = 0.999 * v_full + 0.001 * gs * gs
+    upd = (m_ref / (1 - 0.9 ** step)) / ((v_ref / (1 - 0.999 ** step)).sqrt() + opt.eps) + 0.01 * master_full
+    p_ref = master_full - 1e-2 * upd
+    torch.cuda.synchronize()
+    _lib.check_status()
+    if not torch.allclose(master, p_ref[lo:hi], rtol=1e-5, atol=1e-6):
+        print(f"rank {rank}: master mismatch {(master - p_ref[lo:hi]).abs().max().item()}", flush=True)
+        ok = False
+    if not torch.allclose(parena[start:start + n].float(), p_ref.bfloat16().float(), rtol=0, atol=1e-6):
+        print(f"rank {rank}: all-gathered bf16 params mismatch "
+              f"{(parena[start:start + n].float() - p_ref.bfloat16().float()).abs().max().item()}", flush=True)
+        ok = False
+
+    # ---- all-reduce form ---------------------------------------------------------------------------------
+    garena[start:start + n].copy_(g_local)
+    heap.barrier()
+    heap.dp_all_reduce(ranks, garena, start, chunk, 1.0)
+    heap.barrier()
+    torch.cuda.synchronize()
+    if not torch.allclose(garena[start:start + n], g_sum, rtol=1e-5, atol=1e-5):
+        print(f"rank {rank}: all-reduce mismatch", flush=True)
+        ok = False
+
+    # ---- a barrier that nobody completes times out into the status word instead of hanging ----------------
+    if os.environ.get("HSB_TEST_TIMEOUT") == "1":
+        import ctypes
+        arr = (ctypes.c_void_p * world)(*heap.pad.peer_bases)
+        # wait for an epoch that is never written, with a 0.2 s limit
+        _lib.lib().hsb_symm_barrier(arr, world, rank, 200, 12345, 200_000_000, _lib.status_tensor(dev).data_ptr(),
+                                    _lib.stream_ptr())
+        torch.cuda.synchronize()
+        code = int(_lib.status_tensor(dev).item())
+        _lib.status_tensor(dev).zero_()
+        # slot 200 received 12345 from every live peer, so it completes; a slot written by nobody must not
+        arr1 = (ctypes.c_void_p * world)(*([heap.pad.peer_bases[rank]] * world))
+        _lib.lib().hsb_symm_barrier(arr1, world, 0, 201, 777, 200_000_000, _lib.status_tensor(dev).data_ptr(),
+                                    _lib.stream_ptr())
+        torch.cuda.synchronize()
+        code2 = int(_lib.status_tensor(dev).item())
+        _lib.status_tensor(dev).zero_()
+        if code != 0 or (world > 1 and code2 != 4):
+            print(f"rank {rank}: timeout test codes {code} {code2}", flush=True)
+            ok = False
+        dist.barrier()
+
+    t = torch.tensor([0 if ok else 1], device=dev)
+    dist.all_reduce(t)
+    print(f"rank {rank}: symm ok={ok}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(t.item()) == 0 else 3)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,55 @@
+"""Multi-GPU tests (NCCL + peer-memory kernels): skipped unless at least two GPUs are visible."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _torchrun(world, script, *args, env=None, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, script), *args]
+    e = dict(os.environ, NCCL_NVLS_ENABLE="0", **(env or {}))
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=e)
+    assert proc.returncode == 0, proc.stdout[-6000:]
+    return proc.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_symmetric_heap_barrier_reduce_adam():
+    _torchrun(2, "symm_worker.py", env={"HSB_TEST_TIMEOUT": "1"})
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_hot_switch_two_gpus(mode):
+    strategies = [[1, 2, 1, False], [2, 1, 1, True]]
+    plan = [[0, "alloc", 256, 2], [1, "grad", 128, 4], [0, "update", 256, 2]]
+    _torchrun(2, "dist_worker.py", "--strategies", json.dumps(strategies), "--plan", json.dumps(plan),
+              "--switch_mode", mode, "--device", "cuda", "--tol", "5e-4")
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
+def test_hot_switch_four_gpus_fused():
+    strategies = [[1, 2, 2, False], [4, 1, 1, True], [2, 2, 1, True]]
+    plan = [[0, "alloc", 256, 2], [1, "grad", 64, 8], [2, "grad", 128, 4], [0, "update", 256, 2]]
+    _torchrun(4, "dist_worker.py", "--strategies", json.dumps(strategies), "--plan", json.dumps(plan),
+              "--switch_mode", "fused", "--device", "cuda", "--tol", "5e-4")

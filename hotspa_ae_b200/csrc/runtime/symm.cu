@@ -80,10 +80,12 @@ reshard_kernel(const HsbReshardDesc* __restrict__ descs, const int32_t* __restri
         for (int k = 0; k < 4; ++k) {
           if (!on[k]) continue;
           if (OP == 1) {
-            float4 a = *reinterpret_cast<float4*>(dst + dof[k]);
-            a.x += __uint_as_float(v[k].x); a.y += __uint_as_float(v[k].y);
-            a.z += __uint_as_float(v[k].z); a.w += __uint_as_float(v[k].w);
-            *reinterpret_cast<float4*>(dst + dof[k]) = a;
+            // several descriptors (one per owner of a gradient replica) may add into the same destination
+            // concurrently, so the add is a reduction at the memory side
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + dof[k]),
+                         "f"(__uint_as_float(v[k].x)), "f"(__uint_as_float(v[k].y)), "f"(__uint_as_float(v[k].z)),
+                         "f"(__uint_as_float(v[k].w))
+                         : "memory");
           } else {
             *reinterpret_cast<uint4*>(dst + dof[k]) = v[k];
           }
@@ -98,7 +100,7 @@ reshard_kernel(const HsbReshardDesc* __restrict__ descs, const int32_t* __restri
         const int64_t r = r0 + i / g_per_row, c = (i % g_per_row) * G;
         if (OP == 1) {
           const float s = *reinterpret_cast<const volatile float*>(src + r * desc.src_ld_bytes + c);
-          *reinterpret_cast<float*>(dst + r * desc.dst_ld_bytes + c) += s;
+          atomicAdd(reinterpret_cast<float*>(dst + r * desc.dst_ld_bytes + c), s);
         } else {
           const unsigned short s = *reinterpret_cast<const volatile unsigned short*>(src + r * desc.src_ld_bytes + c);
           *reinterpret_cast<unsigned short*>(dst + r * desc.dst_ld_bytes + c) = s;

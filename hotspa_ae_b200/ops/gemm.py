@@ -40,12 +40,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         assert out is not None and out.dtype == torch.float32
     if out is None:
         if out_dtype is None:
-            out_dtype = torch.bfloat16 if a.is_cuda else a.dtype
+            out_dtype = a.dtype
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     assert out.shape == (M, N) and out.stride(-1) == 1
 
-    if not _use_cuda(a, b) or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
-        # reference path: CPU tensors (unit tests of the layers above) and fp32 debugging runs on a GPU
+    if a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16:
+        if a.stride(-1) != 1:
+            a = a.contiguous()
+        if b.stride(-1) != 1:
+            b = b.contiguous()
+    tma_ok = a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+    if not _use_cuda(a, b) or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or not tma_ok:
+        # reference path: CPU tensors (unit tests of the layers above), fp32 debugging runs on a GPU, and
+        # operands whose rows are not 16-byte multiples (TMA cannot describe them)
         A = a.float().t() if a_mn else a.float()
         B = b.float() if b_mn else b.float().t()
         res = A @ B
@@ -55,15 +62,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             out.copy_(res.to(out.dtype))
         return out
 
-    if a.stride(-1) != 1:
-        a = a.contiguous()
-    if b.stride(-1) != 1:
-        b = b.contiguous()
-    if a.stride(0) % 8 or b.stride(0) % 8 or a.data_ptr() % 16 or b.data_ptr() % 16:
-        a, b = a.contiguous(), b.contiguous()
-        if a.stride(0) % 8 or b.stride(0) % 8:
-            # rows that are not 16-byte multiples cannot be described to TMA: pad K
-            raise ValueError("gemm: leading dimensions must be multiples of 8 elements")
     if out.dtype == torch.bfloat16:
         epi = EPI_BF16
     else:

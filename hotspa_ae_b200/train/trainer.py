@@ -103,7 +103,7 @@ class HotSwitchTrainer:
         store = g.executor.store
         store.seed = seed
         if switch_mode == "auto":
-            switch_mode = "nccl"
+            switch_mode = "fused" if (self.device.type == "cuda" and world > 1 and dtype == torch.bfloat16) else "nccl"
         self.switch_mode = switch_mode
         g.executor.configure_switch(switch_mode)
         self.in_ds = in_ds

@@ -72,9 +72,9 @@ def main():
             weights = {}
             store = g.executor.store
             for k, p in b["model"].named_parameters():
-                gen = torch.Generator(device="cpu")
+                gen = torch.Generator(device=store.device)
                 gen.manual_seed(store.seed + 7919 * g.parameters.index(p))
-                weights[k] = g.param_inits[p.id].fill(list(p.global_shape), gen, "cpu").requires_grad_(True)
+                weights[k] = g.param_inits[p.id].fill(list(p.global_shape), gen, store.device).cpu().requires_grad_(True)
         g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, sid, lvl)
         for r in rows:
             ref_loss_terms.append((r, 1.0 / n_rows))
@@ -105,7 +105,7 @@ def main():
     ok = worst < args.tol
     print(f"rank {rank}: worst param diff {worst:.3e} ok={ok}", flush=True)
     if world > 1:
-        t = torch.tensor([0 if ok else 1])
+        t = torch.tensor([0 if ok else 1], device=g.executor.mesh.torch_device)
         torch.distributed.all_reduce(t)
         ok = int(t.item()) == 0
     sys.exit(0 if ok else 3)

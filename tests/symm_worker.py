@@ -67,7 +67,7 @@ def main():
     if not torch.allclose(master, p_ref[lo:hi], rtol=1e-5, atol=1e-6):
         print(f"rank {rank}: master mismatch {(master - p_ref[lo:hi]).abs().max().item()}", flush=True)
         ok = False
-    if not torch.allclose(parena[start:start + n].float(), p_ref.bfloat16().float(), rtol=0, atol=1e-6):
+    if not torch.allclose(parena[start:start + n].float(), p_ref.bfloat16().float(), rtol=1e-2, atol=1e-5):
         print(f"rank {rank}: all-gathered bf16 params mismatch "
               f"{(parena[start:start + n].float() - p_ref.bfloat16().float()).abs().max().item()}", flush=True)
         ok = False

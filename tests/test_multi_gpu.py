@@ -29,7 +29,9 @@ def _torchrun(world, script, *args, env=None, timeout=600):
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, script), *args]
     e = dict(os.environ, NCCL_NVLS_ENABLE="0", **(env or {}))
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=e)
-    assert proc.returncode == 0, proc.stdout[-6000:]
+    if proc.returncode != 0:
+        keep = [ln for ln in proc.stdout.splitlines() if ln.startswith("[rank") or ln.startswith("rank ")]
+        raise AssertionError("\n".join(keep[-60:]) or proc.stdout[-4000:])
     return proc.stdout
 
 

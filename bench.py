@@ -54,7 +54,10 @@ def parse():
     ap.add_argument("--model", default="7b")
     ap.add_argument("--tokens_per_gpu", type=int, default=TOKENS_PER_GPU)
     ap.add_argument("--switch_mode", default="auto")
+    ap.add_argument("--mb_tokens", type=int, default=32768, help="token budget of a micro-batch")
     ap.add_argument("--no_e2e", action="store_true", help="skip the end-to-end region (profiling runs)")
+    ap.add_argument("--breakdown", action="store_true", help="after the timed regions, run one more step with "
+                                                             "per-bucket / per-switch CUDA-event timing (stderr)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling runs only; the "
                                                            "result is then marked as not the headline config)")
     return ap.parse_args()
@@ -130,8 +133,11 @@ def main():
     overrides = {"vocab_size": 32000}
     if args.layers:
         overrides["num_layers"] = args.layers
+    # micro-batches are sized by tokens (documents are independent under varlen attention); pipelined strategies
+    # get smaller ones so that the pipeline has several micro-batches in flight
+    mb_tokens = [args.mb_tokens if pp == 1 else args.mb_tokens // 2 for _, _, pp, _ in strategies]
     trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=True,
-                               switch_mode=args.switch_mode, **overrides)
+                               switch_mode=args.switch_mode, micro_batch_tokens=mb_tokens, **overrides)
     vocab = trainer.config.vocab_size
     tokens = args.tokens_per_gpu * world
     K, W = args.steps, args.warmup
@@ -206,6 +212,16 @@ def main():
                "d2h_bytes_per_step": d2h // K, "ms_per_step": ms_b / K, "last_loss": last_loss}
         _lib.check_status()
 
+    if args.breakdown:
+        import time as _t
+        trainer.profile = True
+        t0 = _t.perf_counter()
+        pb = trainer.prepare(batch(500))
+        t1 = _t.perf_counter()
+        trainer.run_prepared(pb, read_loss=True)
+        print(f"[rank {rank}] prepare {1e3 * (t1 - t0):.1f} ms host; " + json.dumps(trainer.last_profile),
+              file=sys.stderr, flush=True)
+        trainer.profile = False
     if rank == 0:
         par = "+".join(f"dp{dp}tp{tp}pp{pp}" + ("z" if z else "") for dp, tp, pp, z in strategies)
         out = {
@@ -217,7 +233,7 @@ def main():
             "config": {"model": f"llama-{args.model}" + (f"-{args.layers}layers(not headline)" if args.layers else ""),
                        "global_batch": f"{tokens} tokens/step", "seq_len": f"varlen<= {bounds[0]}",
                        "parallelism": par, "buckets": list(bounds), "optimizer": "Adam fp32 master",
-                       "recompute": "per block", "switch_mode": trainer.switch_mode,
+                       "recompute": "per block", "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
                        "l2": "inputs larger than L2 (weights and activations of several GB stream every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

@@ -426,7 +426,10 @@ class Executor:
                 out.append((t.local_shape(sid), self._act_dtype(t), dev, plan.comm[op.id].dst_peer))
             return out
 
+        hook = getattr(self.graph, "micro_batch_hook", None)
         for is_fwd, mb in tasks:
+            if hook is not None:
+                hook(mb)             # lets the application set symbolic shapes of a ragged micro-batch
             if is_fwd:
                 recvd = PC.p2p_exchange(pending_sends, recv_specs_fwd()) if (pending_sends or plan.recv_ops) else []
                 pending_sends = []

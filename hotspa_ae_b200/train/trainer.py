@@ -48,7 +48,7 @@ class HotSwitchTrainer:
     def __init__(self, model: str | LlamaConfig = "7b", strategies=((1, 1, 1, False),), bucket_bounds=(32768, 0),
                  lr: float = 1e-4, dtype=torch.bfloat16, recompute: bool | list = True, switch_mode: str = "auto",
                  weight_decay: float = 0.0, ds_parallel_configs: list | None = None, gpus_per_node: int = 8,
-                 pad_id: int = 0, seed: int = 2023, **config_overrides):
+                 pad_id: int = 0, seed: int = 2023, micro_batch_tokens=None, **config_overrides):
         self.mesh = ht.init_comm_group(gpus_per_node)
         world = self.mesh.world_size
         self.config = model if isinstance(model, LlamaConfig) else llama_config(model, **config_overrides)
@@ -108,9 +108,18 @@ class HotSwitchTrainer:
         g.executor.configure_switch(switch_mode)
         self.in_ds = in_ds
         self._dp_index = [self._my_dp_index(s) for s in range(len(cfgs))]
+        # tokens per micro-batch and strategy: None = one packed row of the bucket's length per micro-batch (the
+        # reference's scheme); otherwise rows are packed by token budget (documents never attend to each other)
+        if micro_batch_tokens is None or isinstance(micro_batch_tokens, int):
+            micro_batch_tokens = [micro_batch_tokens] * len(cfgs)
+        self.micro_batch_tokens = list(micro_batch_tokens)
+        self._row_lens: list = []
+        g.micro_batch_hook = self._on_micro_batch
         self._pinned: dict = {}
         self._stat_dev = None
         self._upload_done = None
+        self.profile = False            # record CUDA-event times per bucket and per switch
+        self.last_profile: dict = {}
         # materialise the home strategy (fp32 master + optimizer state) before the first step
         g.run(self.loss, [self.loss, self.train_op], {}, 0, 0, ht.run_level("alloc"))
 
@@ -127,6 +136,10 @@ class HotSwitchTrainer:
             if rank in st:
                 return int(self.input_ids.ds(sid).get_dup_group_index(list(st).index(rank)))
         return 0
+
+    def _on_micro_batch(self, mb: int) -> None:
+        if self._row_lens:
+            self.config.seq_len_symbol.set_data(self._row_lens[mb])
 
     # ---- host -> device staging -----------------------------------------------------------------------
     def _stage(self, key, arr: np.ndarray) -> torch.Tensor:
@@ -160,15 +173,33 @@ class HotSwitchTrainer:
             if not pk.rows:
                 buckets.append(None)
                 continue
-            mb = D.micro_batches_for_rank(sequences, pk, self.dp_of(b), self._dp_index[b], self.pad_id)
+            budget = self.micro_batch_tokens[b]
             feed = {}
-            for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"),
-                            (self.position_ids, "position_ids"), (self.cu_seqlens, "cu_seqlens")):
-                t = self._stage((b, key), mb[key])
-                h2d += t.numel() * t.element_size()
-                feed[ph] = t.to(self.device, non_blocking=True)
-            buckets.append(dict(feed=feed, nmb=mb["num_micro_batches"], max_len=pk.max_len,
-                                docs=mb["cu_seqlens"].shape[1], rows=len(pk.rows), tokens=pk.tokens))
+            if budget:
+                members = [i for row in pk.rows for i in row]
+                mb = D.token_budget_micro_batches(sequences, members, self.dp_of(b), self._dp_index[b], budget,
+                                                  self.pad_id)
+                for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"),
+                                (self.position_ids, "position_ids"), (self.cu_seqlens, "cu_seqlens")):
+                    flat = self._stage((b, key), np.concatenate([a.reshape(-1) for a in mb[key]]))
+                    h2d += flat.numel() * flat.element_size()
+                    dev = flat.to(self.device, non_blocking=True)
+                    parts, o = [], 0
+                    for a in mb[key]:
+                        parts.append(dev[o:o + a.size].view(a.shape))
+                        o += a.size
+                    feed[ph] = parts
+                row_lens = mb["row_len"]
+            else:
+                mb = D.micro_batches_for_rank(sequences, pk, self.dp_of(b), self._dp_index[b], self.pad_id)
+                for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"),
+                                (self.position_ids, "position_ids"), (self.cu_seqlens, "cu_seqlens")):
+                    t = self._stage((b, key), mb[key])
+                    h2d += t.numel() * t.element_size()
+                    feed[ph] = t.to(self.device, non_blocking=True)
+                row_lens = [pk.max_len] * mb["num_micro_batches"]
+            buckets.append(dict(feed=feed, nmb=mb["num_micro_batches"], max_len=max(row_lens), row_lens=row_lens,
+                                docs=int(mb["cu_seqlens"][0].shape[-1]), rows=len(pk.rows), tokens=pk.tokens))
         if self.device.type == "cuda":
             self._upload_done = torch.cuda.Event()
             self._upload_done.record()
@@ -184,6 +215,18 @@ class HotSwitchTrainer:
             self._stat_dev = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._stat_dev.zero_()
         info = []
+        marks = []
+        prof = self.profile and self.device.type == "cuda"
+        store = self.graph.executor.store
+        n_sw0 = len(store.switch_log)
+
+        def mark(name):
+            if prof:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append((name, e))
+
+        mark("start")
         for b in list(range(n - 1, 0, -1)) + [0]:
             bk = batch["buckets"][b]
             level = ht.run_level("update" if b == 0 else "grad")
@@ -196,12 +239,22 @@ class HotSwitchTrainer:
             self.config.mbs_times_dp_symbol.set_data(dp)
             self.config.seq_len_symbol.set_data(bk["max_len"])
             self.docs_symbol.set_data(bk["docs"])
+            self._row_lens = bk["row_lens"]
             out = self.graph.run(self.loss, [self.loss, self.train_op], bk["feed"], nmb, b, level,
                                  grad_scale=float(nmb * dp) / total_targets)
             if out and out[0] is not None:
                 # tensor-parallel peers of the last stage hold the same loss: count it once
                 self._stat_dev += out[0].float().sum() / self.tp_of(b)
             info.append(dict(strategy=b, rows=bk["rows"], tokens=bk["tokens"], micro_batches=nmb))
+            mark(f"bucket{b}")
+        if prof:
+            torch.cuda.synchronize()
+            spans = {name: marks[i - 1][1].elapsed_time(e) for i, (name, e) in enumerate(marks) if i > 0}
+            sw = [dict(src=x["src"], dst=x["dst"], kind=x["kind"], mode=x["mode"],
+                       ms=x["events"][0].elapsed_time(x["events"][1]), remote_mb=x["remote_elems"] *
+                       (4 if x["kind"] == "grad" else 2) / 1e6) for x in store.switch_log[n_sw0:]]
+            self.last_profile = dict(bucket_ms=spans, switches=sw)
+        del store.switch_log[:max(0, len(store.switch_log) - 64)]
         self.step_count += 1
         loss = self._collect_loss(total_targets) if read_loss else float("nan")
         return StepResult(loss, batch["tokens"], total_targets, batch["h2d_bytes"], 4 if read_loss else 0, info)

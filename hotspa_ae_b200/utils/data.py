@@ -107,3 +107,43 @@ def micro_batches_for_rank(seqs, packed: PackedRows, dp: int, dp_rank: int, pad_
         ntok += int((b != IGNORE).sum())
     return {"input_ids": np.stack(ids), "labels": np.stack(labs), "position_ids": np.stack(poss),
             "cu_seqlens": np.stack(cus), "num_micro_batches": n_mb, "valid_tokens": ntok}
+
+
+def token_budget_micro_batches(seqs, members, dp: int, dp_rank: int, tokens_per_mb: int, pad_id: int = 0,
+                               multiple: int = 256):
+    """Micro-batches of one bucket for data-parallel rank `dp_rank`, sized by tokens instead of by rows.
+
+    Attention is per document (cu_seqlens), so a micro-batch may hold any number of documents: the bucket's
+    sequences (`members`, indices into `seqs`) are spread over the `dp` ranks balancing tokens, each rank packs
+    its share first-fit into micro-batches of at most `tokens_per_mb` tokens, and every micro-batch is padded only
+    up to the next multiple of `multiple` tokens.  All ranks run the same number of micro-batches (ranks with
+    fewer get all-padding ones).  Returns per-micro-batch lists of arrays (lengths differ between micro-batches).
+    """
+    lens = [int(len(seqs[i])) for i in members]
+    assign = C.balance_rows(lens, dp) if members else [[] for _ in range(dp)]
+    per_rank = []
+    for r in range(dp):
+        mine = sorted((members[k] for k in assign[r]), key=lambda i: -len(seqs[i]))
+        mbs, loads = [], []
+        for i in mine:
+            n = len(seqs[i])
+            for k in range(len(mbs)):
+                if loads[k] + n <= tokens_per_mb:
+                    mbs[k].append(i); loads[k] += n
+                    break
+            else:
+                mbs.append([i]); loads.append(n)
+        per_rank.append((mbs, loads))
+    n_mb = max(1, max(len(m) for m, _ in per_rank))
+    mbs, loads = per_rank[dp_rank]
+    out = {"input_ids": [], "labels": [], "position_ids": [], "cu_seqlens": [], "row_len": [],
+           "num_micro_batches": n_mb, "valid_tokens": 0}
+    for k in range(n_mb):
+        docs = [seqs[i] for i in mbs[k]] if k < len(mbs) else []
+        total = int(sum(len(d) for d in docs))
+        row_len = max(multiple, (total + multiple - 1) // multiple * multiple)
+        a, b, c, d = build_row(docs, row_len, pad_id, None)
+        out["input_ids"].append(a[None]); out["labels"].append(b[None]); out["position_ids"].append(c[None])
+        out["cu_seqlens"].append(d[None]); out["row_len"].append(row_len)
+        out["valid_tokens"] += int((b != IGNORE).sum())
+    return out

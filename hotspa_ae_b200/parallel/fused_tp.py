@@ -1,0 +1,214 @@
+"""Tensor-parallel linears fused with their collective (all-gather -> GEMM, GEMM -> reduce-scatter).
+
+One :class:`TPGroup` per tensor-parallel rank list holds what the fused kernels need: a flag pad, two staging
+buffers for the shards that peers pull (all-gather side) and two receive buffers that peers push partial tiles
+into (reduce-scatter side), all in peer-visible memory, plus the per-group call counter that both sides use as
+the flag epoch.  Buffers are double buffered by call parity: a rank can only be one call ahead of its peers on
+the same group because every call needs every member's data.
+
+``ag_linear``   y[T, out/t]  = gather_rows(x[T/t, in]) @ W[out/t, in]^T      (column-parallel forward)
+``linear_rs``   y[T/t, out]  = reduce_scatter_rows(x[T, in/t] @ W[in/t, out]) (row-parallel forward)
+The backward of each is the other kernel (the dual collective) plus a plain weight-gradient GEMM.
+When a shape does not fit the kernels (token count not a multiple of 256 per rank, fp32 debugging runs, CPU)
+the same functions run NCCL/gloo collectives around the plain GEMM.
+Reference: python_refactor/hetu/nn/modules/parallel_multi_ds.py:342-355, 449-452 (comm + linear pairs).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _lib
+from ..ops.gemm import gemm
+from . import comm as PC
+from . import mesh as M
+
+c_void_p, c_int, c_u32, c_u64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64
+
+PAD_WORDS = 64 + 3 * 16 * 128
+READY_WORD, COUNT_WORD = 0, 64
+CHUNK = 256
+TIMEOUT_NS = 20_000_000_000
+_declared = False
+_groups: dict = {}
+enabled = True
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    _lib.declare("hsb_gemm_fused_comm",
+                 [c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_int, c_int, c_int, c_u32,
+                  ctypes.POINTER(c_void_p), c_int, c_int, ctypes.POINTER(c_void_p), c_void_p,
+                  ctypes.POINTER(c_void_p), c_void_p, c_int, c_int, c_u64, c_void_p, c_void_p, c_int])
+    _declared = True
+
+
+class TPGroup:
+    def __init__(self, ranks):
+        from . import symm
+        _declare()
+        self.ranks = tuple(ranks)
+        self.n = len(self.ranks)
+        self.heap = symm.heap()
+        self.mesh = M.mesh()
+        self.pos = self.ranks.index(self.mesh.rank)
+        self.pg = self.mesh.group(self.ranks)
+        self.pad = self.heap.alloc_group(PAD_WORDS * 4, self.ranks)
+        self.stage = [None, None]       # all-gather sources (this rank's shard), by call parity
+        self.recv = [None, None]        # reduce-scatter receive buffers, by call parity
+        self.stage_bytes = self.recv_bytes = 0
+        self.ag_epoch = self.rs_epoch = 0     # separate call counters: flags / counter sets are per kind
+        self.chunk_flags = torch.zeros(self.n * 128, dtype=torch.int32, device=self.mesh.torch_device)
+        self.n_comm_ctas = 4
+
+    def _ptrs(self, sb):
+        return (c_void_p * self.n)(*[sb.peer_bases[r] for r in self.ranks])
+
+    def _ensure(self, kind: str, nbytes: int):
+        """Group-collective growth of the double-buffered staging / receive buffers (same decision everywhere:
+        every member sees the same shapes)."""
+        cur = self.stage_bytes if kind == "stage" else self.recv_bytes
+        if nbytes <= cur:
+            return
+        nbytes = int(nbytes * 1.25)
+        bufs = [self.heap.alloc_group(nbytes, self.ranks) for _ in range(2)]
+        if kind == "stage":
+            self.stage, self.stage_bytes = bufs, nbytes
+        else:
+            self.recv, self.recv_bytes = bufs, nbytes
+
+    # ---- kernels -------------------------------------------------------------------------------------------
+    def usable(self, rows_per_rank: int, *tensors) -> bool:
+        return (enabled and rows_per_rank % CHUNK == 0 and rows_per_rank // CHUNK <= 128 and
+                all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors))
+
+    def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor):
+        """(gather_rows(x_shard) @ w^T, gathered x).  x_shard [R, K], w [N, K] (K-major), both bf16."""
+        R, K = x_shard.shape
+        N = w.shape[0]
+        self._ensure("stage", R * K * 2)
+        self.ag_epoch += 1
+        par = self.ag_epoch & 1
+        stage = self.stage[par]
+        stage.tensor[:R * K * 2].view(torch.bfloat16).view(R, K).copy_(x_shard)
+        xg = torch.empty((self.n * R, K), dtype=torch.bfloat16, device=x_shard.device)
+        xg[self.pos * R:(self.pos + 1) * R].copy_(x_shard)
+        y = torch.empty((self.n * R, N), dtype=torch.bfloat16, device=x_shard.device)
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        rc = _lib.lib().hsb_gemm_fused_comm(
+            1, xg.data_ptr(), w.data_ptr(), y.data_ptr(), self.n * R, N, K, K, w.stride(0), N, self.n, self.pos, R,
+            self.ag_epoch & 0xFFFFFFFF, self._ptrs(self.pad), READY_WORD, COUNT_WORD, self._ptrs(stage),
+            self.chunk_flags.data_ptr(), None, None, 0, self.n_comm_ctas, TIMEOUT_NS,
+            _lib.status_tensor(x_shard.device).data_ptr(), _lib.stream_ptr(), 0)
+        _lib.check(rc, "hsb_gemm_fused_comm(all-gather)")
+        _lib.count_launch()
+        return y, xg
+
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """reduce_scatter_rows(x @ w).  x [T, K], w [K, N] (row-major), bf16; returns [T / n, N]."""
+        T, K = x.shape
+        N = w.shape[1]
+        R = T // self.n
+        self._ensure("recv", (self.n - 1) * R * N * 2)
+        self.rs_epoch += 1
+        par = self.rs_epoch & 1
+        out = torch.empty((R, N), dtype=torch.bfloat16, device=x.device)
+        x = x if x.stride(-1) == 1 else x.contiguous()
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        rc = _lib.lib().hsb_gemm_fused_comm(
+            2, x.data_ptr(), w.data_ptr(), None, T, N, K, x.stride(0), w.stride(0), 0, self.n, self.pos, R,
+            self.rs_epoch & 0xFFFFFFFF, self._ptrs(self.pad), READY_WORD, COUNT_WORD, None, None,
+            self._ptrs(self.recv[par]), out.data_ptr(), N, 0, TIMEOUT_NS,
+            _lib.status_tensor(x.device).data_ptr(), _lib.stream_ptr(), 0)
+        _lib.check(rc, "hsb_gemm_fused_comm(reduce-scatter)")
+        _lib.count_launch()
+        return out
+
+
+def group_state(ranks) -> TPGroup:
+    key = (id(M.mesh()), tuple(ranks))
+    st = _groups.get(key)
+    if st is None:
+        st = TPGroup(ranks)
+        _groups[key] = st
+    return st
+
+
+class AGLinearFn(torch.autograd.Function):
+    """y = gather_rows(x) @ W^T with W stored [out_local, in]; backward: reduce-scatter of dy @ W, wgrad on the
+    gathered activations kept from the forward."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad, ranks):
+        st = group_state(ranks)
+        ctx.st, ctx.main_grad = st, main_grad
+        if st.usable(x.shape[0], x, w):
+            y, xg = st.ag_gemm(x.contiguous(), w)
+        else:
+            xg = PC.all_gather_dim0(x.contiguous(), st.pg)
+            y = gemm(xg, w)
+        ctx.save_for_backward(xg, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, w = ctx.saved_tensors
+        st = ctx.st
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            R = xg.shape[0] // st.n
+            if st.usable(R, dy, w):
+                dx = st.gemm_rs(dy, w)                       # dy [T, out_l] @ W [out_l(K), in(N)]
+            else:
+                dx = PC.reduce_scatter_dim0(gemm(dy, w, b_mn=True), st.pg)
+        if ctx.needs_input_grad[1]:
+            if ctx.main_grad is not None:
+                gemm(dy, xg, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+            else:
+                dw = gemm(dy, xg, a_mn=True, b_mn=True)
+        return dx, dw, None, None
+
+
+class LinearRSFn(torch.autograd.Function):
+    """y = reduce_scatter_rows(x @ W) with W stored [in_local, out]; backward: all-gather of dy fused with
+    dx = dy @ W^T, wgrad on the gathered dy."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad, ranks):
+        st = group_state(ranks)
+        ctx.st, ctx.main_grad = st, main_grad
+        ctx.save_for_backward(x, w)
+        R = x.shape[0] // st.n
+        if x.shape[0] % st.n == 0 and st.usable(R, x, w):
+            return st.gemm_rs(x, w)
+        return PC.reduce_scatter_dim0(gemm(x, w, b_mn=True), st.pg)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        st = ctx.st
+        dy = dy.contiguous()
+        dx = dw = None
+        if st.usable(dy.shape[0], dy, w):
+            dx, dyg = st.ag_gemm(dy, w)                      # dyg [T, out] @ (W [in_l(N), out(K)])^T
+        else:
+            dyg = PC.all_gather_dim0(dy, st.pg)
+            dx = gemm(dyg, w) if ctx.needs_input_grad[0] else None
+        if ctx.needs_input_grad[1]:
+            if ctx.main_grad is not None:
+                gemm(x, dyg, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+            else:
+                dw = gemm(x, dyg, a_mn=True, b_mn=True)
+        return dx, dw, None, None
+
+
+def ag_linear(x, w, main_grad, ranks):
+    return AGLinearFn.apply(x, w, main_grad, tuple(ranks))
+
+
+def linear_rs(x, w, main_grad, ranks):
+    return LinearRSFn.apply(x, w, main_grad, tuple(ranks))

@@ -84,34 +84,40 @@ class SymmHeap:
         self._desc_cache: dict = {}
 
     # ---- allocation ----------------------------------------------------------------------------------
-    def _alloc_bytes(self, nbytes: int) -> SymmBuffer:
+    def _alloc_bytes(self, nbytes: int, ranks=None) -> SymmBuffer:
+        """Collective over `ranks` (default: every rank): allocate locally, exchange IPC handles, map the peers."""
         nbytes = max(int(nbytes), 256)
         nbytes = (nbytes + 255) // 256 * 256
+        ranks = list(range(self.world)) if ranks is None else list(ranks)
         ptr = c_void_p()
         _lib.check(_lib.lib().hsb_symm_malloc(nbytes, ctypes.byref(ptr)), "hsb_symm_malloc")
         handle = (ctypes.c_ubyte * 64)()
         _lib.check(_lib.lib().hsb_ipc_get_handle(ptr, handle), "hsb_ipc_get_handle")
         mine = (bytes(handle), nbytes)
-        if self.world > 1:
-            everyone = [None] * self.world
-            dist.all_gather_object(everyone, mine)
+        if len(ranks) > 1:
+            everyone = [None] * len(ranks)
+            dist.all_gather_object(everyone, mine, group=self.mesh.group(ranks))
         else:
             everyone = [mine]
-        bases, sizes = [], []
-        for r, (h, n) in enumerate(everyone):
-            sizes.append(n)
+        bases, sizes = {}, {}
+        for r, (h, n) in zip(ranks, everyone):
+            sizes[r] = n
             if r == self.rank:
-                bases.append(ptr.value)
+                bases[r] = ptr.value
                 continue
             out = c_void_p()
             buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
             _lib.check(_lib.lib().hsb_ipc_open_handle(buf, ctypes.byref(out)), "hsb_ipc_open_handle")
-            bases.append(out.value)
+            bases[r] = out.value
         t = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=self.device)
         sb = SymmBuffer(t, ptr.value, nbytes, bases, sizes)
         self.buffers.append(sb)
         self._by_ptr[ptr.value] = sb
         return sb
+
+    def alloc_group(self, nbytes: int, ranks) -> SymmBuffer:
+        """Collective over `ranks` only: a byte buffer visible to those ranks."""
+        return self._alloc_bytes(nbytes, ranks)
 
     def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """Collective.  Returns a zero-filled tensor of `numel` elements in peer-visible memory."""

@@ -1,0 +1,78 @@
+"""Worker: fused all-gather->GEMM and GEMM->reduce-scatter (forward and backward) against NCCL + fp32 matmul."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.ops import _lib  # noqa: E402
+from hotspa_ae_b200.parallel import fused_tp  # noqa: E402
+
+
+def rel_err(a, b):
+    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+
+
+def main():
+    ht.init_comm_group(8)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ranks = tuple(range(world))
+    ok = True
+    for it, (R, K, N) in enumerate([(256, 512, 768), (1024, 4096, 1536), (512, 1024, 4096), (2048, 4096, 4096)]):
+        # ---- column-parallel: y = gather(x) @ W^T ------------------------------------------------------
+        torch.manual_seed(1000 + 17 * it + rank)
+        x = (torch.randn(R, K, device=dev) * 0.5).bfloat16().requires_grad_(True)
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16().requires_grad_(True)
+        w.main_grad = torch.zeros(N, K, device=dev, dtype=torch.float32)
+        y = fused_tp.ag_linear(x, w, w.main_grad, ranks)
+        dy = (torch.randn(world * R, N, device=dev) * 0.1).bfloat16()
+        y.backward(dy)
+        xs = [torch.empty_like(x) for _ in ranks]
+        dist.all_gather(xs, x.detach())
+        xg = torch.cat(xs).float()
+        y_ref = xg @ w.detach().float().t()
+        dxg = dy.float() @ w.detach().float()
+        dist.all_reduce(dxg)
+        dx_ref = dxg[rank * R:(rank + 1) * R]
+        dw_ref = dy.float().t() @ xg
+        torch.cuda.synchronize()
+        _lib.check_status()
+        e = (rel_err(y, y_ref), rel_err(x.grad, dx_ref), rel_err(w.main_grad, dw_ref))
+        if max(e) > 2e-2:
+            print(f"rank {rank}: ag_linear R={R} K={K} N={N} errors y/dx/dw = {e}", flush=True)
+            ok = False
+        # ---- row-parallel: y = reduce_scatter(x @ W) ---------------------------------------------------
+        T = world * R
+        x2 = (torch.randn(T, K, device=dev) * 0.5).bfloat16().requires_grad_(True)
+        w2 = (torch.randn(K, N, device=dev) * 0.05).bfloat16().requires_grad_(True)
+        w2.main_grad = torch.zeros(K, N, device=dev, dtype=torch.float32)
+        y2 = fused_tp.linear_rs(x2, w2, w2.main_grad, ranks)
+        dy2 = (torch.randn(R, N, device=dev) * 0.1).bfloat16()
+        y2.backward(dy2)
+        full = x2.detach().float() @ w2.detach().float()
+        dist.all_reduce(full)
+        y2_ref = full[rank * R:(rank + 1) * R]
+        dys = [torch.empty_like(dy2) for _ in ranks]
+        dist.all_gather(dys, dy2)
+        dyg = torch.cat(dys).float()
+        dx2_ref = dyg @ w2.detach().float().t()
+        dw2_ref = x2.detach().float().t() @ dyg
+        torch.cuda.synchronize()
+        _lib.check_status()
+        e = (rel_err(y2, y2_ref), rel_err(x2.grad, dx2_ref), rel_err(w2.main_grad, dw2_ref))
+        if max(e) > 2e-2:
+            print(f"rank {rank}: linear_rs R={R} K={K} N={N} errors y/dx/dw = {e}", flush=True)
+            ok = False
+    t = torch.tensor([0 if ok else 1], device=dev)
+    dist.all_reduce(t)
+    print(f"rank {rank}: fused tp ok={ok}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(t.item()) == 0 else 3)
+
+
+if __name__ == "__main__":
+    main()

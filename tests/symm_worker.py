@@ -85,7 +85,7 @@ def main():
     # ---- a barrier that nobody completes times out into the status word instead of hanging ----------------
     if os.environ.get("HSB_TEST_TIMEOUT") == "1":
         import ctypes
-        arr = (ctypes.c_void_p * world)(*heap.pad.peer_bases)
+        arr = (ctypes.c_void_p * world)(*[heap.pad.peer_bases[r] for r in range(world)])
         # wait for an epoch that is never written, with a 0.2 s limit
         _lib.lib().hsb_symm_barrier(arr, world, rank, 200, 12345, 200_000_000, _lib.status_tensor(dev).data_ptr(),
                                     _lib.stream_ptr())

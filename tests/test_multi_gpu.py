@@ -55,3 +55,8 @@ def test_hot_switch_four_gpus_fused():
     plan = [[0, "alloc", 256, 2], [1, "grad", 64, 8], [2, "grad", 128, 4], [0, "update", 256, 2]]
     _torchrun(4, "dist_worker.py", "--strategies", json.dumps(strategies), "--plan", json.dumps(plan),
               "--switch_mode", "fused", "--device", "cuda", "--tol", "5e-4")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_all_gather_gemm_and_gemm_reduce_scatter():
+    _torchrun(2, "fused_tp_worker.py")

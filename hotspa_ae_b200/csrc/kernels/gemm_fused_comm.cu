@@ -34,7 +34,10 @@ namespace fused {
 constexpr int BM = 128, BNH = 128, BN = 256, BK = 64, UMMA_K = 16, THREADS = 192;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STAGES = 6, ACC_STAGES = 2, TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_WARP_STAGE = 32 * 256;        // mode 2: per epilogue warp, 32 rows x 128 bf16
+constexpr int EPI_STAGE_BYTES = 4 * EPI_WARP_STAGE;
+constexpr int RECV_BLOCK_BYTES = 2 * EPI_WARP_STAGE;   // one warp's 32 x 256 part of a tile in the receive buffer
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES;
 constexpr int CHUNK_ROWS = 256;             // rows per readiness flag / per reduce-scatter row block
 constexpr int PIECE_BYTES = 32 * 1024;      // one bulk copy
 constexpr int RING = 6;                     // pieces in flight per copy CTA
@@ -52,7 +55,9 @@ struct Args {
   uint32_t* chunk_flags;    // mode 1: local [n * rows_per_rank / 256], epoch valued
   char* xg;                 // mode 1: local gathered A
   int64_t row_bytes;        // mode 1: K * 2
-  PeerPtrs recv;            // mode 2: members' receive buffers [(n - 1) * rows_per_rank, N] bf16
+  PeerPtrs recv;            // mode 2: members' receive buffers: per source slot, 16 KB blocks indexed
+                            // [row block][n tile][cta half][lane quarter], each block = 2 column halves of
+                            // 32 rows x 256 B with 16-byte pieces XOR-swizzled by (row & 15)
   __nv_bfloat16* out;       // mode 2: local [rows_per_rank, N]
   int ld_out;
 };
@@ -294,6 +299,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t empty_remote = mapa_u32(smem_u32(&tmem_empty[0]), 0);
     uint32_t tile_iter = 0;
     bool ok = true;
+    bool pending = false;                 // mode 2: a remote tile part whose arrival is not yet counted
+    uint32_t* pend_counter = nullptr;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_iter) {
       int tm, tn;
       tile_of(t, tiles_m, tiles_n, tm, tn);
@@ -325,6 +332,94 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         crow_base = Cout + static_cast<size_t>(row) * ldc;
       }
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (MODE == 2) {
+        uint8_t* stg = smem + STAGES * STAGE_BYTES + 256 + (warp - 2) * EPI_WARP_STAGE;
+        if (pending) {
+          // the previous remote tile's bulk stores have had a whole tile time to land: count it at its owner
+          if (lane == 0) {
+            bulk_wait_all();
+            fence_proxy_async_all();
+            __threadfence_system();
+            red_add_release_sys(pend_counter, 1u);
+          }
+          pending = false;
+        }
+        if (remote) {
+          // Remote tile part: stage 128 columns of the 32 rows in the receive-block layout and ship each half
+          // to the owner with ONE 8 KB bulk copy (shared memory -> peer HBM).
+          const int slot = a.my_pos < owner ? a.my_pos : a.my_pos - 1;
+          const size_t slot_bytes = static_cast<size_t>(a.rows_per_rank / 32) * tiles_n * RECV_BLOCK_BYTES;
+          char* blk = reinterpret_cast<char*>(a.recv.p[owner]) + slot * slot_bytes +
+                      ((static_cast<size_t>(rb * tiles_n + tn) * 2 + rank) * 4 + quarter) * RECV_BLOCK_BYTES;
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
+            if (lane == 0) bulk_wait_read_all();          // the staging area has been read by the previous copy
+            __syncwarp();
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(taddr0 + pass * 128 + cc * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[8 * k + 0]), __uint_as_float(r[8 * k + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * k + 2]), __uint_as_float(r[8 * k + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * k + 4]), __uint_as_float(r[8 * k + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * k + 6]), __uint_as_float(r[8 * k + 7]));
+                const int j = cc * 4 + k;
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((j ^ (lane & 15)) << 4)) = o;
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              bulk_store_s2g(blk + pass * EPI_WARP_STAGE, stg, EPI_WARP_STAGE);
+              bulk_commit();
+            }
+          }
+          pending = true;
+          pend_counter = reinterpret_cast<uint32_t*>(a.pads.p[owner]) + a.count_word +
+                         (set * 16 + a.my_pos) * MAX_RB + rb;
+        } else {
+          // Local tile part: stage 64 columns, then eight lanes per row write 128-byte row segments into `out`.
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+          __nv_bfloat16* tile_row0 = crow_base - static_cast<size_t>(lane) * a.ld_out;      // row of lane 0
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr0 + c, r0);
+            tmem_ld_32x32b_x32(taddr0 + c + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+              uint4 q;
+              q.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+              q.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+              q.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+              q.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+              *reinterpret_cast<uint4*>(stg + lane * 128 + (((j + 4) ^ (lane & 7)) << 4)) = q;
+            }
+            __syncwarp();
+            const int j = lane & 7;
+            const int col = n0 + c + j * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3);
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((j ^ (rr & 7)) << 4));
+              if (col < N) *reinterpret_cast<uint4*>(tile_row0 + static_cast<size_t>(rr) * a.ld_out + col) = v;
+            }
+            __syncwarp();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -341,13 +436,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
               o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
               o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              if (remote) st_peer_v4(reinterpret_cast<uint4*>(crow) + v, o);
-              else reinterpret_cast<uint4*>(crow)[v] = o;
+              reinterpret_cast<uint4*>(crow)[v] = o;
             }
           } else {
             for (int j = 0; j < 32 && col + j < N; ++j) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -355,15 +450,23 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (leader) mbar_arrive(&tmem_empty[acc]);
         else mbar_arrive_cluster(empty_remote + acc * 8);
       }
-      if (MODE == 2) {
-        // this warp's 32 rows of the tile are stored (in `out` for the local shard, on their way to the owner
-        // otherwise): count them at the owner, whose trailing reduce waits for every source including itself
-        __threadfence_system();
+      if (MODE == 2 && !remote) {
+        // local tile part stored in `out`: count it in this rank's own pad (the trailing reduce waits for every
+        // source including itself)
+        __threadfence();
         __syncwarp();
         if (lane == 0)
-          red_add_release_sys(reinterpret_cast<uint32_t*>(a.pads.p[owner]) + a.count_word +
-                                  (set * 16 + a.my_pos) * MAX_RB + rb, 1u);
+          red_add_release_sys(my_pad + a.count_word + (set * 16 + a.my_pos) * MAX_RB + rb, 1u);
       }
+    }
+    if (MODE == 2 && pending) {
+      if (lane == 0) {
+        bulk_wait_all();
+        fence_proxy_async_all();
+        __threadfence_system();
+        red_add_release_sys(pend_counter, 1u);
+      }
+      pending = false;
     }
     if (!ok && lane == 0) atomicCAS(status, ST_OK, ST_TIMEOUT_EPILOGUE);
 
@@ -374,34 +477,67 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int units = a.rows_per_rank / 8;
       const int ew = warp - 2;                                   // 0..3
       const int vec_per_row = N >> 3;
+      const size_t slot_bytes = static_cast<size_t>(a.rows_per_rank / 32) * tiles_n * RECV_BLOCK_BYTES;
+      const char* my_recv = reinterpret_cast<const char*>(a.recv.p[a.my_pos]);
+      int waited_rb = -1;
       for (int u = gemm_cta; u < units; u += gemm_ctas) {
         const int r0 = u * 8;
         const int rbk = r0 / CHUNK_ROWS;
-        bool got = true;
-        if (lane < a.n)
-          got = wait_flag_sys(my_pad + a.count_word + (set * 16 + lane) * MAX_RB + rbk, want, a.timeout_ns, status);
-        if (!__all_sync(0xffffffffu, got)) break;
+        if (rbk != waited_rb) {
+          bool got = true;
+          if (lane < a.n)
+            got = wait_flag_sys(my_pad + a.count_word + (set * 16 + lane) * MAX_RB + rbk, want, a.timeout_ns, status);
+          if (!__all_sync(0xffffffffu, got)) break;
+          waited_rb = rbk;
+        }
         for (int rr = ew * 2; rr < ew * 2 + 2; ++rr) {
           const int lr = r0 + rr;
           __nv_bfloat16* orow = a.out + static_cast<size_t>(lr) * a.ld_out;
-          for (int v = lane; v < vec_per_row; v += 32) {
-            uint4 mine = *reinterpret_cast<const uint4*>(orow + v * 8);
-            float f[8];
-            float2 t0 = unpack_bf16x2(mine.x), t1 = unpack_bf16x2(mine.y), t2 = unpack_bf16x2(mine.z),
-                   t3 = unpack_bf16x2(mine.w);
-            f[0] = t0.x; f[1] = t0.y; f[2] = t1.x; f[3] = t1.y; f[4] = t2.x; f[5] = t2.y; f[6] = t3.x; f[7] = t3.y;
-            for (int s = 0; s < a.n - 1; ++s) {
-              const __nv_bfloat16* rrow = reinterpret_cast<const __nv_bfloat16*>(a.recv.p[a.my_pos]) +
-                                          (static_cast<size_t>(s) * a.rows_per_rank + lr) * N;
-              const uint4 g = ld_peer_v4(rrow + v * 8);
-              float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
-              f[0] += g0.x; f[1] += g0.y; f[2] += g1.x; f[3] += g1.y;
-              f[4] += g2.x; f[5] += g2.y; f[6] += g3.x; f[7] += g3.y;
+          const int half = (lr & 255) >> 7, q4 = (lr & 127) >> 5, r32 = lr & 31;
+          // eight independent 16-byte vectors per lane and pass keep enough loads in flight
+          for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+            float f[8][8];
+            size_t boff[8];
+            bool on[8];
+            uint4 tmp[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int v = v0 + lane + 32 * k;
+              on[k] = v < vec_per_row;
+              const int c0 = v * 8;
+              const int btn = c0 >> 8, bpass = (c0 >> 7) & 1, bj = (c0 & 127) >> 3;
+              boff[k] = ((static_cast<size_t>(rbk * tiles_n + btn) * 2 + half) * 4 + q4) * RECV_BLOCK_BYTES +
+                        static_cast<size_t>(bpass * 32 + r32) * 256 + ((bj ^ (r32 & 15)) << 4);
+              if (on[k]) tmp[k] = *reinterpret_cast<const uint4*>(orow + c0);
             }
-            uint4 o;
-            o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-            o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-            *reinterpret_cast<uint4*>(orow + v * 8) = o;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              float2 t0 = unpack_bf16x2(tmp[k].x), t1 = unpack_bf16x2(tmp[k].y), t2 = unpack_bf16x2(tmp[k].z),
+                     t3 = unpack_bf16x2(tmp[k].w);
+              f[k][0] = t0.x; f[k][1] = t0.y; f[k][2] = t1.x; f[k][3] = t1.y;
+              f[k][4] = t2.x; f[k][5] = t2.y; f[k][6] = t3.x; f[k][7] = t3.y;
+            }
+            for (int s = 0; s < a.n - 1; ++s) {
+              const char* rbase = my_recv + s * slot_bytes;
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                if (on[k]) tmp[k] = ld_peer_v4(rbase + boff[k]);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                float2 g0 = unpack_bf16x2(tmp[k].x), g1 = unpack_bf16x2(tmp[k].y), g2 = unpack_bf16x2(tmp[k].z),
+                       g3 = unpack_bf16x2(tmp[k].w);
+                f[k][0] += g0.x; f[k][1] += g0.y; f[k][2] += g1.x; f[k][3] += g1.y;
+                f[k][4] += g2.x; f[k][5] += g2.y; f[k][6] += g3.x; f[k][7] += g3.y;
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if (!on[k]) continue;
+              uint4 o;
+              o.x = pack_bf16x2(f[k][0], f[k][1]); o.y = pack_bf16x2(f[k][2], f[k][3]);
+              o.z = pack_bf16x2(f[k][4], f[k][5]); o.w = pack_bf16x2(f[k][6], f[k][7]);
+              *reinterpret_cast<uint4*>(orow + (v0 + lane + 32 * k) * 8) = o;
+            }
           }
         }
       }

@@ -39,6 +39,7 @@ class CommInfo:
     count: int = 1
     src_peer: int = -1      # for P2P: the rank we receive from
     dst_peer: int = -1      # for P2P: the rank we send to
+    fused: bool = False     # the neighbouring linear op performs this collective inside its GEMM kernel
 
 
 @dataclass
@@ -61,6 +62,7 @@ class ExecPlan:
     comm: dict
     dp: int
     loss_local: bool = False
+    fused_linear: dict = field(default_factory=dict)    # linear op id -> ("ag" | "rs", group ranks)
 
 
 class Runtime:
@@ -104,12 +106,18 @@ class Runtime:
             ranks = self.group_ranks_by_dim(a, -1)
             if not gathered and len(ranks) > 1 and not self.mesh.virtual:
                 x = PC.CopyToGroup.apply(x, self.mesh.group(ranks))
+        fl = self.plan.fused_linear.get(op.id)
+        if fl is not None:
+            from ..parallel import fused_tp
+            kind, ranks = fl
+            fn = fused_tp.ag_linear if kind == "ag" else fused_tp.linear_rs
+            return fn(x, w, getattr(w, "main_grad", None), ranks)
         return gemm_linear(x, w, getattr(w, "main_grad", None), trans_b=trans_b)
 
     def comm(self, op, x):
         info: CommInfo = self.plan.comm[op.id]
         k = info.kind
-        if k == C._C.COMM_UNUSED:
+        if k == C._C.COMM_UNUSED or info.fused:
             return x
         group = self.mesh.group(info.group_ranks) if len(info.group_ranks) > 1 else None
         if k == C._C.COMM_ALL_GATHER:
@@ -132,6 +140,7 @@ class Executor:
         self.const_cache: dict = {}
         self.stats: dict = {"runs": 0}
         self.pipeline_schedule = "1f1b"
+        self.fuse_tp_comm = True      # run tensor-parallel comm+linear pairs as one fused kernel on GPUs
 
     def configure_switch(self, mode: str):
         """'nccl': pack -> grouped send/recv -> unpack.  'fused': one pull kernel over peer-mapped arenas
@@ -242,8 +251,37 @@ class Executor:
         segments = self._segments(my_ops, sid, send_ops)
         loss_local = False
         plan = ExecPlan(sid, stages, my_stage, my_ops, segments, recv_ops, send_ops, comm, dp, loss_local)
+        if self.fuse_tp_comm and self.mesh.torch_device.type == "cuda":
+            self._fuse_linear_comm(plan, my_ops)
         self.plans[sid] = plan
         return plan
+
+    def _fuse_linear_comm(self, plan: ExecPlan, my_ops) -> None:
+        """comm(all-gather rows) -> linear(x, W^T) and linear(x, W) -> comm(reduce-scatter rows) pairs become one
+        fused kernel each: the comm op turns into a pass-through and the linear op is tagged with the group."""
+        consumers: dict[int, list] = {}
+        for op in my_ops:
+            for t in op.inputs:
+                consumers.setdefault(t.id, []).append(op)
+        for op in my_ops:
+            if op.type != "linear" or op.attrs.get("trans_a") or len(op.inputs) > 2:
+                continue
+            x, y = op.inputs[0], op.outputs[0]
+            prod = x.producer
+            if op.attrs["trans_b"] and prod is not None and prod.type == "comm" and prod.id in plan.comm:
+                info = plan.comm[prod.id]
+                if (info.kind == C._C.COMM_ALL_GATHER and info.dim == 0 and len(info.group_ranks) > 1
+                        and consumers.get(x.id, []) == [op] and x.ndim == 2):
+                    info.fused = True
+                    plan.fused_linear[op.id] = ("ag", tuple(info.group_ranks))
+                    continue
+            cons = consumers.get(y.id, [])
+            if not op.attrs["trans_b"] and len(cons) == 1 and cons[0].type == "comm" and cons[0].id in plan.comm:
+                info = plan.comm[cons[0].id]
+                if (info.kind == C._C.COMM_REDUCE_SCATTER and info.dim == 0 and len(info.group_ranks) > 1
+                        and y.ndim == 2):
+                    info.fused = True
+                    plan.fused_linear[op.id] = ("rs", tuple(info.group_ranks))
 
     def _collective_group(self, kind, sds, dds, idx, ranks):
         if kind == C._C.COMM_ALL_GATHER:

@@ -1,0 +1,112 @@
+"""Micro-benchmark of the fused tensor-parallel kernels against NCCL + the plain GEMM (run under torchrun).
+
+    torchrun --nproc-per-node 2 -m hotspa_ae_b200.parallel.bench_fused_tp --tokens 8192
+
+For the Llama-7B projections at tensor-parallel degree = world size it times, with CUDA events (max over ranks,
+L2 flushed between iterations): all-gather -> GEMM fused vs ``all_gather_into_tensor`` + GEMM, and
+GEMM -> reduce-scatter fused vs GEMM + ``reduce_scatter_tensor``.  The roofline of a fused call is the slower of
+its FLOPs at the measured GEMM peak and the bytes it must move over NVLink at the measured 770 GB/s per direction.
+"""
+from __future__ import annotations
+
+import argparse
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops.bench_kernels import flush_l2, peaks
+from ..ops.gemm import gemm
+from . import fused_tp
+from . import mesh as M
+
+NVLINK_GBS = 770.0
+
+
+def timed(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    out = []
+    for _ in range(iters):
+        flush_l2()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out.append(float(t.item()))
+    return statistics.median(out)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=11008)
+    ap.add_argument("--only", default="", help="ag or rs: run only that kernel, fused only (profiling runs)")
+    args = ap.parse_args()
+    mesh = M.init_comm_group(8)
+    world, rank = mesh.world_size, mesh.rank
+    ranks = tuple(range(world))
+    st = fused_tp.group_state(ranks)
+    pk = peaks()
+    T, h, f = args.tokens, args.hidden, args.ffn
+    R = T // world
+    dev = mesh.torch_device
+    cases_ag = [("qkv", 3 * h // world), ("fc1", 2 * f // world)]
+    cases_rs = [("o-proj", h // world), ("fc2", f // world)]
+    lines = []
+    if args.only in ("", "ag"):
+        for name, N in cases_ag:
+            x = torch.randn(R, h, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(N, h, device=dev, dtype=torch.bfloat16) * 0.02
+            xg = torch.empty(T, h, device=dev, dtype=torch.bfloat16)
+            ms_f = timed(lambda: st.ag_gemm(x, w), args.iters)
+            flops = 2.0 * T * N * h
+            nv_bytes = (world - 1) * R * h * 2
+            roof = max(flops / (pk["tflops"] * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
+            line = f"all-gather->GEMM {name:7s} T={T} N={N} K={h} tp={world}: fused {ms_f * 1e3:8.1f} us " \
+                   f"({roof / ms_f:.2f} of roofline {roof * 1e3:.1f} us)"
+            if not args.only:
+                def base():
+                    dist.all_gather_into_tensor(xg, x)
+                    gemm(xg, w)
+                ms_b = timed(base, args.iters)
+                ms_g = timed(lambda: gemm(xg, w), args.iters)
+                line += f" | NCCL all-gather + GEMM {ms_b * 1e3:8.1f} us | GEMM alone {ms_g * 1e3:8.1f} us"
+            lines.append(line)
+    if args.only in ("", "rs"):
+        for name, K in cases_rs:
+            x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(K, h, device=dev, dtype=torch.bfloat16) * 0.02
+            out = torch.empty(R, h, device=dev, dtype=torch.bfloat16)
+            ms_f = timed(lambda: st.gemm_rs(x, w), args.iters)
+            flops = 2.0 * T * h * K
+            nv_bytes = (world - 1) * R * h * 2
+            roof = max(flops / (pk["tflops"] * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
+            line = f"GEMM->reduce-scatter {name:7s} T={T} N={h} K={K} tp={world}: fused {ms_f * 1e3:8.1f} us " \
+                   f"({roof / ms_f:.2f} of roofline {roof * 1e3:.1f} us)"
+            if not args.only:
+                def base():
+                    y = gemm(x, w, b_mn=True)
+                    dist.reduce_scatter_tensor(out, y)
+                ms_b = timed(base, args.iters)
+                ms_g = timed(lambda: gemm(x, w, b_mn=True), args.iters)
+                line += f" | GEMM + NCCL reduce-scatter {ms_b * 1e3:8.1f} us | GEMM alone {ms_g * 1e3:8.1f} us"
+            lines.append(line)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    if rank == 0:
+        print("\n".join(lines), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -112,7 +112,7 @@ class TPGroup:
         T, K = x.shape
         N = w.shape[1]
         R = T // self.n
-        self._ensure("recv", (self.n - 1) * R * N * 2)
+        self._ensure("recv", (self.n - 1) * R * ((N + 255) // 256) * 512)     # tile-blocked layout, padded N
         self.rs_epoch += 1
         par = self.rs_epoch & 1
         out = torch.empty((R, N), dtype=torch.bfloat16, device=x.device)

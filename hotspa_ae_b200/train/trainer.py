@@ -177,8 +177,9 @@ class HotSwitchTrainer:
             feed = {}
             if budget:
                 members = [i for row in pk.rows for i in row]
+                # rows are padded to 256 tokens per tensor-parallel rank: the shape the fused comm+GEMM kernels take
                 mb = D.token_budget_micro_batches(sequences, members, self.dp_of(b), self._dp_index[b], budget,
-                                                  self.pad_id)
+                                                  self.pad_id, 256 * self.tp_of(b))
                 for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"),
                                 (self.position_ids, "position_ids"), (self.cu_seqlens, "cu_seqlens")):
                     flat = self._stage((b, key), np.concatenate([a.reshape(-1) for a in mb[key]]))

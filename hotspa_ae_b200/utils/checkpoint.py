@@ -1,0 +1,177 @@
+"""Checkpoint save / load in the reference's interchange layout, plus resume state.
+
+Layout (reference: python_refactor/hetu/utils/checkpoint/save_checkpoint.py:69-114, load_checkpoint.py:33-69):
+for pipeline stage i of N the first rank of the stage writes ``hetu_pytorch_model-{i+1}-of-{N}.bin``, a
+``torch.save``d OrderedDict {module path name -> full (all-gathered) fp32 tensor}.  ``qkv_dense`` weights are
+stored in Megatron order ``[3 * heads * hd, in]`` (q rows, then k rows, then v rows) and converted to the
+run-time order ``[heads * 3 * hd, in]`` (per head q | k | v) on load.  A single ``hetu_pytorch_model.bin`` is also
+accepted by the loader.  Every rank keeps the slice its distributed states assign to it, so a checkpoint written
+under one strategy loads under any other.
+
+Extension (the reference saves neither): ``optim-rank{r}-of-{W}.bin`` holds this rank's fp32 master / Adam
+moment shards and ``meta.json`` the step count, consumed samples and the strategy signature; the optimizer state
+is restored only when the signature matches, otherwise training resumes from the weights with fresh moments.
+"""
+from __future__ import annotations
+
+import json
+import os
+from collections import OrderedDict
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..parallel import mesh as M
+
+WEIGHTS_NAME = "hetu_pytorch_model"
+WEIGHTS_FORMAT = ".bin"
+
+
+def to_megatron_qkv(w: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """[heads * 3 * hd, ...] (per head q | k | v) -> [3 * heads * hd, ...]."""
+    shape = w.shape
+    hd = shape[0] // (3 * num_heads)
+    return w.reshape(num_heads, 3, hd, *shape[1:]).transpose(0, 1).contiguous().reshape(shape)
+
+
+def from_megatron_qkv(w: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """[3 * heads * hd, ...] -> [heads * 3 * hd, ...]."""
+    shape = w.shape
+    hd = shape[0] // (3 * num_heads)
+    return w.reshape(3, num_heads, hd, *shape[1:]).transpose(0, 1).contiguous().reshape(shape)
+
+
+def _is_qkv(name: str) -> bool:
+    return "qkv_dense" in name
+
+
+def gather_global(graph, p) -> torch.Tensor | None:
+    """Full fp32 value of parameter `p` on every rank that holds a shard of it (None elsewhere).  Collective over the
+    world: every distinct shard is contributed once and summed."""
+    store = graph.executor.store
+    mesh = M.mesh()
+    sid = store.home if store.home is not None else 0
+    if store.home is None:
+        store.ensure_compute(0)
+        sid = store.home
+    e = store.layout(sid).entries.get(p.id)
+    full = torch.zeros(list(p.global_shape), dtype=torch.float32, device=store.device)
+    if e is not None:
+        ds = p.ds(sid)
+        # one contributor per distinct shard: the member whose duplicate index is 0
+        groups = [g for g in p.dg_hierarchy[sid] if g.contains(mesh.rank)]
+        idx = groups[0].get_index(mesh.rank)
+        dup_ranks = ds.get_devices_by_dim(-1, idx, groups[0].ranks())
+        if mesh.rank == min(dup_ranks):
+            sl = ds.local_slice(p.global_shape, e.device_index)
+            view = full[tuple(slice(o, o + n) for o, n in sl)]
+            view.copy_(store.local_value(p, sid).float())
+    if mesh.world_size > 1 and not mesh.virtual:
+        dist.all_reduce(full)
+    return full
+
+
+def save_checkpoint(model, path: str, config=None, graph=None, step: int | None = None,
+                    consumed_samples: int | None = None, save_optimizer: bool = True) -> list[str]:
+    graph = graph or next(iter(model.parameters())).graph
+    mesh = M.mesh()
+    os.makedirs(path, exist_ok=True)
+    store = graph.executor.store
+    if store.home is None:
+        store.ensure_compute(0)
+    plan = graph.executor.plan(store.home)
+    stages = plan.stages
+    num_heads = getattr(config, "num_heads", None) or getattr(getattr(model, "config", None), "num_heads", None)
+    written = []
+    per_stage: list[OrderedDict] = [OrderedDict() for _ in stages]
+    for name, p in model.named_parameters():
+        full = gather_global(graph, p)
+        owner_stage = next((i for i, st in enumerate(stages)
+                            if any(set(g.ranks()) <= set(st) for g in p.dg_hierarchy[store.home])), 0)
+        if mesh.rank == stages[owner_stage][0]:
+            t = full.cpu()
+            if _is_qkv(name) and num_heads:
+                t = to_megatron_qkv(t, num_heads)
+            per_stage[owner_stage][name] = t
+        del full
+    for i, st in enumerate(stages):
+        if mesh.rank == st[0]:
+            f = os.path.join(path, f"{WEIGHTS_NAME}-{i + 1}-of-{len(stages)}{WEIGHTS_FORMAT}")
+            torch.save(per_stage[i], f)
+            written.append(f)
+    if save_optimizer and store.master is not None:
+        state = {"master": [t.cpu() for t in store.master],
+                 "exp_avg": [None if t is None else t.cpu() for t in store.exp_avg],
+                 "exp_avg_sq": [None if t is None else t.cpu() for t in store.exp_avg_sq],
+                 "step_count": store.step_count}
+        f = os.path.join(path, f"optim-rank{mesh.rank}-of-{mesh.world_size}{WEIGHTS_FORMAT}")
+        torch.save(state, f)
+        written.append(f)
+    if mesh.rank == 0:
+        meta = {"step": step if step is not None else store.step_count, "consumed_samples": consumed_samples,
+                "world_size": mesh.world_size, "home_signature": strategy_signature(graph, store.home),
+                "num_stages": len(stages)}
+        with open(os.path.join(path, "meta.json"), "w") as fh:
+            json.dump(meta, fh, indent=2)
+    mesh.barrier()
+    return written
+
+
+def strategy_signature(graph, sid: int) -> str:
+    parts = []
+    for p in graph.parameters:
+        parts.append(f"{p.name}:{p.ds(sid)}:{[g.ranks() for g in p.dg_hierarchy[sid]]}")
+    import hashlib
+    return hashlib.sha1("|".join(parts).encode()).hexdigest()
+
+
+def _read_weights(path: str) -> dict:
+    if os.path.isfile(path):
+        return torch.load(path, map_location="cpu")
+    single = os.path.join(path, WEIGHTS_NAME + WEIGHTS_FORMAT)
+    if os.path.exists(single):
+        return torch.load(single, map_location="cpu")
+    out = OrderedDict()
+    files = sorted(f for f in os.listdir(path) if f.startswith(WEIGHTS_NAME + "-") and f.endswith(WEIGHTS_FORMAT))
+    if not files:
+        raise FileNotFoundError(f"no {WEIGHTS_NAME}*.bin under {path}")
+    for f in files:
+        out.update(torch.load(os.path.join(path, f), map_location="cpu"))
+    return out
+
+
+def load_checkpoint(model, path: str, config=None, graph=None, local_device=None, strict: bool = True,
+                    load_optimizer: bool = True) -> dict:
+    """Loads weights (any strategy) and, when the strategy signature matches, the optimizer state.  Returns the
+    checkpoint's meta dict ({} for a bare weights file)."""
+    graph = graph or next(iter(model.parameters())).graph
+    mesh = M.mesh()
+    state = _read_weights(path)
+    num_heads = getattr(config, "num_heads", None) or getattr(getattr(model, "config", None), "num_heads", None)
+    fixed = OrderedDict()
+    for k, v in state.items():
+        v = v if torch.is_tensor(v) else torch.as_tensor(np.asarray(v))
+        if _is_qkv(k) and num_heads:
+            v = from_megatron_qkv(v, num_heads)
+        fixed[k] = v
+    model.load_state_dict(fixed, local_device=local_device, strict=strict)
+    meta = {}
+    if os.path.isdir(path) and os.path.exists(os.path.join(path, "meta.json")):
+        meta = json.load(open(os.path.join(path, "meta.json")))
+    store = graph.executor.store
+    f = os.path.join(path, f"optim-rank{mesh.rank}-of-{mesh.world_size}{WEIGHTS_FORMAT}") if os.path.isdir(path) else ""
+    if load_optimizer and f and os.path.exists(f) and meta.get("home_signature") == strategy_signature(graph, store.home):
+        st = torch.load(f, map_location="cpu")
+        for i, t in enumerate(st["master"]):
+            store.master[i].copy_(t)
+        for key in ("exp_avg", "exp_avg_sq"):
+            dst = getattr(store, key)
+            for i, t in enumerate(st[key]):
+                if t is not None:
+                    dst[i] = t.to(store.device)
+        store.step_count = int(st["step_count"])
+        meta["optimizer_restored"] = True
+    else:
+        meta["optimizer_restored"] = False
+    return meta

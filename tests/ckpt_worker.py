@@ -1,0 +1,66 @@
+"""Worker: checkpoint written under one strategy loads under another with identical global weights (gloo ranks)."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.models.llama import llama_config  # noqa: E402
+from hotspa_ae_b200.utils import checkpoint as CK  # noqa: E402
+from helpers import build_llama_graph  # noqa: E402
+
+
+def main():
+    src, dst, path = json.loads(sys.argv[1]), json.loads(sys.argv[2]), sys.argv[3]
+    ht.init_comm_group(8)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    cfg = llama_config("tiny", max_seq_len=128, num_layers=2)
+    a = build_llama_graph(cfg, [tuple(src)], world)
+    a["graph"].run(a["loss"], [a["loss"], a["train_op"]], {}, 0, 0, ht.run_level("alloc"))
+    before = {k: CK.gather_global(a["graph"], p).cpu() for k, p in a["model"].named_parameters()}
+    CK.save_checkpoint(a["model"], path, graph=a["graph"], step=7, consumed_samples=99)
+    ok = True
+    if rank == 0:
+        files = sorted(os.listdir(path))
+        n_stage = src[2]
+        want = [f"hetu_pytorch_model-{i + 1}-of-{n_stage}.bin" for i in range(n_stage)]
+        if not all(w in files for w in want):
+            print("missing files", files, want, flush=True)
+            ok = False
+        sd = {}
+        for w in want:
+            sd.update(torch.load(os.path.join(path, w)))
+        k = "transformer.h.0.attn.qkv_dense.weight"
+        if not torch.equal(CK.from_megatron_qkv(sd[k], cfg.num_heads), before[k]):
+            print("qkv permutation wrong", flush=True)
+            ok = False
+        if set(sd) != set(before):
+            print("key mismatch", set(sd) ^ set(before), flush=True)
+            ok = False
+    cfg2 = llama_config("tiny", max_seq_len=128, num_layers=2)
+    b = build_llama_graph(cfg2, [tuple(dst)], world)
+    b["graph"].executor.store.seed = 777          # different init: the load must overwrite it
+    b["graph"].run(b["loss"], [b["loss"], b["train_op"]], {}, 0, 0, ht.run_level("alloc"))
+    meta = CK.load_checkpoint(b["model"], path, graph=b["graph"])
+    for k, p in b["model"].named_parameters():
+        after = CK.gather_global(b["graph"], p).cpu()
+        if not torch.equal(after, before[k]):
+            print(f"rank {rank}: {k} differs after reload: {(after - before[k]).abs().max()}", flush=True)
+            ok = False
+    if meta.get("step") != 7 or meta.get("consumed_samples") != 99:
+        ok = False
+    t = torch.tensor([0 if ok else 1])
+    if world > 1:
+        torch.distributed.all_reduce(t)
+    print(f"rank {rank}: checkpoint ok={ok} optimizer_restored={meta.get('optimizer_restored')}", flush=True)
+    sys.exit(0 if int(t.item()) == 0 else 3)
+
+
+if __name__ == "__main__":
+    main()

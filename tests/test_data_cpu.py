@@ -1,0 +1,68 @@
+"""Tokenizer, datasets, samplers, bucket packing and token-budget micro-batches (CPU)."""
+import json
+
+import numpy as np
+
+from hotspa_ae_b200.utils import data as D
+from hotspa_ae_b200.utils.dataset import (Dataloader, DistBatchSampler, LlamaJsonDataset, NormalSampler,
+                                          get_mask_and_position_ids)
+from hotspa_ae_b200.utils.tokenizer import GPT2BPETokenizer, byte_to_unicode
+
+
+def _toy_tokenizer():
+    b2u = byte_to_unicode()
+    vocab = {b2u[b]: b for b in range(256)}
+    merges = [("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o"), (b2u[ord(" ")], "w")]
+    for a, b in merges:
+        vocab[a + b] = len(vocab)
+    vocab["<|endoftext|>"] = len(vocab)
+    return GPT2BPETokenizer(vocab=vocab, merges=merges)
+
+
+def test_bpe_roundtrip_and_merges():
+    tok = _toy_tokenizer()
+    ids = tok.tokenize("hello world, héllo!")
+    assert tok.detokenize(ids) == "hello world, héllo!"
+    assert ids[0] == tok.encoder["hello"]                       # merged through he + ll + o
+    assert tok.pad == tok.vocab_size and tok.eod == tok.encoder["<|endoftext|>"]
+
+
+def test_json_dataset_and_samplers(tmp_path):
+    tok = _toy_tokenizer()
+    path = tmp_path / "docs.json"
+    with open(path, "w") as f:
+        for i in range(10):
+            f.write(json.dumps({"content": "hello " * (i + 1)}) + "\n")
+        f.write(json.dumps({"content": ""}) + "\n")
+    ds = LlamaJsonDataset(str(path), "content", 8, None, None, tokenizer=tok)
+    assert len(ds) == 10 and max(len(d) for d in ds.data) <= 9
+    assert (tmp_path / "docs_cache.pkl").exists()
+    assert [b for b in NormalSampler(10, 2, 4)] == [[2, 3, 4, 5], [6, 7, 8, 9]]
+    assert [b for b in DistBatchSampler(12, 0, 2, 1, 2)] == [[2, 3], [6, 7], [10, 11]]
+    mask, pos = get_mask_and_position_ids(np.array([[5, 6, 0], [7, 0, 0]]), 0)
+    assert mask.tolist() == [[True, True, False], [True, False, False]] and pos.tolist() == [[0, 1, 2], [0, 1, 2]]
+    dl = Dataloader(np.arange(40).reshape(20, 2), 4)
+    dl.set_dp_rank(1, 2)
+    assert dl.batch_num == 2 and dl.get_next_arr()[0, 0] == 20
+
+
+def test_bucketing_and_token_budget_micro_batches():
+    lens = D.lognormal_lengths(40000, seed=3, max_len=8192)
+    assert lens.sum() == 40000
+    seqs = D.synthetic_sequences(lens, 1000, seed=3)
+    packed = D.bucket_and_pack(lens, [8192, 2048, 0], 1, False)
+    members = sorted(i for b in packed for r in b.rows for i in r)
+    assert members == list(range(len(lens)))                    # nothing dropped, nothing duplicated
+    for b in packed:
+        for r in b.rows:
+            assert sum(lens[i] for i in r) <= b.max_len + 1
+    short = [i for r in packed[1].rows for i in r]
+    seen, n_mb = [], None
+    for rank in range(4):
+        mb = D.token_budget_micro_batches(seqs, short, 4, rank, 4096, 0, 256)
+        n_mb = mb["num_micro_batches"] if n_mb is None else n_mb
+        assert mb["num_micro_batches"] == n_mb
+        for ids, lab, cu, L in zip(mb["input_ids"], mb["labels"], mb["cu_seqlens"], mb["row_len"]):
+            assert ids.shape == (1, L) and L % 256 == 0 and cu[0, -1] == L
+            seen.append(int((lab != -1).sum()))
+    assert sum(seen) == sum(lens[i] - 1 for i in short)         # every target token appears exactly once

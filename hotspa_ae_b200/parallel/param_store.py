@@ -375,6 +375,74 @@ class ParamStore:
         for i, part in enumerate(parts):
             arena[c.start + i * c.chunk:c.start + (i + 1) * c.chunk].copy_(part)
 
+    # ---- moving the optimizer state to another strategy (elastic re-planning) ------------------------------
+    def _global_state(self, p, which: str) -> torch.Tensor:
+        """Full fp32 tensor of parameter `p`'s master weights / Adam moments (collective over the world)."""
+        sid = self.home
+        lay = self.layout(sid)
+        full = torch.zeros(list(p.global_shape), dtype=torch.float32, device=self.device)
+        e = lay.entries.get(p.id)
+        if e is not None:
+            c = lay.classes[e.cls]
+            zero = self.zero_enabled(sid)
+            sharded = zero and len(c.ranks) > 1
+            src = {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq}[which][e.cls]
+            lo, hi = self._owned_range(c, zero)
+            a, b = max(lo, e.offset), min(hi, e.offset + e.numel)
+            if src is not None and a < b and (sharded or self.rank == min(c.ranks)):
+                local = torch.zeros(e.numel, dtype=torch.float32, device=self.device)
+                local[a - e.offset:b - e.offset] = src[a - lo:b - lo]
+                sl = p.ds(sid).local_slice(p.global_shape, e.device_index)
+                full[tuple(slice(o, o + n) for o, n in sl)] += local.view(e.local_shape)
+        if self.mesh.world_size > 1 and not self.mesh.virtual:
+            dist.all_reduce(full)
+        return full
+
+    def rehome(self, new_sid: int) -> None:
+        """Make `new_sid` the home strategy: fp32 master weights and Adam moments are gathered parameter by
+        parameter and re-sliced into the new layout (the reference switches 'origin param and optimizer' buffers,
+        hetu/graph/define_and_run_graph.cc:1054-1085).  Collective; gradients must have been consumed."""
+        new_sid = self.canonical(new_sid)
+        if self.home is None:
+            self.materialize_home(new_sid)
+            return
+        if new_sid == self.home:
+            return
+        had_moments = any(t is not None for t in self.exp_avg)
+        new_lay = self.layout(new_sid)
+        zero = self.zero_enabled(new_sid)
+        n_master, n_m, n_v = [], [], []
+        for c in new_lay.classes:
+            n = c.chunk if (zero and len(c.ranks) > 1) else (c.end - c.start)
+            n_master.append(torch.zeros(n, dtype=torch.float32, device=self.device))
+            n_m.append(torch.zeros(n, dtype=torch.float32, device=self.device) if had_moments else None)
+            n_v.append(torch.zeros(n, dtype=torch.float32, device=self.device) if had_moments else None)
+        arena = self.arena(new_sid)
+        self.grad_arena(new_sid)
+        for p in self.graph.parameters:
+            for which, dst in (("master", n_master), ("exp_avg", n_m), ("exp_avg_sq", n_v)):
+                if which != "master" and not had_moments:
+                    continue
+                full = self._global_state(p, which)
+                e = new_lay.entries.get(p.id)
+                if e is None:
+                    continue
+                sl = p.ds(new_sid).local_slice(p.global_shape, e.device_index)
+                flat = full[tuple(slice(o, o + n) for o, n in sl)].reshape(-1)
+                c = new_lay.classes[e.cls]
+                lo, hi = self._owned_range_of(c, zero)
+                a, b = max(lo, e.offset), min(hi, e.offset + e.numel)
+                if a < b:
+                    dst[e.cls][a - lo:b - lo].copy_(flat[a - e.offset:b - e.offset])
+                if which == "master":
+                    arena[e.offset:e.offset + e.numel].copy_(flat)
+        self.home = new_sid
+        self.master, self.exp_avg, self.exp_avg_sq = n_master, n_m, n_v
+        self.valid = {new_sid}
+
+    def _owned_range_of(self, c: ReduceClass, zero: bool):
+        return self._owned_range(c, zero)
+
     # ---- access by global value (checkpoint, tests) ---------------------------------------------------------
     def local_value(self, p, sid: int | None = None) -> torch.Tensor:
         sid = self.home if sid is None else sid

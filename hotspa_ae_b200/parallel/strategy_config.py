@@ -19,14 +19,24 @@ def _leaf(split: dict, dup: int, ranks: list, kind: str) -> dict:
 
 
 def generate_llama_3d_config(num_layers: int = 32, num_gpus: int = 8, dp: int = 2, tp: int = 2, pp: int = 2,
-                             zero: bool = True, device_offset: int = 0) -> dict:
+                             zero: bool = True, device_offset: int = 0, layers_per_stage: list | None = None,
+                             rank_order: list | None = None) -> dict:
+    """`layers_per_stage` gives an uneven split of the layers over the pipeline stages (slow stages get fewer
+    layers); `rank_order` permutes which physical ranks fill the dp x tp x pp grid (e.g. to group slow devices)."""
     if dp * tp * pp != num_gpus:
         raise ValueError(f"dp*tp*pp = {dp * tp * pp} != num_gpus = {num_gpus}")
-    if num_layers % pp:
-        raise ValueError("num_layers must be divisible by pp")
+    if layers_per_stage is None:
+        if num_layers % pp:
+            raise ValueError("num_layers must be divisible by pp")
+        layers_per_stage = [num_layers // pp] * pp
+    if len(layers_per_stage) != pp or sum(layers_per_stage) != num_layers or min(layers_per_stage) < 1:
+        raise ValueError(f"layers_per_stage {layers_per_stage} does not split {num_layers} layers over {pp} stages")
     zero = bool(zero) and dp > 1
-    per_stage, width = num_layers // pp, num_gpus // pp
-    stage_ranks = [[device_offset + s * width + i for i in range(width)] for s in range(pp)]
+    width = num_gpus // pp
+    order = list(rank_order) if rank_order is not None else [device_offset + i for i in range(num_gpus)]
+    if sorted(order) != sorted(device_offset + i for i in range(num_gpus)):
+        raise ValueError("rank_order must be a permutation of the ranks")
+    stage_ranks = [[order[s * width + i] for i in range(width)] for s in range(pp)]
     first, last = stage_ranks[0], stage_ranks[-1]
     var, ph = "variable", "placeholder"
     cfg = {
@@ -42,8 +52,10 @@ def generate_llama_3d_config(num_layers: int = 32, num_gpus: int = 8, dp: int = 
         "lm_head": _leaf({1: tp}, dp, last, var),
         "label": _leaf({0: dp}, tp, last, ph),
     }
+    first_layer = 0
     for s, ranks in enumerate(stage_ranks):
-        a, b = s * per_stage, (s + 1) * per_stage - 1
+        a, b = first_layer, first_layer + layers_per_stage[s] - 1
+        first_layer = b + 1
         cfg["llama"]["blocks"][f"blocks{a}-{b}"] = {
             "range": [a, b],
             "layernorm1": _leaf({}, dp * tp, ranks, var),

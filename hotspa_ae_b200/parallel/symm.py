@@ -177,22 +177,41 @@ class SymmHeap:
             r, rb, sld, dld = c.rows, row_bytes, c.src_ld * esz, c.dst_ld * esz
             if sld == rb and dld == rb:
                 r, rb, sld, dld = 1, rb * c.rows, rb * c.rows, rb * c.rows
-            rows.append((s_ptr, d_ptr, r, rb, sld, dld))
+            rows.append((s_ptr, d_ptr, r, rb, sld, dld, c.src_rank))
         n = len(rows)
         if n == 0:
             self._desc_cache[key] = None
             return None
         # split single-row rectangles into units by bytes, multi-row ones by rows
         descs = []
-        for s_ptr, d_ptr, r, rb, sld, dld in rows:
+        by_src: dict[int, list] = {}
+        for s_ptr, d_ptr, r, rb, sld, dld, src_rank in rows:
+            bucket = by_src.setdefault(src_rank, [])
             if r == 1 and rb > UNIT_BYTES:
                 nchunk = (rb + UNIT_BYTES - 1) // UNIT_BYTES
                 for k in range(nchunk):
                     b0 = k * UNIT_BYTES
-                    descs.append((s_ptr + b0, d_ptr + b0, 1, min(UNIT_BYTES, rb - b0), 0, 0, 1))
+                    bucket.append((s_ptr + b0, d_ptr + b0, 1, min(UNIT_BYTES, rb - b0), 0, 0, 1))
             else:
                 unit_rows = max(1, UNIT_BYTES // max(rb, 1))
-                descs.append((s_ptr, d_ptr, r, rb, sld, dld, unit_rows))
+                n_units = (r + unit_rows - 1) // unit_rows
+                # strided rectangles are cut into one descriptor per unit so that they can be interleaved too
+                for k in range(n_units):
+                    r0 = k * unit_rows
+                    bucket.append((s_ptr + r0 * sld, d_ptr + r0 * dld, min(unit_rows, r - r0), rb, sld, dld,
+                                   unit_rows))
+        # Interleave the sources round-robin, starting with the next rank: at any moment the ranks of the node pull
+        # from different peers instead of all hammering the owner of the same parameter.
+        order = sorted(by_src, key=lambda q: (q - self.rank - 1) % self.world)
+        cursors = {q: 0 for q in order}
+        left = sum(len(v) for v in by_src.values())
+        while left:
+            for q in order:
+                i = cursors[q]
+                if i < len(by_src[q]):
+                    descs.append(by_src[q][i])
+                    cursors[q] = i + 1
+                    left -= 1
         nd = len(descs)
         arr = np.zeros((nd, 6), dtype=np.int64)
         unit_rows = np.zeros(nd, dtype=np.int32)

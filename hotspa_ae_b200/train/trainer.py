@@ -228,6 +228,7 @@ class HotSwitchTrainer:
                 marks.append((name, e))
 
         mark("start")
+        t_enq0 = time.perf_counter()
         for b in list(range(n - 1, 0, -1)) + [0]:
             bk = batch["buckets"][b]
             level = ht.run_level("update" if b == 0 else "grad")
@@ -248,6 +249,7 @@ class HotSwitchTrainer:
                 self._stat_dev += out[0].float().sum() / self.tp_of(b)
             info.append(dict(strategy=b, rows=bk["rows"], tokens=bk["tokens"], micro_batches=nmb))
             mark(f"bucket{b}")
+        t_enq1 = time.perf_counter()
         if prof:
             torch.cuda.synchronize()
             spans = {name: marks[i - 1][1].elapsed_time(e) for i, (name, e) in enumerate(marks) if i > 0}
@@ -257,13 +259,24 @@ class HotSwitchTrainer:
             self.last_profile = dict(bucket_ms=spans, switches=sw)
         del store.switch_log[:max(0, len(store.switch_log) - 64)]
         self.step_count += 1
+        t_h = time.perf_counter()
         loss = self._collect_loss(total_targets) if read_loss else float("nan")
+        if prof:
+            self.last_profile["host_enqueue_ms"] = 1e3 * (t_enq1 - t_enq0)
+            self.last_profile["loss_read_ms"] = 1e3 * (time.perf_counter() - t_h)
         return StepResult(loss, batch["tokens"], total_targets, batch["h2d_bytes"], 4 if read_loss else 0, info)
 
     def step(self, sequences) -> StepResult:
         """One optimizer step over the global batch `sequences` (list of 1-D integer token arrays; every rank
         passes the same list): host-side packing, upload from pinned memory, the device step, loss read-back."""
-        return self.run_prepared(self.prepare(sequences), read_loss=True)
+        if not self.profile:
+            return self.run_prepared(self.prepare(sequences), read_loss=True)
+        t0 = time.perf_counter()
+        batch = self.prepare(sequences)
+        t1 = time.perf_counter()
+        res = self.run_prepared(batch, read_loss=True)
+        self.last_profile["host_ms"] = {"prepare": 1e3 * (t1 - t0), "run_and_read": 1e3 * (time.perf_counter() - t1)}
+        return res
 
     def _collect_loss(self, total_targets: int) -> float:
         """Global mean loss per target token: per-rank loss sums, all-reduced, read back to the host."""

@@ -192,8 +192,8 @@ def main():
     # ---- region B: end to end through the public API -------------------------------------------------
     e2e = None
     if not args.no_e2e:
-        seqs_b = [batch(100 + i) for i in range(K)]
-        trainer.step(batch(99))
+        seqs_b = seqs[W:W + K]            # the same global batches as region A: the difference is the I/O path
+        trainer.step(seqs[0])
         fence()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -218,9 +218,14 @@ def main():
         t0 = _t.perf_counter()
         pb = trainer.prepare(batch(500))
         t1 = _t.perf_counter()
+        ms0 = torch.cuda.memory_stats()
         trainer.run_prepared(pb, read_loss=True)
-        print(f"[rank {rank}] prepare {1e3 * (t1 - t0):.1f} ms host; " + json.dumps(trainer.last_profile),
-              file=sys.stderr, flush=True)
+        ms1 = torch.cuda.memory_stats()
+        alloc = {k: ms1[k] - ms0[k] for k in ("num_alloc_retries", "num_device_alloc", "num_device_free")}
+        alloc["reserved_gb"] = ms1["reserved_bytes.all.current"] / 2**30
+        alloc["allocated_peak_gb"] = ms1["allocated_bytes.all.peak"] / 2**30
+        print(f"[rank {rank}] prepare {1e3 * (t1 - t0):.1f} ms host; " + json.dumps(trainer.last_profile) +
+              " allocator " + json.dumps(alloc), file=sys.stderr, flush=True)
         trainer.profile = False
     if rank == 0:
         par = "+".join(f"dp{dp}tp{tp}pp{pp}" + ("z" if z else "") for dp, tp, pp, z in strategies)

@@ -13,6 +13,7 @@
 #include "fa_api.h"
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#include <cstdlib>
 
 namespace hsb {
 
@@ -393,6 +394,19 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+int launch_fa_bwd_pipe(const void* qkv, const void* dout, const float* lse, const float* delta, void* dqkv,
+                       float* dq_acc, const int* table, int max_tiles, int T, int heads, float scale, int* status,
+                       cudaStream_t st, int num_sms);
+
+static bool use_pipelined_bwd() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HSB_FA_BWD_SERIAL");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <int HD>
 static int launch_fa_bwd(const void* qkv, const void* out, const void* dout, const float* lse, const int* cu, int ndocs,
                          void* dqkv, float* delta, float* dq_acc, int* table, int max_tiles, int T, int heads,
@@ -406,18 +420,24 @@ static int launch_fa_bwd(const void* qkv, const void* out, const void* dout, con
   fa_delta_kernel<<<148 * 4, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
                                            reinterpret_cast<const __nv_bfloat16*>(dout), delta, T, heads, HD);
   if (cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * heads * HD * sizeof(float), st) != cudaSuccess) return -5;
-  auto kern = fa_bwd_kernel<HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return -3;
-    attr_set = true;
+  if (HD == 128 && use_pipelined_bwd()) {
+    const int rc = launch_fa_bwd_pipe(qkv, dout, lse, delta, dqkv, dq_acc, table, max_tiles, T, heads, scale, status,
+                                      st, num_sms);
+    if (rc) return rc;
+  } else {
+    auto kern = fa_bwd_kernel<HD>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+        return -3;
+      attr_set = true;
+    }
+    const long work = static_cast<long>(max_tiles) * heads;
+    const int grid = static_cast<int>(work < num_sms ? work : num_sms);
+    kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tm_qkv, tm_do, table, lse, delta,
+                                                   reinterpret_cast<__nv_bfloat16*>(dqkv), dq_acc, T, heads, scale,
+                                                   scale * 1.4426950408889634f, status);
   }
-  const long work = static_cast<long>(max_tiles) * heads;
-  const int grid = static_cast<int>(work < num_sms ? work : num_sms);
-  kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tm_qkv, tm_do, table, lse, delta,
-                                                 reinterpret_cast<__nv_bfloat16*>(dqkv), dq_acc, T, heads, scale,
-                                                 scale * 1.4426950408889634f, status);
   fa_dq_convert_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv),
                                                 static_cast<long>(T) * heads, HD, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

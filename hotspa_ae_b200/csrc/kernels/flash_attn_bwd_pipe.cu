@@ -1,0 +1,381 @@
+// Varlen causal flash attention backward for head_dim 128, software-pipelined (sm_100a, tcgen05).
+//
+// Same math and work decomposition as flash_attn_bwd.cu (one work item = kv tile j of a document x head; the
+// CTA keeps K_j, V_j in shared memory and dK_j, dV_j in TMEM while it walks the query tiles of the document),
+// but the query dimension is tiled by 64 and every per-tile resource is double buffered so that the tensor
+// cores, the softmax warps and TMA work on different query tiles at the same time:
+//
+//   TMA      loads Q_{i+2}, dO_{i+2}                                        (2-stage ring, 64 x 128 tiles)
+//   MMA      S^T_{i+2} = K Q^T,  dP^T_{i+2} = V dO^T    [128 kv x 64 q]     (TMEM, 2 buffers of 64 + 64 columns)
+//            dV += P^T_i dO_i,  dK += dS^T_i Q_i,  dQ^T_i = K^T dS_i         (dQ^T_i overwrites S^T_i's columns)
+//   softmax  drains dQ^T_{i-1} (red.add into the fp32 accumulator), then turns S^T_i, dP^T_i into the bf16
+//            tiles P^T_i, dS^T_i in shared memory (2 buffers)
+//
+// dQ is produced transposed ([d x q], lanes = d) so that it fits the 64 columns that S^T_i occupied and the
+// 32 lanes of a warp add 32 consecutive floats of one query row at a time.
+// TMEM: S0 dP0 S1 dP1 (4 x 64 columns) | dV (128) | dK (128) = 512 columns.
+#include "common.cuh"
+#include "fa_api.h"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace hsb {
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, uint32_t box_cols);
+
+namespace fbp {
+
+constexpr int HD = 128;
+constexpr int KV_T = 128;          // kv rows per work item
+constexpr int Q_T = 64;            // query rows per pipeline step
+constexpr int THREADS = 320;        // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
+constexpr int SM_WARPS = 8;
+constexpr int KV_TILE_BYTES = KV_T * HD * 2;     // 32 KB
+constexpr int Q_TILE_BYTES = Q_T * HD * 2;       // 16 KB
+constexpr int PT_BYTES = KV_T * Q_T * 2;         // 16 KB
+constexpr int SMEM_BYTES = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 4 * PT_BYTES + 1024 + 1024 + 512;
+constexpr int TMEM_COLS = 512;
+constexpr int DV_COL = 256, DK_COL = 384;
+
+__device__ __forceinline__ void group_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
+                   const __grid_constant__ CUtensorMap tm_do, const int* __restrict__ table,
+                   const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dqkv,
+                   float* __restrict__ dq_acc, int T, int heads, float scale, float scale_log2,
+                   int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KV_TILE_BYTES;
+  uint8_t* sQ = sV + KV_TILE_BYTES;            // [2] x 16 KB
+  uint8_t* sdO = sQ + 2 * Q_TILE_BYTES;        // [2] x 16 KB
+  uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;       // [2] x 16 KB
+  uint8_t* sdST = sPT + 2 * PT_BYTES;          // [2] x 16 KB
+  float* sLse = reinterpret_cast<float*>(sdST + 2 * PT_BYTES);   // [2][64]
+  float* sDelta = sLse + 2 * Q_T;                                // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sLse) + 1024);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* kv_empty = bars + 1;
+  uint64_t* qdo_full = bars + 2;     // [2]
+  uint64_t* qdo_empty = bars + 4;    // [2]  second-phase MMAs of the tile retired (TMA may refill)
+  uint64_t* sdp_full = bars + 6;     // [2]  S^T, dP^T of the tile are in TMEM
+  uint64_t* pds_full = bars + 8;     // [2]  P^T, dS^T of the tile are in shared memory (4 warps arrive)
+  uint64_t* mma2_done = bars + 10;   // [2]  dV, dK, dQ^T MMAs of the tile retired (softmax side: smem free, dQ^T ready)
+  uint64_t* dq_drained = bars + 12;  // [2]  dQ^T of the tile has been read out of TMEM (4 warps arrive)
+  uint64_t* dkv_drained = bars + 14; // dK, dV of the item have been read out (4 warps arrive)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_items = table[0];
+  const long n_work = static_cast<long>(n_items) * heads;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(kv_empty, 1); mbar_init(dkv_drained, SM_WARPS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1); mbar_init(&sdp_full[b], 1);
+      mbar_init(&pds_full[b], SM_WARPS); mbar_init(&mma2_done[b], 1); mbar_init(&dq_drained[b], SM_WARPS);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_holder, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------ TMA producer ------------------------------------
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do);
+      uint32_t n_kv = 0, n_q = 0;
+      bool ok = true;
+      for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int item = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+        const int* t = table + 2 + 4 * item;
+        const int kv_start = t[0], doc_end = t[2];
+        const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;        // query tiles from the diagonal to the end
+        const int col_q = h * 3 * HD, col_k = col_q + HD, col_v = col_q + 2 * HD;
+        if (!mbar_wait(kv_empty, (n_kv & 1) ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(kv_full, 2 * KV_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          tma_load_2d(sK + s * (KV_T * 128), &tm_kv, kv_full, col_k + s * 64, kv_start);
+          tma_load_2d(sV + s * (KV_T * 128), &tm_kv, kv_full, col_v + s * 64, kv_start);
+        }
+        ++n_kv;
+        for (int i = 0; i < nq && ok; ++i, ++n_q) {
+          const int b = n_q & 1;
+          const int q_start = kv_start + i * Q_T;
+          if (!mbar_wait(&qdo_empty[b], ((n_q >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&qdo_full[b], 2 * Q_TILE_BYTES);
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            tma_load_2d(sQ + b * Q_TILE_BYTES + s * (Q_T * 128), &tm_q, &qdo_full[b], col_q + s * 64, q_start);
+            tma_load_2d(sdO + b * Q_TILE_BYTES + s * (Q_T * 128), &tm_do, &qdo_full[b], h * HD + s * 64, q_start);
+          }
+        }
+      }
+      if (!ok) atomicCAS(status, ST_OK, ST_TIMEOUT_PRODUCER);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------ MMA issuer --------------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(KV_T, Q_T, 0, 0);    // S^T, dP^T: both operands K-major
+      constexpr uint32_t idesc_kn = make_idesc_bf16(KV_T, HD, 0, 1);     // dV, dK: A K-major, B MN-major
+      constexpr uint32_t idesc_qt = make_idesc_bf16(HD, Q_T, 1, 1);      // dQ^T: A = K (MN-major), B = dS^T (MN-major)
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      const uint32_t aPT = smem_u32(sPT), adST = smem_u32(sdST);
+      uint32_t n_kv = 0, n_item = 0;
+      uint32_t n_s = 0;      // S/dP tiles issued so far (global counter -> buffer and phase)
+      uint32_t n_m = 0;      // second-phase tiles issued so far
+      bool ok = true;
+      auto issue_sdp = [&](uint32_t idx) -> bool {
+        const int b = idx & 1;
+        const uint32_t ph = (idx >> 1) & 1;
+        if (!mbar_wait(&qdo_full[b], ph, abort_flag)) return false;
+        // the buffer's previous tenant (tile idx - 2) left its dQ^T in the S columns: it must have been read out
+        if (!mbar_wait(&dq_drained[b], ph ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t q = aQ + b * Q_TILE_BYTES, d_o = adO + b * Q_TILE_BYTES;
+        const uint32_t s_col = tmem_base + b * 128, dp_col = s_col + 64;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t ka = (kk / 4) * (KV_T * 128) + (kk % 4) * 32;
+          const uint32_t qb = (kk / 4) * (Q_T * 128) + (kk % 4) * 32;
+          umma_bf16_ss(s_col, make_smem_desc_sw128(aK + ka, 16, 1024), make_smem_desc_sw128(q + qb, 16, 1024),
+                       idesc_st, kk != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t va = (kk / 4) * (KV_T * 128) + (kk % 4) * 32;
+          const uint32_t ob = (kk / 4) * (Q_T * 128) + (kk % 4) * 32;
+          umma_bf16_ss(dp_col, make_smem_desc_sw128(aV + va, 16, 1024), make_smem_desc_sw128(d_o + ob, 16, 1024),
+                       idesc_st, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&sdp_full[b]);
+        return true;
+      };
+      for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int item = static_cast<int>(w / heads);
+        const int* t = table + 2 + 4 * item;
+        const int kv_start = t[0], doc_end = t[2];
+        const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;
+        if (!mbar_wait(kv_full, n_kv & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(dkv_drained, (n_item & 1) ^ 1, abort_flag)) { ok = false; break; }
+        // prologue: two tiles of S^T / dP^T in flight
+        uint32_t issued = 0;
+        for (; issued < 2u && issued < static_cast<uint32_t>(nq) && ok; ++issued, ++n_s) ok = issue_sdp(n_s);
+        for (int i = 0; i < nq && ok; ++i, ++n_m) {
+          const int b = n_m & 1;
+          const uint32_t ph = (n_m >> 1) & 1;
+          if (!mbar_wait(&pds_full[b], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t q = aQ + b * Q_TILE_BYTES, d_o = adO + b * Q_TILE_BYTES;
+          const uint32_t pt = aPT + b * PT_BYTES, dst = adST + b * PT_BYTES;
+          const uint32_t acc = i > 0 ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < Q_T / 16; ++kk)      // dV[kv, d] += P^T[kv, q] dO[q, d]
+            umma_bf16_ss(tmem_base + DV_COL, make_smem_desc_sw128(pt + kk * 32, 16, 1024),
+                         make_smem_desc_sw128(d_o + kk * 2048, Q_T * 128, 1024), idesc_kn, (acc | (kk != 0)) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < Q_T / 16; ++kk)      // dK[kv, d] += dS^T[kv, q] Q[q, d]
+            umma_bf16_ss(tmem_base + DK_COL, make_smem_desc_sw128(dst + kk * 32, 16, 1024),
+                         make_smem_desc_sw128(q + kk * 2048, Q_T * 128, 1024), idesc_kn, (acc | (kk != 0)) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < KV_T / 16; ++kk)     // dQ^T[d, q] = K^T[d, kv] dS^T[kv, q]   (over S^T's columns)
+            umma_bf16_ss(tmem_base + b * 128, make_smem_desc_sw128(aK + kk * 2048, KV_T * 128, 1024),
+                         make_smem_desc_sw128(dst + kk * 2048, Q_T * 128, 1024), idesc_qt, kk != 0 ? 1u : 0u);
+          umma_commit(&mma2_done[b]);
+          umma_commit(&qdo_empty[b]);
+          // keep two S^T / dP^T tiles ahead of the softmax warps
+          if (issued < static_cast<uint32_t>(nq)) {
+            if (!issue_sdp(n_s)) { ok = false; break; }
+            ++n_s; ++issued;
+          }
+        }
+        if (!ok) break;
+        umma_commit(kv_empty);
+        ++n_kv; ++n_item;
+      }
+      if (!ok) atomicCAS(status, ST_OK, ST_TIMEOUT_MMA);
+    }
+  } else {
+    // ------------------------------------ softmax / dS / drains ---------------------------------
+    // warps w and w + 4 share a TMEM lane quarter and split the columns of every tile between them: two
+    // warps per scheduler hide each other's ALU and TMEM latencies
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                    // which half of the columns this warp handles
+    const int row = quarter * 32 + lane;                 // kv row (softmax) or d index (dQ^T drain) == TMEM lane
+    const int tid256 = threadIdx.x - 64;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    uint32_t n_t = 0;                                    // tiles processed so far (global counter)
+    bool ok = true;
+    auto drain_dq = [&](uint32_t idx, int q_start, int doc_end, int h) -> bool {
+      const int b = idx & 1;
+      if (!mbar_wait(&mma2_done[b], (idx >> 1) & 1, abort_flag)) return false;
+      tc_fence_after();
+      const int q_lim = min(doc_end, T) - q_start;       // query rows of this tile inside the document
+      float* base = dq_acc + (static_cast<size_t>(q_start) * heads + h) * HD + row;
+      {
+        const int c = half * 32;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (c + e < q_lim) red_add_f32(base + static_cast<size_t>(c + e) * heads * HD, __uint_as_float(r[e]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_drained[b]);
+      return true;
+    };
+    for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const int item = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+      const int* t = table + 2 + 4 * item;
+      const int kv_start = t[0], doc_end = t[2];
+      const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;
+      for (int i = 0; i < nq && ok; ++i, ++n_t) {
+        const int b = n_t & 1;
+        const uint32_t ph = (n_t >> 1) & 1;
+        const int q_start = kv_start + i * Q_T;
+        // the previous tile's dQ^T first: it frees its S columns for the MMA warp's look-ahead
+        if (i > 0) { if (!drain_dq(n_t - 1, q_start - Q_T, doc_end, h)) { ok = false; break; } }
+        {
+          const int c = tid256 & 63;
+          const int qi = q_start + c;
+          const bool v = qi < doc_end && qi < T;
+          if (tid256 < 64) sLse[b * Q_T + c] = v ? lse[static_cast<size_t>(h) * T + qi] : 0.f;
+          else if (tid256 < 128) sDelta[b * Q_T + c] = v ? delta[static_cast<size_t>(h) * T + qi] : 0.f;
+        }
+        group_sync();
+        if (!mbar_wait(&sdp_full[b], ph, abort_flag)) { ok = false; break; }
+        // P^T / dS^T buffer b was read by the MMAs of tile n_t - 2
+        if (n_t >= 2) { if (!mbar_wait(&mma2_done[b], ph ^ 1, abort_flag)) { ok = false; break; } }
+        tc_fence_after();
+        const int q_valid = min(Q_T, doc_end - q_start);
+        const bool diag = q_start < kv_start + KV_T;          // tile touches the causal diagonal
+        const int shift = q_start - kv_start;                 // keep (row, col) iff col + shift >= row
+        uint8_t* prow = sPT + b * PT_BYTES + row * 128;
+        uint8_t* drow = sdST + b * PT_BYTES + row * 128;
+        const float* lse_b = sLse + b * Q_T;
+        const float* del_b = sDelta + b * Q_T;
+        {
+          const int c = half * 32;
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + c, rs);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + 64 + c, rp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float p[8], ds[8];
+            const float4 l0 = *reinterpret_cast<const float4*>(lse_b + c + g * 8);
+            const float4 l1 = *reinterpret_cast<const float4*>(lse_b + c + g * 8 + 4);
+            const float4 d0 = *reinterpret_cast<const float4*>(del_b + c + g * 8);
+            const float4 d1 = *reinterpret_cast<const float4*>(del_b + c + g * 8 + 4);
+            const float lv[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+            const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int col = c + g * 8 + e;
+              const bool keep = col < q_valid && (!diag || col + shift >= row);
+              const float pv = exp2f(__uint_as_float(rs[g * 8 + e]) * scale_log2 - lv[e]);
+              p[e] = keep ? pv : 0.f;
+              ds[e] = keep ? pv * (__uint_as_float(rp[g * 8 + e]) - dv[e]) : 0.f;
+            }
+            uint4 pk, dk;
+            pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
+            pk.z = pack_bf16x2(p[4], p[5]); pk.w = pack_bf16x2(p[6], p[7]);
+            dk.x = pack_bf16x2(ds[0], ds[1]); dk.y = pack_bf16x2(ds[2], ds[3]);
+            dk.z = pack_bf16x2(ds[4], ds[5]); dk.w = pack_bf16x2(ds[6], ds[7]);
+            const int chunk = (c + g * 8) >> 3;
+            const int off = (chunk ^ (row & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + off) = pk;
+            *reinterpret_cast<uint4*>(drow + off) = dk;
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pds_full[b]);
+      }
+      if (!ok) break;
+      // last tile's dQ^T, then the finished dK_j, dV_j (their last MMAs retired with that tile's commit)
+      if (!drain_dq(n_t - 1, kv_start + (nq - 1) * Q_T, doc_end, h)) { ok = false; break; }
+      {
+        const int ki = kv_start + row;
+        const bool v = ki < doc_end && ki < T;
+        __nv_bfloat16* dk_dst = dqkv + (static_cast<size_t>(ki) * heads + h) * 3 * HD + HD;
+        __nv_bfloat16* dv_dst = dk_dst + HD;
+#pragma unroll
+        for (int c = half * 64; c < half * 64 + 64; c += 32) {
+          uint32_t rk[32], rv[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + DK_COL + c, rk);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + DV_COL + c, rv);
+          tmem_ld_wait();
+          if (v) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 ok_, ov_;
+              ok_.x = pack_bf16x2(__uint_as_float(rk[8 * q4 + 0]) * scale, __uint_as_float(rk[8 * q4 + 1]) * scale);
+              ok_.y = pack_bf16x2(__uint_as_float(rk[8 * q4 + 2]) * scale, __uint_as_float(rk[8 * q4 + 3]) * scale);
+              ok_.z = pack_bf16x2(__uint_as_float(rk[8 * q4 + 4]) * scale, __uint_as_float(rk[8 * q4 + 5]) * scale);
+              ok_.w = pack_bf16x2(__uint_as_float(rk[8 * q4 + 6]) * scale, __uint_as_float(rk[8 * q4 + 7]) * scale);
+              ov_.x = pack_bf16x2(__uint_as_float(rv[8 * q4 + 0]), __uint_as_float(rv[8 * q4 + 1]));
+              ov_.y = pack_bf16x2(__uint_as_float(rv[8 * q4 + 2]), __uint_as_float(rv[8 * q4 + 3]));
+              ov_.z = pack_bf16x2(__uint_as_float(rv[8 * q4 + 4]), __uint_as_float(rv[8 * q4 + 5]));
+              ov_.w = pack_bf16x2(__uint_as_float(rv[8 * q4 + 6]), __uint_as_float(rv[8 * q4 + 7]));
+              reinterpret_cast<uint4*>(dk_dst + c)[q4] = ok_;
+              reinterpret_cast<uint4*>(dv_dst + c)[q4] = ov_;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dkv_drained);
+    }
+    if (!ok && lane == 0) atomicCAS(status, ST_OK, ST_TIMEOUT_EPILOGUE);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace fbp
+
+// Launch of the pipelined kernel (table already built; delta computed; dq_acc cleared).
+int launch_fa_bwd_pipe(const void* qkv, const void* dout, const float* lse, const float* delta, void* dqkv,
+                       float* dq_acc, const int* table, int max_tiles, int T, int heads, float scale, int* status,
+                       cudaStream_t st, int num_sms) {
+  using namespace fbp;
+  CUtensorMap tm_kv, tm_q, tm_do;
+  const uint64_t ld_qkv = static_cast<uint64_t>(heads) * 3 * HD, ld_o = static_cast<uint64_t>(heads) * HD;
+  if (make_tmap_bf16_2d(&tm_kv, qkv, T, ld_qkv, ld_qkv, KV_T, 64)) return -2;
+  if (make_tmap_bf16_2d(&tm_q, qkv, T, ld_qkv, ld_qkv, Q_T, 64)) return -2;
+  if (make_tmap_bf16_2d(&tm_do, dout, T, ld_o, ld_o, Q_T, 64)) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(fa_bwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  const long work = static_cast<long>(max_tiles) * heads;
+  const int grid = static_cast<int>(work < num_sms ? work : num_sms);
+  fa_bwd_pipe_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tm_kv, tm_q, tm_do, table, lse, delta,
+                                                       reinterpret_cast<__nv_bfloat16*>(dqkv), dq_acc, T, heads,
+                                                       scale, scale * 1.4426950408889634f, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace hsb

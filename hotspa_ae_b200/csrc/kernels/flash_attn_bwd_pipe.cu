@@ -39,6 +39,11 @@ constexpr int TMEM_COLS = 512;
 constexpr int DV_COL = 256, DK_COL = 384;
 
 __device__ __forceinline__ void group_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
@@ -229,9 +234,16 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + c, r);
         tmem_ld_wait();
+        const size_t qstride = static_cast<size_t>(heads) * HD;
+        float* pq = base + static_cast<size_t>(c) * qstride;
+        if (c + 32 <= q_lim) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e)
-          if (c + e < q_lim) red_add_f32(base + static_cast<size_t>(c + e) * heads * HD, __uint_as_float(r[e]));
+          for (int e = 0; e < 32; ++e, pq += qstride) red_add_f32(pq, __uint_as_float(r[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e, pq += qstride)
+            if (c + e < q_lim) red_add_f32(pq, __uint_as_float(r[e]));
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -274,6 +286,8 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
           tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + c, rs);
           tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + 64 + c, rp);
           tmem_ld_wait();
+          // tiles away from the diagonal and inside the document (the common case) need no masking at all
+          const bool need_mask = diag || q_valid < Q_T;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float p[8], ds[8];
@@ -285,11 +299,17 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
             const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              const int col = c + g * 8 + e;
-              const bool keep = col < q_valid && (!diag || col + shift >= row);
-              const float pv = exp2f(__uint_as_float(rs[g * 8 + e]) * scale_log2 - lv[e]);
-              p[e] = keep ? pv : 0.f;
-              ds[e] = keep ? pv * (__uint_as_float(rp[g * 8 + e]) - dv[e]) : 0.f;
+              p[e] = ex2_approx(fmaf(__uint_as_float(rs[g * 8 + e]), scale_log2, -lv[e]));
+              ds[e] = p[e] * (__uint_as_float(rp[g * 8 + e]) - dv[e]);
+            }
+            if (need_mask) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int col = c + g * 8 + e;
+                const bool keep = col < q_valid && (!diag || col + shift >= row);
+                p[e] = keep ? p[e] : 0.f;
+                ds[e] = keep ? ds[e] : 0.f;
+              }
             }
             uint4 pk, dk;
             pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);

@@ -32,12 +32,14 @@ if ROOT not in sys.path:
 
 TOKENS_PER_GPU = 32768
 
-# (bucket bounds, [(dp, tp, pp, zero) per bucket, longest bucket first]) per world size, Llama-7B
+# per world size, Llama-7B: bucket bounds; (dp, tp, pp, zero) per bucket, longest bucket first; the strategies
+# that recompute their blocks in backward (the others keep activations: their per-rank state is small enough);
+# token budget of a micro-batch per strategy
 PLANS = {
-    1: ((32768, 0), [(1, 1, 1, False)]),
-    2: ((32768, 4096, 0), [(1, 2, 1, False), (2, 1, 1, True)]),
-    4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)]),
-    8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)]),
+    1: ((32768, 0), [(1, 1, 1, False)], [0], [32768]),
+    2: ((32768, 4096, 0), [(1, 2, 1, False), (2, 1, 1, True)], [0, 1], [32768, 32768]),
+    4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)], [0, 1], [32768, 32768, 12288]),
+    8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)], [0, 1], [16384, 16384, 12288]),
 }
 
 REFERENCE_UNAVAILABLE = (
@@ -54,7 +56,7 @@ def parse():
     ap.add_argument("--model", default="7b")
     ap.add_argument("--tokens_per_gpu", type=int, default=TOKENS_PER_GPU)
     ap.add_argument("--switch_mode", default="auto")
-    ap.add_argument("--mb_tokens", type=int, default=32768, help="token budget of a micro-batch")
+    ap.add_argument("--mb_tokens", type=int, default=0, help="override the token budget of a micro-batch")
     ap.add_argument("--no_e2e", action="store_true", help="skip the end-to-end region (profiling runs)")
     ap.add_argument("--breakdown", action="store_true", help="after the timed regions, run one more step with "
                                                              "per-bucket / per-switch CUDA-event timing (stderr)")
@@ -129,14 +131,14 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a GPU")
-    bounds, strategies = PLANS[world]
+    bounds, strategies, recompute, mb_tokens = PLANS[world]
     overrides = {"vocab_size": 32000}
     if args.layers:
         overrides["num_layers"] = args.layers
-    # micro-batches are sized by tokens (documents are independent under varlen attention); pipelined strategies
-    # get smaller ones so that the pipeline has several micro-batches in flight
-    mb_tokens = [args.mb_tokens if pp == 1 else args.mb_tokens // 2 for _, _, pp, _ in strategies]
-    trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=True,
+    # micro-batches are sized by tokens (documents are independent under varlen attention)
+    if args.mb_tokens:
+        mb_tokens = [args.mb_tokens] * len(strategies)
+    trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=recompute,
                                switch_mode=args.switch_mode, micro_batch_tokens=mb_tokens, **overrides)
     vocab = trainer.config.vocab_size
     tokens = args.tokens_per_gpu * world
@@ -238,7 +240,7 @@ def main():
             "config": {"model": f"llama-{args.model}" + (f"-{args.layers}layers(not headline)" if args.layers else ""),
                        "global_batch": f"{tokens} tokens/step", "seq_len": f"varlen<= {bounds[0]}",
                        "parallelism": par, "buckets": list(bounds), "optimizer": "Adam fp32 master",
-                       "recompute": "per block", "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
+                       "recompute": f"per block in strategies {recompute}", "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
                        "l2": "inputs larger than L2 (weights and activations of several GB stream every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

@@ -33,13 +33,14 @@ if ROOT not in sys.path:
 TOKENS_PER_GPU = 32768
 
 # per world size, Llama-7B: bucket bounds; (dp, tp, pp, zero) per bucket, longest bucket first; the strategies
-# that recompute their blocks in backward (the others keep activations: their per-rank state is small enough);
+# that recompute their blocks in backward (keeping the activations of a 12K-token micro-batch of the 7B model
+# took > 100 GB next to the arenas of three strategies and ran out of memory on 8 GPUs, so all of them recompute);
 # token budget of a micro-batch per strategy
 PLANS = {
     1: ((32768, 0), [(1, 1, 1, False)], [0], [32768]),
     2: ((32768, 4096, 0), [(1, 2, 1, False), (2, 1, 1, True)], [0, 1], [32768, 32768]),
-    4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)], [0, 1], [32768, 32768, 12288]),
-    8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)], [0, 1], [16384, 16384, 12288]),
+    4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)], [0, 1, 2], [32768, 32768, 32768]),
+    8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)], [0, 1, 2], [16384, 16384, 32768]),
 }
 
 REFERENCE_UNAVAILABLE = (

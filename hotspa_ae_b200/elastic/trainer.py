@@ -1,0 +1,189 @@
+"""Straggler-aware elastic trainer: static-parallel training that re-plans its strategy when devices slow down
+or drop out, and moves the whole training state (bf16 weights, fp32 master weights, Adam moments) to the new
+strategy with a hot switch.
+
+Loop (reference: python_refactor/elastic/engine/trainer.py:299-659):
+  every step     run one optimizer step under the current strategy; record this rank's compute time
+  every window   exchange the times (and heartbeats) on the host, turn them into slow-down ratios, ask
+                 :class:`StrategyModel` for the best plan; when it differs from the current one, add the new
+                 strategy to the graph (``merge_strategy`` re-traces the model), re-home the optimizer state and
+                 continue under the new strategy id.
+Failures are injected and detected on the host only: a rank that stops beating is excluded from the next plan
+before any kernel that would wait for it is launched.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import torch
+
+import hetu as ht
+
+from ..models.llama import LlamaLMHeadModel
+from ..parallel import mesh as M
+from ..parallel.strategy_config import generate_llama_3d_config, propagate_zero
+from ..train.trainer import HotSwitchTrainer
+from .straggler import SLIDING_WINDOW, StepTimeWindow, Straggler, WorkloadInfo, gather_times
+from .strategy import Plan, StrategyModel, to_config_args
+
+
+class ElasticTrainer(HotSwitchTrainer):
+    def __init__(self, model="7b", strategy=(1, 1, 1, False), max_len: int = 4096, window: int = SLIDING_WINDOW,
+                 threshold: float = 1.15, allowed=None, **kw):
+        from ..models.llama import LlamaConfig, llama_config
+        if not isinstance(model, LlamaConfig):
+            keys = {"num_layers", "hidden_size", "ffn_hidden_size", "num_heads", "vocab_size", "max_seq_len"}
+            model = llama_config(model, **{k: kw.pop(k) for k in list(kw) if k in keys})
+        model.uniform_trace = True
+        super().__init__(model, [tuple(strategy)], (max_len, 0), **kw)
+        self.window = StepTimeWindow(self.mesh.world_size, window, threshold)
+        self.allowed = allowed
+        self.zero = bool(strategy[3])
+        self.current = 0                                  # strategy id in use
+        self.pool: dict = {}                              # plan key -> strategy id
+        self.plans: list = [None]
+        self.injected_slowdown: dict = {}                 # rank -> factor (host-side fault injection for tests)
+        self.straggler = Straggler(self.device, None, WorkloadInfo(1, 1024, self.config.hidden_size))
+        self.replans = 0
+
+    # ---- strategies ------------------------------------------------------------------------------------
+    def add_strategy(self, cfg: dict) -> int:
+        """Adds one strategy to the live graph by re-tracing the model under ``merge_strategy``."""
+        cfg = propagate_zero(cfg)
+        g = self.graph
+        with ht.merge_strategy(g, num_strategy=1):
+            ac = ht.autocast(g.autocast_dtype) if g.autocast_dtype is not None else None
+            if ac is not None:
+                ac.__enter__()
+            try:
+                model = LlamaLMHeadModel(self.config, [cfg])
+                u, dg = ht.nn.config2ds(cfg["input"])
+                lu, ldg = ht.nn.config2ds(cfg["label"])
+                shape = [self.config.mbs_times_dp_symbol, self.config.seq_len_symbol]
+                ids = ht.parallel_placeholder(ht.int64, shape, [u], [dg], name="input_ids")
+                pos = ht.parallel_placeholder(ht.int64, shape, [u], [dg], name="position_ids")
+                cu = ht.parallel_placeholder(ht.int32, [self.config.mbs_times_dp_symbol, self.docs_symbol], [u], [dg],
+                                             name="cu_seqlens")
+                lab = ht.parallel_placeholder(ht.int64, shape, [lu], [ldg], name="labels")
+                model(ids, pos, cu, lab, reduction="sum")
+            finally:
+                if ac is not None:
+                    ac.__exit__(None, None, None)
+        sid = g.num_strategy - 1
+        self.cfgs.append(cfg)
+        self.in_ds.append(u)
+        self._dp_index.append(self._my_dp_index(sid))
+        self.micro_batch_tokens.append(self.micro_batch_tokens[0])
+        return sid
+
+    def switch_to(self, sid: int) -> None:
+        """Moves parameters, master weights and optimizer moments to strategy `sid` and trains under it from now on."""
+        self.graph.executor.store.rehome(sid)
+        self.current = sid
+
+    # ---- one step under the current strategy --------------------------------------------------------------
+    def step(self, sequences):
+        t0 = time.perf_counter()
+        if self.device.type == "cuda":
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        res = self._step_under(self.current, sequences)
+        if self.device.type == "cuda":
+            e1.record()
+            torch.cuda.synchronize()
+            mine = e0.elapsed_time(e1) / 1e3
+        else:
+            mine = time.perf_counter() - t0
+        mine *= self.injected_slowdown.get(self.mesh.rank, 1.0)
+        self.window.add(gather_times(mine))
+        return res
+
+    def _step_under(self, sid: int, sequences):
+        """The parent's step with bucket 0 mapped to strategy `sid`."""
+        batch = self._prepare_for(sid, sequences)
+        return self._run_for(sid, batch)
+
+    def _prepare_for(self, sid, sequences):
+        # one bucket holding everything; reuse the parent's machinery by temporarily viewing `sid` as bucket 0
+        from ..utils import data as D
+        packed = D.bucket_and_pack([len(s) for s in sequences], self.bounds, 1, False)[0]
+        members = [i for row in packed.rows for i in row]
+        budget = self.micro_batch_tokens[sid] or packed.max_len
+        mb = D.token_budget_micro_batches(sequences, members, self.dp_of(sid), self._dp_index[sid], budget,
+                                          self.pad_id, (256 if self.device.type == "cuda" else 8) * self.tp_of(sid))
+        feed = {}
+        for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"), (self.position_ids, "position_ids"),
+                        (self.cu_seqlens, "cu_seqlens")):
+            feed[ph] = [torch.from_numpy(a).to(self.device) for a in mb[key]]
+        total_targets = max(int(sum(max(len(s) - 1, 0) for s in sequences)), 1)
+        return dict(feed=feed, nmb=mb["num_micro_batches"], row_lens=mb["row_len"], total_targets=total_targets,
+                    tokens=int(sum(len(s) for s in sequences)), docs=int(mb["cu_seqlens"][0].shape[-1]))
+
+    def _run_for(self, sid, batch):
+        from ..train.trainer import StepResult
+        dp = self.dp_of(sid)
+        self.config.mbs_times_dp_symbol.set_data(dp)
+        self.docs_symbol.set_data(batch["docs"])
+        self._row_lens = batch["row_lens"]
+        if self._stat_dev is None:
+            self._stat_dev = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._stat_dev.zero_()
+        out = self.graph.run(self.loss, [self.loss, self.train_op], batch["feed"], batch["nmb"], sid,
+                             ht.run_level("update"), grad_scale=float(batch["nmb"] * dp) / batch["total_targets"])
+        if out and out[0] is not None:
+            self._stat_dev += out[0].float().sum() / self.tp_of(sid)
+        self.step_count += 1
+        loss = self._collect_loss(batch["total_targets"])
+        return StepResult(loss, batch["tokens"], batch["total_targets"], 0, 4,
+                          [dict(strategy=sid, micro_batches=batch["nmb"])])
+
+    # ---- detection and re-planning ------------------------------------------------------------------------------
+    def detect_straggler_and_plan(self, dead_ranks=()) -> Plan | None:
+        """When the window is full: best plan under the measured slow-downs, or None when nothing changes."""
+        if not self.window.full():
+            return None
+        slow = self.window.stragglers()
+        ranks = list(range(self.mesh.world_size))
+        model = StrategyModel(self.config.num_layers, ranks, slow, unused=list(dead_ranks), allowed=self.allowed)
+        plan = model.best()
+        cur = self.plans[self.current]
+        self.window.samples.clear()
+        if cur is not None and plan == cur:
+            return None
+        if cur is None and not slow and not dead_ranks:
+            return None
+        return plan
+
+    def apply_plan(self, plan: Plan) -> int:
+        key = plan.key()
+        if key in self.pool:
+            sid = self.pool[key]
+        else:
+            a = to_config_args(plan)
+            if plan.unused:
+                raise NotImplementedError("plans that drop devices need a new process group; restart from a checkpoint")
+            cfg = generate_llama_3d_config(self.config.num_layers, self.mesh.world_size, a["dp"], a["tp"], a["pp"],
+                                           self.zero, layers_per_stage=a["layers_per_stage"], rank_order=a["rank_order"])
+            sid = self.add_strategy(cfg)
+            self.pool[key] = sid
+            while len(self.plans) <= sid:
+                self.plans.append(None)
+            self.plans[sid] = plan
+        self.switch_to(sid)
+        self.replans += 1
+        return sid
+
+    def train(self, batches, log=None):
+        """Trains over `batches`, re-planning at every full window.  Returns the per-step results."""
+        out = []
+        for i, seqs in enumerate(batches):
+            res = self.step(seqs)
+            out.append(res)
+            plan = self.detect_straggler_and_plan()
+            if plan is not None:
+                sid = self.apply_plan(plan)
+                if log is not None and M.mesh().rank == 0:
+                    log(f"step {i}: re-planned to dp{plan.dp} tp{plan.tp} pp{plan.pp} layers {plan.layers_per_stage[0]} "
+                        f"(strategy {sid}, estimated step {plan.est_time:.2f})")
+        return out

@@ -84,6 +84,21 @@ class Tensor:
         return self.ds()
 
     def check_ds_hierarchy_equal(self, other_hierarchy) -> bool:
+        merge = getattr(self.graph, "_merge", None)
+        if merge is not None:
+            # While strategies are merged into an existing graph the program must re-issue exactly the recorded op
+            # sequence: a layer's "reshard only if needed" test follows what the original trace did at this point
+            # (a recorded comm is extended, and becomes a no-op for a strategy that does not need it).
+            cur = merge["op_cursor"]
+            ops = self.graph.ops
+            if cur < len(ops) and ops[cur].type == "comm" and ops[cur].inputs[0] is self:
+                return False
+            mine = self.ds_hierarchy[-len(other_hierarchy):] if len(self.ds_hierarchy) >= len(other_hierarchy) else []
+            same = len(mine) == len(other_hierarchy) and all(a.check_equal(b) for a, b in zip(mine, other_hierarchy))
+            if not same:
+                raise RuntimeError(f"merge_strategy: {self.name} needs a reshard under the new strategy that the "
+                                   f"original program does not contain")
+            return True
         if len(other_hierarchy) != len(self.ds_hierarchy):
             return False
         return all(a.check_equal(b) for a, b in zip(self.ds_hierarchy, other_hierarchy))

@@ -28,6 +28,8 @@ class LlamaConfig:
     reference_parity: bool = False     # LayerNorm with bias, no RoPE (the reference's "LLaMA")
     recompute: bool = False            # re-run each block in backward instead of keeping activations
     init_std: float = 0.02
+    uniform_trace: bool = False        # issue the same op sequence whatever the pipeline split (needed when strategies
+                                       # with other stage boundaries are merged into the graph later)
 
     @property
     def head_dim(self) -> int:
@@ -139,7 +141,7 @@ class LlamaModel(ht.nn.Module):
             groups = block.groups()
             crosses = prev_groups is not None and any(
                 [g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, groups))
-            if crosses and residual is not None:
+            if (crosses or c.uniform_trace) and residual is not None:
                 x, residual = x + residual, None                  # one tensor crosses the stage boundary
             x = ht.comm(x, block.rmsnorm_1.ds_union_map["split0"], groups, name=f"pipeline_layer_{block.layer_idx}_comm")
             if c.recompute:
@@ -149,7 +151,7 @@ class LlamaModel(ht.nn.Module):
                 x, residual = block(x, residual, position_ids, cu_seqlens)
             prev_groups = groups
         fin_groups = self.rmsnorm_f.device_group_unions
-        if any([g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, fin_groups)):
+        if c.uniform_trace or any([g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, fin_groups)):
             x, residual = x + residual, None
             x = ht.comm(x, self.rmsnorm_f.ds_union_map["split0"], fin_groups, name="pipeline_final_comm")
         return self.rmsnorm_f(x, residual)[0] if residual is not None else self.rmsnorm_f(x)

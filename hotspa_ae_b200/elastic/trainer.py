@@ -66,7 +66,8 @@ class ElasticTrainer(HotSwitchTrainer):
                 cu = ht.parallel_placeholder(ht.int32, [self.config.mbs_times_dp_symbol, self.docs_symbol], [u], [dg],
                                              name="cu_seqlens")
                 lab = ht.parallel_placeholder(ht.int64, shape, [lu], [ldg], name="labels")
-                model(ids, pos, cu, lab, reduction="sum")
+                loss = model(ids, pos, cu, lab, reduction="sum")
+                ht.group([loss], name="train_op")          # the op that AdamOptimizer.minimize recorded
             finally:
                 if ac is not None:
                     ac.__exit__(None, None, None)

@@ -1,0 +1,85 @@
+"""Elastic engine on the host: re-planner, straggler profile protocol, heartbeat liveness, and a 4-rank run whose
+slowed-down rank triggers a re-plan and a hot switch of the whole training state."""
+import os
+import socket
+import subprocess
+import sys
+import time
+
+import numpy as np
+import pytest
+
+from hotspa_ae_b200.elastic.straggler import Heartbeat, StepTimeWindow, Straggler, WorkloadInfo
+from hotspa_ae_b200.elastic.strategy import StrategyModel, split_layers, to_config_args
+from hotspa_ae_b200.parallel.strategy_config import generate_llama_3d_config
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_split_layers_balances_slow_stages():
+    counts, bott = split_layers(32, [1.0, 1.0])
+    assert counts == [16, 16] and bott == 16
+    counts, bott = split_layers(32, [1.0, 2.0])
+    assert sum(counts) == 32 and counts[0] > counts[1] and bott <= 22 + 1e-9
+    counts, _ = split_layers(5, [1.0, 1.0, 10.0])
+    assert counts[2] == 1 and sum(counts) == 5
+
+
+def test_replanner_moves_work_away_from_a_straggler():
+    healthy = StrategyModel(32, list(range(8)), {}, micro_batches=8, allowed=[(2, 2, 2), (8, 1, 1), (1, 4, 2)]).best()
+    slow = StrategyModel(32, list(range(8)), {5: 3.0}, micro_batches=8, allowed=[(2, 2, 2), (1, 4, 2)]).best()
+    assert healthy.est_time < slow.est_time
+    # the slow device sits in the stage that got the fewest layers of its pipeline
+    a = to_config_args(slow)
+    cfg = generate_llama_3d_config(32, 8, a["dp"], a["tp"], a["pp"], False, layers_per_stage=a["layers_per_stage"],
+                                   rank_order=a["rank_order"])
+    blocks = cfg["llama"]["blocks"]
+    sizes = {k: (v["range"][1] - v["range"][0] + 1, v["layernorm1"]["device_group_union"][0]) for k, v in blocks.items()}
+    slow_stage = [n for n, ranks in sizes.values() if 5 in ranks][0]
+    assert slow_stage == min(n for n, _ in sizes.values())
+    assert sorted(r for _, ranks in sizes.values() for r in ranks) == list(range(8))
+    # an unusable device is left out of every group
+    fewer = StrategyModel(32, list(range(8)), {}, unused=[7], micro_batches=8).best()
+    assert 7 in fewer.unused and 7 not in fewer.rank_order
+
+
+def test_step_time_window_and_profile_files(tmp_path):
+    w = StepTimeWindow(4, window=3, threshold=1.2)
+    for _ in range(3):
+        w.add([1.0, 1.0, 1.6, 1.0])
+    assert w.full() and list(w.stragglers()) == [2]
+    s = Straggler("cpu", str(tmp_path / "prof" / "dev0.txt"), WorkloadInfo(1, 32, 32))
+    s.begin_profile()
+    for _ in range(4):
+        assert s.run_profile() > 0
+    s.end_profile()
+    vals = Straggler.read_profile(s.log_file, 3)
+    assert len(vals) == 3
+    with pytest.raises(TimeoutError):
+        Straggler.read_profile(str(tmp_path / "never.txt"), 1, timeout_s=0.2)
+
+
+def test_heartbeat_reports_a_rank_that_stopped(tmp_path):
+    hb = [Heartbeat(r, 3, directory=str(tmp_path), limit_s=0.5) for r in range(3)]
+    for h in hb:
+        h.beat()
+    assert hb[0].dead_ranks() == []
+    time.sleep(0.7)
+    hb[0].beat(); hb[1].beat()                       # rank 2 went silent
+    assert hb[0].dead_ranks() == [2] and hb[1].dead_ranks() == [2]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_replan_and_switch_keeps_training_state():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "elastic_worker.py")]
+    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900, env=env)
+    assert proc.returncode == 0, proc.stdout[-3000:]

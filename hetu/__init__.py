@@ -6,8 +6,12 @@ package (python_refactor/hetu/__init__.py and its bound ops, codegen/ops.yml).
 """
 from hotspa_ae_b200.core import (DistributedStates, DistributedStatesUnion, IntSymbol, NULL_HETERO_DIM,  # noqa: F401
                                  map_to_local_data)
-from hotspa_ae_b200.graph.graph import (Graph, autocast, from_numpy_parallel, graph, merge_strategy,  # noqa: F401
-                                        parallel_parameter, parallel_placeholder, placeholder, recompute, run_level)
+from hotspa_ae_b200.graph.graph import (Graph, autocast, from_numpy, from_numpy_parallel, graph,  # noqa: F401
+                                        merge_strategy, parallel_parameter, parallel_placeholder, placeholder,
+                                        recompute, run_level)
+from hotspa_ae_b200.graph.gradscaler import GradScaler  # noqa: F401
+from hotspa_ae_b200.utils.dataset import Dataloader  # noqa: F401
+from hotspa_ae_b200.core.stream import Event, Stream, get_stream  # noqa: F401
 from hotspa_ae_b200.graph.init import *  # noqa: F401,F403
 from hotspa_ae_b200.graph.ops import *  # noqa: F401,F403
 from hotspa_ae_b200.graph.ops import (abs, bool, pow, reduce, round, slice)  # noqa: F401,A004

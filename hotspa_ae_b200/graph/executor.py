@@ -516,7 +516,22 @@ class Executor:
         if wants_train and run_level == UPDATE:
             if self.store.home != self.store.canonical(sid):
                 raise RuntimeError("UPDATE must run under the home strategy (the one that was allocated first)")
-            self.store.reduce_and_step(self.graph.optimizer, 1.0)
+            opt = self.graph.optimizer
+            scaler = getattr(opt, "grad_scaler", None)
+            if scaler is not None and scaler.enabled:
+                # dynamic loss scaling: skip the update (and shrink the scale) when any rank saw a non-finite gradient
+                garena = self.store.grad_arena(self.store.home)
+                bad = torch.tensor([0.0 if scaler.check_finite(garena) else 1.0], device=garena.device)
+                if self.mesh.world_size > 1 and not self.mesh.virtual:
+                    torch.distributed.all_reduce(bad)
+                if float(bad.item()) > 0:
+                    garena.zero_()
+                    scaler.step_update(True)
+                else:
+                    self.store.reduce_and_step(opt, scaler.unscale_factor())
+                    scaler.step_update(False)
+            else:
+                self.store.reduce_and_step(opt, 1.0)
 
         out = []
         for f in fetches:

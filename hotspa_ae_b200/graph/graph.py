@@ -213,6 +213,11 @@ class Graph:
                        None if n_out == 1 and name is None else (f"{op.name}:{k}"), req)
             op.outputs.append(t)
         self.ops.append(op)
+        if self.kind == "eager":
+            # eager graphs compute every op as soon as it is made (reference: hetu/graph/eager_graph.cc)
+            vals = self.run(None, list(op.outputs), {}, 1, 0, UPDATE)
+            for t, v in zip(op.outputs, vals):
+                t.eager_value = v
         return op.outputs
 
     def _deduce_strategy(self, impl, inputs, attrs, s, n_out):
@@ -340,6 +345,14 @@ def parallel_parameter(init, global_shape, ds_hierarchy, local_idx=None, dtype=t
 
 def from_numpy_parallel(data, ds_hierarchy, requires_grad=False, device_group_hierarchy=None, name=None):
     return current_graph().from_numpy_parallel(data, ds_hierarchy, requires_grad, device_group_hierarchy, name)
+
+
+def from_numpy(data, requires_grad: bool = False, name=None):
+    """A replicated constant tensor holding `data` (reference: hetu.from_numpy)."""
+    n = M.mesh().world_size
+    ds = DistributedStatesUnion([DistributedStates(n, {-1: n}, [-1])])
+    g = current_graph()
+    return g.from_numpy_parallel(np.asarray(data), [ds] * g.num_strategy, requires_grad, None, name)
 
 
 def placeholder(dtype, shape, name=None):

@@ -150,7 +150,18 @@ class Tensor:
         return self.graph.get_local_data(self)
 
     def numpy(self, force: bool = True):
-        return self.get_data()
+        """Parameters / constants: their local data.  Other tensors of eager and define-by-run graphs: their value,
+        computed now if it is not known yet (reference: DefineByRunGraph::GetOrCompute)."""
+        if self.is_parameter or self.id in self.graph.constants:
+            return self.get_data()
+        if getattr(self, "eager_value", None) is not None:
+            return self.eager_value.detach().float().cpu().numpy() if self.eager_value.is_floating_point() \
+                else self.eager_value.cpu().numpy()
+        if self.graph.kind in ("eager", "define_by_run"):
+            (v,) = self.graph.run(None, [self], {}, 1, 0, 0)
+            self.eager_value = v
+            return v.detach().float().cpu().numpy() if v.is_floating_point() else v.cpu().numpy()
+        raise ValueError(f"{self} has no value outside a run; fetch it through graph.run")
 
     def reset_data(self, array: np.ndarray) -> None:
         """Overwrite a parameter from a *global* numpy array (sliced by the current strategy-0 DS)."""

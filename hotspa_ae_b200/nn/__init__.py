@@ -3,3 +3,6 @@ from .parallel_layers import (HtMultiColumnParallelLinear, HtMultiParallelEmbedd
                               HtMultiParallelLayerNorm, HtMultiParallelRMSNorm, HtMultiRowParallelLinear,
                               HtMultiVocabParallelEmbedding, config2ds, get_local_index, parallel_data_provider,
                               parallel_multi_data_provider)
+from .layers import (CrossEntropyLoss, Embedding, GELU, HtColumnParallelLinear, HtParallelEmbedding,  # noqa: F401
+                     HtParallelLayerNorm, HtParallelRMSNorm, HtRowParallelLinear, HtVocabParallelEmbedding, LayerNorm,
+                     Linear, MSELoss, ReLU, RMSNorm, SiLU, Sigmoid, Tanh)

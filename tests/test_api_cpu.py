@@ -1,0 +1,83 @@
+"""API surface on one CPU process: eager / define-by-run graphs, plain nn layers with an optimizer, GradScaler,
+streams and events, logging, profiler hooks."""
+import json
+import os
+
+import numpy as np
+import torch
+
+import hetu as ht
+from hotspa_ae_b200.utils import logging as L
+from hotspa_ae_b200.utils.profiler import CUDAProfiler, MemoryTrace
+
+
+def test_eager_and_define_by_run_graphs():
+    ht.init_comm_group(8)
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    b = np.ones((4, 2), dtype=np.float32)
+    with ht.graph("eager"):
+        y = ht.matmul(ht.from_numpy(a), ht.from_numpy(b))
+        assert y.eager_value is not None                       # computed at definition time
+        np.testing.assert_allclose(y.numpy(), a @ b)
+    with ht.graph("define_by_run"):
+        z = ht.relu(ht.from_numpy(a) - 5.0)
+        assert getattr(z, "eager_value", None) is None          # lazy until asked for
+        np.testing.assert_allclose(z.numpy(), np.maximum(a - 5.0, 0))
+
+
+def test_plain_layers_train_with_adam():
+    ht.init_comm_group(8)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((64, 8)).astype(np.float32)
+    w_true = rng.standard_normal((8, 1)).astype(np.float32)
+    y = x @ w_true
+    with ht.graph("define_and_run") as g:
+        xp, yp = ht.placeholder(ht.float32, [64, 8], name="x"), ht.placeholder(ht.float32, [64, 1], name="y")
+        net = ht.nn.Sequential([ht.nn.Linear(8, 16, name="l1"), ht.nn.Tanh(), ht.nn.Linear(16, 1, name="l2")])
+        loss = ht.nn.MSELoss()(net(xp), yp)
+        train_op = ht.AdamOptimizer(lr=1e-2).minimize(loss)
+    losses = [float(g.run(loss, [loss, train_op], {xp: x, yp: y}, 1, 0, ht.run_level("update"))[0]) for _ in range(60)]
+    assert losses[-1] < 0.2 * losses[0]
+
+
+def test_grad_scaler_skips_overflow_and_adapts():
+    s = ht.GradScaler(init_scale=1024.0, growth_interval=2)
+    assert s.check_finite(torch.ones(4)) and not s.check_finite(torch.tensor([1.0, float("inf")]))
+    s.step_update(True)
+    assert s.get_scale() == 512.0
+    s.step_update(False); s.step_update(False)
+    assert s.get_scale() == 1024.0
+    # inside the executor: an overflowing step leaves the weights untouched
+    ht.init_comm_group(8)
+    with ht.graph("define_and_run") as g:
+        xp = ht.placeholder(ht.float32, [4, 3], name="x")
+        lin = ht.nn.Linear(3, 2, name="gs")
+        loss = ht.reduce_sum(lin(xp))
+        opt = ht.AdamOptimizer(lr=1e-1)
+        scaler = ht.GradScaler(init_scale=8.0)
+        train_op = scaler.minimize(opt, loss)
+    good = np.ones((4, 3), dtype=np.float32)
+    g.run(loss, [loss, train_op], {xp: good}, 1, 0, ht.run_level("update"), **scaler.run_kwargs())
+    w1 = lin.weight.get_data().copy()
+    bad = good.copy(); bad[0, 0] = np.inf
+    g.run(loss, [loss, train_op], {xp: bad}, 1, 0, ht.run_level("update"), **scaler.run_kwargs())
+    np.testing.assert_array_equal(lin.weight.get_data(), w1)
+    assert scaler.get_scale() == 4.0
+
+
+def test_streams_events_logging_profiler(tmp_path, monkeypatch):
+    st = ht.get_stream("cpu", 6)
+    e0, e1 = ht.Event("cpu"), ht.Event("cpu")
+    with st:
+        e0.record(st)
+        e1.record(st)
+    assert e1.time_since(e0) >= 0.0
+    L.set_level("INFO")
+    L.TIK("t"); assert L.TOK("t") >= 0 and L.COST_MSEC("t") >= 0
+    L.info("hello")
+    info = CUDAProfiler("cpu").memory_info()
+    assert "mempool_reserved" in info
+    monkeypatch.setenv("HETU_MEMORY_PROFILE", "MICRO_BATCH")
+    tr = MemoryTrace(str(tmp_path / "mem.json"))
+    tr.sample(0, True); tr.flush()
+    assert json.load(open(tmp_path / "mem.json"))[0]["micro_batch_id"] == 0

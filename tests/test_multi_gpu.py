@@ -60,3 +60,12 @@ def test_hot_switch_four_gpus_fused():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_all_gather_gemm_and_gemm_reduce_scatter():
     _torchrun(2, "fused_tp_worker.py")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("strategies,bounds", [
+    ([[2, 1, 1, True]], [2048, 0]),                            # static data parallel + ZeRO: fused reduce+Adam+all-gather
+    ([[1, 2, 1, False], [2, 1, 1, True]], [2048, 512, 0]),     # hot switch tp2 <-> dp2: fused reshard + fused tp GEMMs
+])
+def test_trainer_fused_paths_track_nccl_paths(strategies, bounds):
+    _torchrun(2, "trainer_worker.py", json.dumps(strategies), json.dumps(bounds))

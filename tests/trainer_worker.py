@@ -1,0 +1,51 @@
+"""Worker: bf16 training through the public trainer on GPUs; the fused peer-memory paths (reshard, reduce+Adam,
+all-gather/reduce-scatter GEMMs) must track the NCCL paths step by step."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.ops import _lib  # noqa: E402
+from hotspa_ae_b200.parallel import fused_tp, mesh  # noqa: E402
+from hotspa_ae_b200.train.trainer import HotSwitchTrainer  # noqa: E402
+from hotspa_ae_b200.utils import data as D  # noqa: E402
+
+
+def run(strategies, bounds, mode, steps):
+    mesh.reset_mesh()
+    fused_tp.enabled = mode == "fused"
+    tr = HotSwitchTrainer("tiny", strategies, bounds, lr=2e-3, dtype=torch.bfloat16, recompute=True, switch_mode=mode,
+                          micro_batch_tokens=2048, num_layers=2, hidden_size=512, ffn_hidden_size=1024, num_heads=4,
+                          vocab_size=2048, max_seq_len=2048)
+    tr.graph.executor.fuse_tp_comm = mode == "fused"
+    losses = []
+    for i in range(steps):
+        lens = D.lognormal_lengths(8192, seed=i % 2, median=300, max_len=2048)
+        losses.append(tr.step(D.synthetic_sequences(lens, 2048, seed=i % 2)).loss)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return losses
+
+
+def main():
+    strategies = [tuple(s) for s in json.loads(sys.argv[1])]
+    bounds = json.loads(sys.argv[2])
+    ht.init_comm_group(8)
+    rank = int(os.environ.get("RANK", "0"))
+    a = run(strategies, bounds, "nccl", 6)
+    b = run(strategies, bounds, "fused", 6)
+    ok = all(np.isfinite(a)) and all(np.isfinite(b)) and b[-1] < b[0] and np.allclose(a, b, rtol=2e-2, atol=2e-2)
+    print(f"rank {rank}: nccl {np.round(a, 4).tolist()} fused {np.round(b, 4).tolist()} ok={ok}", flush=True)
+    t = torch.tensor([0 if ok else 1], device="cuda")
+    torch.distributed.all_reduce(t)
+    torch.distributed.destroy_process_group()
+    sys.exit(0 if int(t.item()) == 0 else 3)
+
+
+if __name__ == "__main__":
+    main()

@@ -39,6 +39,10 @@ def parse_args(argv=None):
     ap.add_argument("--bucket_sizes", default="32768 0")
     ap.add_argument("--zero", action="store_true", help="shard optimizer state over data-parallel ranks (ZeRO-1)")
     ap.add_argument("--global_tokens", type=int, default=0, help="synthetic tokens per step (whole job)")
+    ap.add_argument("--fixed_len", type=int, default=0,
+                    help="synthetic data: global_batch_size sequences of exactly this length per step")
+    ap.add_argument("--micro_batch_tokens", type=int, default=0,
+                    help="token budget of a micro-batch (0: one packed row of the bucket's length per micro-batch)")
     ap.add_argument("--global_batch_size", type=int, default=64, help="sequences per step when reading a dataset")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("-e", "--epochs", type=int, default=1)
@@ -76,6 +80,10 @@ def batches(args, trainer):
         return
     world = M.mesh().world_size
     tokens = args.global_tokens or 32768 * world
+    if args.fixed_len:
+        for i in range(args.steps * args.epochs):
+            yield D.synthetic_sequences([args.fixed_len] * args.global_batch_size, vocab, seed=args.seed + i)
+        return
     for i in range(args.steps * args.epochs):
         lens = D.lognormal_lengths(tokens, seed=args.seed + i, max_len=max_len)
         yield D.synthetic_sequences(lens, vocab, seed=args.seed + i)

@@ -319,7 +319,8 @@ def build_trainer_from_args(args) -> HotSwitchTrainer:
     return HotSwitchTrainer(args.model_size, strategies or (), bounds, lr=args.lr,
                             dtype=torch.bfloat16 if args.bf16 else torch.float32, recompute=not args.no_recompute,
                             switch_mode=args.switch_mode, weight_decay=args.adam_weight_decay,
-                            ds_parallel_configs=cfgs, **overrides)
+                            ds_parallel_configs=cfgs, micro_batch_tokens=getattr(args, "micro_batch_tokens", 0) or None,
+                            **overrides)
 
 
 def timed_steps(trainer: HotSwitchTrainer, batches, log=None):

@@ -26,7 +26,8 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 
 constexpr int FA_BM = 128;      // query rows per tile
 constexpr int FA_BN = 128;      // kv rows per tile
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
+constexpr int FA_SM_WARPS = 8;
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;   // log2 units
 
 // work table layout (int32): [0] = number of tiles, [1] = scratch, then 4 ints per tile:
@@ -71,7 +72,8 @@ struct FaCfg {
   static constexpr int TILE_BYTES = FA_BM * HD * 2;   // Q, K, V tiles
   static constexpr int P_BYTES = FA_BM * FA_BN * 2;
   static constexpr int KV_STAGES = 2;
-  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 1024 + 256;
+  // tiles + barriers (256 B) + cross-warp exchange (2 KB); the dynamic shared memory is declared 1024-byte aligned
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 2 * P_BYTES + 256 + 2048;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
 };
@@ -83,13 +85,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
               int* __restrict__ status) {
   using Cfg = FaCfg<HD>;
   constexpr int SUB = Cfg::SUB;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {            // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(status, ST_OK, ST_BAD_ARGUMENT);
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::TILE_BYTES;
   uint8_t* sV = sK + Cfg::KV_STAGES * Cfg::TILE_BYTES;
   uint8_t* sP = sV + Cfg::KV_STAGES * Cfg::TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::P_BYTES);     // P is double buffered
   uint64_t* q_full = bars + 0;
   uint64_t* q_empty = bars + 1;
   uint64_t* k_full = bars + 2;    // [2]
@@ -103,6 +109,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
   uint64_t* o_empty = bars + 16;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* x_max = reinterpret_cast<float*>(bars + 20);       // [2 halves][128 rows] partial row maxima
+  float* x_sum = x_max + 2 * FA_BM;                          // [2 halves][128 rows] partial row sums (epilogue)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = table[0];
@@ -113,9 +121,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], FA_SM_WARPS);
     }
-    mbar_init(p_full, 4); mbar_init(pv_done, 1); mbar_init(o_empty, 4);
+    mbar_init(p_full, FA_SM_WARPS); mbar_init(pv_done, 1); mbar_init(o_empty, FA_SM_WARPS);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -183,7 +191,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
 #pragma unroll
         for (int kk = 0; kk < FA_BN / 16; ++kk) {
           // A = P: K-major, kv 0..63 in sub-tile 0, 64..127 in sub-tile 1
-          const uint64_t ad = make_smem_desc_sw128(aP + (kk / 4) * (FA_BM * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t ad = make_smem_desc_sw128(aP + (n_p & 1) * Cfg::P_BYTES + (kk / 4) * (FA_BM * 128) + (kk % 4) * 32, 16, 1024);
           // B = V: MN-major ([kv rows, HD cols]); 16 kv rows = 2048 bytes; 64-column blocks FA_BN*128 apart
           const uint64_t bd = make_smem_desc_sw128(vb + kk * 2048, FA_BN * 128, 1024);
           umma_bf16_ss(tmem_base + Cfg::O_COL, ad, bd, idesc_pv, (first && kk == 0) ? 0u : 1u);
@@ -226,61 +234,68 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
     }
   } else {
     // ------------------------------------ softmax + epilogue ---------------------------------
+    // Warps w and w + 4 share a TMEM lane quarter (the same 32 query rows) and split the 128 kv columns of every
+    // score tile between them; the row maximum is combined through shared memory with a 64-thread named barrier.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                    // 0: kv columns 0..63, 1: columns 64..127
     const int row = quarter * 32 + lane;                 // row inside the query tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    uint32_t n_s = 0, n_pv = 0;
+    const int c0 = half * 64;
+    uint32_t n_s = 0, n_pv = 0, n_pt = 0;      // n_pt: P tiles written so far (selects the P buffer, like the MMA side)
     bool ok = true;
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory"); };
     for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
       const int tile = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
       const int* t = table + 2 + 4 * tile;
       const int q_start = t[0], doc_end = t[2], qt = t[3];
       const int q_idx = q_start + row;
-      float m_ref = -INFINITY, l_sum = 0.f;
+      float m_ref = -INFINITY, l_sum = 0.f;              // l_sum: this warp's half of the row sum
       for (int j = 0; j <= qt && ok; ++j) {
         const int sb = n_s & 1;
         if (!mbar_wait(&s_full[sb], (n_s >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t s_addr = tmem_base + lane_addr + (sb ? Cfg::S_COL1 : Cfg::S_COL0);
-        float sv[FA_BN];
+        const uint32_t s_addr = tmem_base + lane_addr + (sb ? Cfg::S_COL1 : Cfg::S_COL0) + c0;
+        float sv[64];
 #pragma unroll
-        for (int c = 0; c < FA_BN; c += 32) {
+        for (int c = 0; c < 64; c += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(s_addr + c, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]) * scale_log2;
         }
-        // S buffer may be overwritten by the MMA of tile j+2 now
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[sb]);
         ++n_s;
         if (j == qt) {
-          // diagonal tile: kv (column) beyond the query (row) is masked
 #pragma unroll
-          for (int c = 0; c < FA_BN; ++c)
-            if (c > row) sv[c] = -INFINITY;
+          for (int c = 0; c < 64; ++c)
+            if (c0 + c > row) sv[c] = -INFINITY;
         }
         float mx = sv[0];
 #pragma unroll
-        for (int c = 1; c < FA_BN; ++c) mx = fmaxf(mx, sv[c]);
-        // the previous PV must have retired before P is overwritten / O is rescaled
-        if (j > 0) {
-          if (!mbar_wait(pv_done, n_pv & 1, abort_flag)) { ok = false; break; }
-          ++n_pv;
-          tc_fence_after();
-        }
+        for (int c = 1; c < 64; ++c) mx = fmaxf(mx, sv[c]);
+        x_max[half * FA_BM + row] = mx;
+        pair_sync();
+        mx = fmaxf(mx, x_max[(half ^ 1) * FA_BM + row]);
         float alpha = 1.f;
+        bool waited = false;
         const bool grow = mx > m_ref + FA_RESCALE_THRESHOLD;
+        // both warps of a quarter hold the same rows and the same combined maxima: they take the same branch
         if (j == 0) {
           m_ref = mx;
         } else if (__any_sync(0xffffffffu, grow)) {
+          // O is rescaled in TMEM: the previous PV must have retired first (the only early wait on it)
+          if (!mbar_wait(pv_done, n_pv & 1, abort_flag)) { ok = false; break; }
+          ++n_pv;
+          waited = true;
+          tc_fence_after();
           if (grow) { alpha = exp2f(m_ref - mx); m_ref = mx; }
           l_sum *= alpha;
-          const uint32_t o_addr = tmem_base + lane_addr + Cfg::O_COL;
+          const uint32_t o_addr = tmem_base + lane_addr + Cfg::O_COL + half * (HD / 2);
 #pragma unroll
-          for (int c = 0; c < HD; c += 16) {
+          for (int c = 0; c < HD / 2; c += 16) {
             uint32_t r[16];
             tmem_ld_32x32b_x16(o_addr + c, r);
             tmem_ld_wait();
@@ -290,37 +305,52 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
           }
           tmem_st_wait();
         }
-        // P = exp2(s - m_ref), packed to bf16 into the swizzled K-major tile
         float rs = 0.f;
-        uint8_t* prow = sP + row * 128;
+        // P tiles alternate between two buffers: tile j is written while the PV MMA of tile j-1 still reads the other
+        uint8_t* prow = sP + (n_pt & 1) * Cfg::P_BYTES + row * 128 + half * (FA_BM * 128);
 #pragma unroll
-        for (int c = 0; c < FA_BN; c += 8) {
+        for (int c = 0; c < 64; c += 8) {
           float p[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) { p[i] = exp2f(sv[c + i] - m_ref); rs += p[i]; }
+          for (int i = 0; i < 8; ++i) {
+            float e;
+            const float x = sv[c + i] - m_ref;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+            p[i] = e;
+            rs += e;
+          }
           uint4 pk;
           pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
           pk.z = pack_bf16x2(p[4], p[5]); pk.w = pack_bf16x2(p[6], p[7]);
-          const int sub = c >> 6, chunk = (c & 63) >> 3;
-          *reinterpret_cast<uint4*>(prow + sub * (FA_BM * 128) + ((chunk ^ (row & 7)) << 4)) = pk;
+          const int chunk = c >> 3;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = pk;
         }
         l_sum += rs;
+        // PV of tile j-1 retired: keeps the wait count in step and frees buffer (j-1)&1 for tile j+1
+        if (j > 0 && !waited) {
+          if (!mbar_wait(pv_done, n_pv & 1, abort_flag)) { ok = false; break; }
+          ++n_pv;
+        }
         fence_proxy_async_smem();
         tc_fence_before();
-        __syncwarp();
+        pair_sync();                 // x_max may be rewritten by the faster warp only after both have read it
         if (lane == 0) mbar_arrive(p_full);
+        ++n_pt;
       }
       if (!ok) break;
-      // epilogue: wait for the last PV, normalise, store
+      // epilogue: combine the halves of the row sum, wait for the last PV, normalise, store
+      x_sum[half * FA_BM + row] = l_sum;
       if (!mbar_wait(pv_done, n_pv & 1, abort_flag)) { ok = false; break; }
       ++n_pv;
       tc_fence_after();
-      const float inv = 1.f / l_sum;
-      const uint32_t o_addr = tmem_base + lane_addr + Cfg::O_COL;
+      pair_sync();
+      const float l_tot = l_sum + x_sum[(half ^ 1) * FA_BM + row];
+      const float inv = 1.f / l_tot;
+      const uint32_t o_addr = tmem_base + lane_addr + Cfg::O_COL + half * (HD / 2);
       const bool valid = q_idx < doc_end && q_idx < T;
-      __nv_bfloat16* orow = out + (static_cast<size_t>(q_idx) * heads + h) * HD;
+      __nv_bfloat16* orow = out + (static_cast<size_t>(q_idx) * heads + h) * HD + half * (HD / 2);
 #pragma unroll
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = 0; c < HD / 2; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(o_addr + c, r);
         tmem_ld_wait();
@@ -336,9 +366,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
           }
         }
       }
-      if (valid) lse[static_cast<size_t>(h) * T + q_idx] = m_ref + log2f(l_sum);
+      if (valid && half == 0) lse[static_cast<size_t>(h) * T + q_idx] = m_ref + log2f(l_tot);
       tc_fence_before();
-      __syncwarp();
+      pair_sync();                   // x_sum is reused by the next work item
       if (lane == 0) mbar_arrive(o_empty);
     }
     if (!ok && lane == 0) atomicCAS(status, ST_OK, ST_TIMEOUT_EPILOGUE);

@@ -40,6 +40,7 @@ class CommInfo:
     src_peer: int = -1      # for P2P: the rank we receive from
     dst_peer: int = -1      # for P2P: the rank we send to
     fused: bool = False     # the neighbouring linear op performs this collective inside its GEMM kernel
+    repartition: bool = False   # boundary op whose pieces come from the reshard planner (layouts differ)
 
 
 @dataclass
@@ -211,7 +212,19 @@ class Executor:
                     comm[op.id] = info
                     continue
                 if kind == C._C.COMM_BATCHED_SEND_RECV:
-                    raise NotImplementedError(f"{op}: activation repartition between different layouts/groups")
+                    # activation repartition between two device groups whose layouts differ (e.g. the
+                    # tensor-parallel degree changes across a pipeline boundary): pieces come from the reshard
+                    # planner at run time (reference: ComplexExecComm, hetu/graph/switch_exec_graph.cc:2021-2193)
+                    if set(s_ranks) & set(d_ranks):
+                        raise NotImplementedError(f"{op}: repartition between overlapping device groups")
+                    info = CommInfo(kind, name)
+                    info.repartition = True
+                    if rank in s_ranks:
+                        send_ops.append(op)
+                    if rank in d_ranks:
+                        recv_ops.append(op)
+                    comm[op.id] = info
+                    continue
                 # every rank computes every rank's collective group so that groups are created collectively
                 sds, dds = x.ds(sid), y.ds(sid)
                 for idx in range(len(s_ranks)):
@@ -248,6 +261,11 @@ class Executor:
         for ph in g.placeholders:
             dp = max(dp, ph.ds(sid).get_dim(0))
             break
+        # the loss-gradient seed is 1 / (micro-batches x data-parallel partitions of the LOSS): a loss that is not
+        # split over replicas (e.g. behind a gather) is not averaged over them
+        loss_op_out = getattr(g, "train_op", None)
+        if loss_op_out is not None and loss_op_out.producer is not None and loss_op_out.producer.inputs:
+            dp = max(1, loss_op_out.producer.inputs[0].ds(sid).get_dim(0))
         segments = self._segments(my_ops, sid, send_ops)
         loss_local = False
         plan = ExecPlan(sid, stages, my_stage, my_ops, segments, recv_ops, send_ops, comm, dp, loss_local)
@@ -339,6 +357,89 @@ class Executor:
             if not s.outputs:
                 s.outputs = list(s.ops[-1].outputs)
         return segs
+
+    # ---- stage-boundary transfers ---------------------------------------------------------------------------
+    def _pieces(self, op, sid):
+        """For a boundary comm op: the rectangles this rank sends and receives, in a fixed global order.
+        Plain pipeline p2p is one whole-shard piece; a repartition asks the reshard planner."""
+        x, y = op.inputs[0], op.outputs[0]
+        info = self.plan(sid).comm[op.id]
+        rank = self.mesh.rank
+        if not info.repartition:
+            sends = [] if info.dst_peer < 0 else [(info.dst_peer, None)]
+            recvs = [] if info.src_peer < 0 else [(info.src_peer, None)]
+            return sends, recvs
+        shape = list(x.global_shape)
+        key = (op.id, sid, tuple(shape))
+        cache = self.const_cache.setdefault("_pieces", {})
+        if key not in cache:
+            s_regs, d_regs = [], []
+            for m, g in enumerate(x.dg_hierarchy[sid]):
+                s_regs += C.regions_of(shape, x.ds(sid, m), g.ranks(), -1)
+            for m, g in enumerate(y.dg_hierarchy[sid]):
+                d_regs += C.regions_of(shape, y.ds(sid, m), g.ranks(), -1)
+            pl = C.ReshardPlanner(self.mesh.world_size, 3)
+            pl.add_tensor_regions(0, s_regs, d_regs, False)
+            copies = list(pl.copies())
+            # backward: the gradient of a replicated tensor is replicated too (its partial sums were all-reduced by
+            # the consumer), so every source cell takes its gradient from ONE of the ranks that received it
+            first: dict = {}
+            for c in copies:
+                k = (c.src_rank, c.src_off, c.rows, c.row_elems)
+                first[k] = min(first.get(k, c.dst_rank), c.dst_rank)
+            active = {id(c): first[(c.src_rank, c.src_off, c.rows, c.row_elems)] == c.dst_rank for c in copies}
+            cache[key] = ([(c.dst_rank, c) for c in copies if c.src_rank == rank],
+                          [(c.src_rank, c) for c in copies if c.dst_rank == rank],
+                          {(c.src_rank, c.dst_rank, c.src_off, c.dst_off) for c in copies if active[id(c)]})
+        return cache[key][0], cache[key][1]
+
+    def _bwd_active(self, op, sid, c) -> bool:
+        if c is None:
+            return True
+        key = (op.id, sid, tuple(op.inputs[0].global_shape))
+        return (c.src_rank, c.dst_rank, c.src_off, c.dst_off) in self.const_cache["_pieces"][key][2]
+
+    @staticmethod
+    def _rect(t2, c, side):
+        off, ld = (c.src_off, c.src_ld) if side == "src" else (c.dst_off, c.dst_ld)
+        flat = t2.reshape(-1)
+        return torch.as_strided(flat, (c.rows, c.row_elems), (ld, 1), flat.storage_offset() + off)
+
+    def _split_for_send(self, op, sid, value, side):
+        """`value` cut into the pieces to send: forward (side='src': pieces of the sent tensor) or backward
+        (side='dst': pieces of the gradient of the received tensor)."""
+        sends, recvs = self._pieces(op, sid)
+        items = sends if side == "src" else [it for it in recvs if self._bwd_active(op, sid, it[1])]
+        out = []
+        for peer, c in items:
+            out.append((value if c is None else self._rect(value.contiguous(), c, side).contiguous(), peer))
+        return out
+
+    def _recv_specs(self, op, sid, side):
+        """Receive buffers: forward (side='dst') pieces of the received tensor, backward (side='src') pieces of the
+        gradient of the sent tensor."""
+        sends, recvs = self._pieces(op, sid)
+        t = op.outputs[0] if side == "dst" else op.inputs[0]
+        dt, dev = self._act_dtype(t), self.mesh.torch_device
+        items = recvs if side == "dst" else [it for it in sends if self._bwd_active(op, sid, it[1])]
+        return [((t.local_shape(sid) if c is None else (c.rows, c.row_elems)), dt, dev, peer) for peer, c in items]
+
+    def _assemble(self, op, sid, pieces, side):
+        """Received pieces -> local tensor (forward: copy into place; backward: sum, several receivers may hold
+        receiver is asked per cell, distinct cells add up)."""
+        sends, recvs = self._pieces(op, sid)
+        items = recvs if side == "dst" else [it for it in sends if self._bwd_active(op, sid, it[1])]
+        t = op.outputs[0] if side == "dst" else op.inputs[0]
+        if len(items) == 1 and items[0][1] is None:
+            return pieces[0]
+        out = torch.zeros(t.local_shape(sid), dtype=self._act_dtype(t), device=self.mesh.torch_device)
+        for (peer, c), piece in zip(items, pieces):
+            dst = self._rect(out, c, side)
+            if side == "dst":
+                dst.copy_(piece)
+            else:
+                dst.add_(piece)
+        return out
 
     # ---- values -----------------------------------------------------------------------------------------
     def _const_value(self, t: Tensor, sid: int):
@@ -450,26 +551,29 @@ class Executor:
         pending_sends: list = []
         dev = self.mesh.torch_device
 
-        def recv_specs_fwd():
-            out = []
-            for op in plan.recv_ops:
-                t = op.outputs[0]
-                out.append((t.local_shape(sid), self._act_dtype(t), dev, plan.comm[op.id].src_peer))
-            return out
+        def recv_specs(ops, side):
+            out, counts = [], []
+            for op in ops:
+                sp = self._recv_specs(op, sid, side)
+                out += sp
+                counts.append(len(sp))
+            return out, counts
 
-        def recv_specs_bwd():
-            out = []
-            for op in plan.send_ops:
-                t = op.inputs[0]
-                out.append((t.local_shape(sid), self._act_dtype(t), dev, plan.comm[op.id].dst_peer))
-            return out
+        def gather(ops, counts, flat, side):
+            vals, o = [], 0
+            for op, n in zip(ops, counts):
+                vals.append(self._assemble(op, sid, flat[o:o + n], side))
+                o += n
+            return vals
 
         hook = getattr(self.graph, "micro_batch_hook", None)
         for is_fwd, mb in tasks:
             if hook is not None:
                 hook(mb)             # lets the application set symbolic shapes of a ragged micro-batch
             if is_fwd:
-                recvd = PC.p2p_exchange(pending_sends, recv_specs_fwd()) if (pending_sends or plan.recv_ops) else []
+                specs, counts = recv_specs(plan.recv_ops, "dst")
+                flat = PC.p2p_exchange(pending_sends, specs) if (pending_sends or specs) else []
+                recvd = gather(plan.recv_ops, counts, flat, "dst")
                 pending_sends = []
                 recv_vals = {}
                 for op, v in zip(plan.recv_ops, recvd):
@@ -479,7 +583,7 @@ class Executor:
                     values = self._forward(rt, plan, feeds[mb], params, recv_vals)
                 live[mb] = {"recv": recv_vals, "send": [values[op.inputs[0].id] for op in plan.send_ops]}
                 for op, v in zip(plan.send_ops, live[mb]["send"]):
-                    pending_sends.append((v.detach(), plan.comm[op.id].dst_peer))
+                    pending_sends += self._split_for_send(op, sid, v.detach(), "src")
                 if loss_t is not None and loss_t.id in values:
                     losses[mb] = values[loss_t.id]
                 for fid in fetched:
@@ -490,7 +594,9 @@ class Executor:
             else:
                 if not wants_train:
                     continue
-                grads_in = PC.p2p_exchange(pending_sends, recv_specs_bwd()) if (pending_sends or plan.send_ops) else []
+                specs, counts = recv_specs(plan.send_ops, "src")
+                flat = PC.p2p_exchange(pending_sends, specs) if (pending_sends or specs) else []
+                grads_in = gather(plan.send_ops, counts, flat, "src")
                 pending_sends = []
                 st = live.pop(mb)
                 roots, root_grads = [], []
@@ -500,13 +606,13 @@ class Executor:
                 for v, gin in zip(st["send"], grads_in):
                     if v.requires_grad:
                         roots.append(v)
-                        root_grads.append(gin.to(v.dtype))
+                        root_grads.append(gin.to(v.dtype).reshape(v.shape))
                 if roots:
                     torch.autograd.backward(roots, root_grads)
                 for op in plan.recv_ops:
                     v = st["recv"][op.outputs[0].id]
                     gsend = v.grad if v.grad is not None else torch.zeros_like(v)
-                    pending_sends.append((gsend, plan.comm[op.id].src_peer))
+                    pending_sends += self._split_for_send(op, sid, gsend, "dst")
                 self._fold_autograd_grads(params)
         if pending_sends:
             PC.p2p_exchange(pending_sends, [])

@@ -44,3 +44,11 @@ def test_hot_switch_three_strategies():
     strategies = [[1, 2, 2, False], [4, 1, 1, False], [2, 2, 1, True]]
     plan = [[0, "alloc", 256, 2], [1, "grad", 64, 8], [2, "grad", 128, 4], [0, "update", 256, 2]]
     run_workers(4, strategies, plan)
+
+
+def test_activation_repartition_between_groups_with_different_layouts():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "repartition_worker.py")]
+    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
+    assert proc.returncode == 0, proc.stdout[-3000:]

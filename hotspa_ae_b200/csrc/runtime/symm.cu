@@ -114,7 +114,8 @@ reshard_kernel(const HsbReshardDesc* __restrict__ descs, const int32_t* __restri
 // ---------------------------------------------------------------------------------------------
 // data-parallel gradient reduce (+ Adam + bf16 all-gather)
 // ---------------------------------------------------------------------------------------------
-constexpr int DPR_THREADS = 512;
+constexpr int DPR_THREADS = 256;
+constexpr int DPR_UNROLL = 4;      // independent 16-byte vectors per thread: bytes in flight per peer load round
 
 // MODE 0: out = scale * sum;  MODE 1: every member's gradient chunk = scale * sum (all-reduce);
 // MODE 2: Adam on the owner's shard, bf16 result written to every member's parameter range.
@@ -126,59 +127,68 @@ dp_reduce_kernel(PeerPtrs grads, PeerPtrs params, int n, int my_pos, int64_t chu
   const int64_t base = static_cast<int64_t>(my_pos) * chunk;
   const int64_t nvec = chunk >> 2;
   const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(DPR_THREADS) + threadIdx.x; i < nvec;
-       i += static_cast<int64_t>(gridDim.x) * DPR_THREADS) {
-    const int64_t e = base + (i << 2);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint4 part[SYMM_MAX_RANKS];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * DPR_THREADS;
+  for (int64_t i0 = blockIdx.x * static_cast<int64_t>(DPR_THREADS) + threadIdx.x; i0 < nvec; i0 += stride * DPR_UNROLL) {
+    float4 acc[DPR_UNROLL];
+    bool on[DPR_UNROLL];
 #pragma unroll
-    for (int r = 0; r < SYMM_MAX_RANKS; ++r)
-      if (r < n) part[r] = ld_peer_v4(reinterpret_cast<const float*>(grads.p[r]) + e);
+    for (int u = 0; u < DPR_UNROLL; ++u) {
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      on[u] = i0 + u * stride < nvec;
+    }
+#pragma unroll 2
+    for (int r = 0; r < n; ++r) {
+      const float* gsrc = reinterpret_cast<const float*>(grads.p[r]) + base;
+      uint4 part[DPR_UNROLL];
 #pragma unroll
-    for (int r = 0; r < SYMM_MAX_RANKS; ++r)
-      if (r < n) {
-        acc.x += __uint_as_float(part[r].x); acc.y += __uint_as_float(part[r].y);
-        acc.z += __uint_as_float(part[r].z); acc.w += __uint_as_float(part[r].w);
-      }
-    acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
-    if (MODE == 0) {
-      reinterpret_cast<float4*>(out)[i] = acc;
-    } else if (MODE == 1) {
-      uint4 o = make_uint4(__float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z),
-                           __float_as_uint(acc.w));
+      for (int u = 0; u < DPR_UNROLL; ++u)
+        if (on[u]) part[u] = ld_peer_v4(gsrc + ((i0 + u * stride) << 2));
 #pragma unroll
-      for (int r = 0; r < SYMM_MAX_RANKS; ++r)
-        if (r < n) st_peer_v4(reinterpret_cast<float*>(grads.p[r]) + e, o);
-    } else {
-      float4 p = reinterpret_cast<float4*>(master)[i];
-      float4 mm = reinterpret_cast<float4*>(m)[i];
-      float4 vv = reinterpret_cast<float4*>(v)[i];
-      float* pp = reinterpret_cast<float*>(&p);
-      float* pm = reinterpret_cast<float*>(&mm);
-      float* pv = reinterpret_cast<float*>(&vv);
-      const float* g = reinterpret_cast<const float*>(&acc);
+      for (int u = 0; u < DPR_UNROLL; ++u)
+        if (on[u]) {
+          acc[u].x += __uint_as_float(part[u].x); acc[u].y += __uint_as_float(part[u].y);
+          acc[u].z += __uint_as_float(part[u].z); acc[u].w += __uint_as_float(part[u].w);
+        }
+    }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        pm[k] = b1 * pm[k] + (1.f - b1) * g[k];
-        pv[k] = b2 * pv[k] + (1.f - b2) * g[k] * g[k];
-        float upd = (pm[k] * inv_bc1) / (sqrtf(pv[k] * inv_bc2) + eps);
-        if (wd != 0.f) upd += wd * pp[k];
-        pp[k] -= lr * upd;
-      }
-      reinterpret_cast<float4*>(master)[i] = p;
-      reinterpret_cast<float4*>(m)[i] = mm;
-      reinterpret_cast<float4*>(v)[i] = vv;
-      uint2 o;
-      o.x = pack_bf16x2(pp[0], pp[1]);
-      o.y = pack_bf16x2(pp[2], pp[3]);
+    for (int u = 0; u < DPR_UNROLL; ++u) {
+      if (!on[u]) continue;
+      const int64_t i = i0 + u * stride;
+      const int64_t e = base + (i << 2);
+      float4 a = acc[u];
+      a.x *= gscale; a.y *= gscale; a.z *= gscale; a.w *= gscale;
+      if (MODE == 0) {
+        reinterpret_cast<float4*>(out)[i] = a;
+      } else if (MODE == 1) {
+        const uint4 o = make_uint4(__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w));
+        for (int r = 0; r < n; ++r) st_peer_v4(reinterpret_cast<float*>(grads.p[r]) + e, o);
+      } else {
+        float4 p = reinterpret_cast<float4*>(master)[i];
+        float4 mm = reinterpret_cast<float4*>(m)[i];
+        float4 vv = reinterpret_cast<float4*>(v)[i];
+        float* pp = reinterpret_cast<float*>(&p);
+        float* pm = reinterpret_cast<float*>(&mm);
+        float* pv = reinterpret_cast<float*>(&vv);
+        const float* g = reinterpret_cast<const float*>(&a);
 #pragma unroll
-      for (int r = 0; r < SYMM_MAX_RANKS; ++r)
-        if (r < n) {
+        for (int k = 0; k < 4; ++k) {
+          pm[k] = b1 * pm[k] + (1.f - b1) * g[k];
+          pv[k] = b2 * pv[k] + (1.f - b2) * g[k] * g[k];
+          float upd = (pm[k] * inv_bc1) / (sqrtf(pv[k] * inv_bc2) + eps);
+          if (wd != 0.f) upd += wd * pp[k];
+          pp[k] -= lr * upd;
+        }
+        reinterpret_cast<float4*>(master)[i] = p;
+        reinterpret_cast<float4*>(m)[i] = mm;
+        reinterpret_cast<float4*>(v)[i] = vv;
+        uint2 o;
+        o.x = pack_bf16x2(pp[0], pp[1]);
+        o.y = pack_bf16x2(pp[2], pp[3]);
+        for (int r = 0; r < n; ++r) {
           __nv_bfloat16* dstp = reinterpret_cast<__nv_bfloat16*>(params.p[r]) + e;
           asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dstp), "r"(o.x), "r"(o.y) : "memory");
         }
-      // the owner's gradient chunk starts the next step at zero
-      reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[my_pos]) + base)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
   }
 }
@@ -252,8 +262,8 @@ extern "C" int hsb_reshard(const HsbReshardDesc* descs, const int32_t* unit_pref
 }
 
 static int dp_grid(int64_t chunk) {
-  const int64_t blocks = ((chunk >> 2) + DPR_THREADS - 1) / DPR_THREADS;
-  return static_cast<int>(blocks < 148 * 4 ? (blocks < 1 ? 1 : blocks) : 148 * 4);
+  const int64_t blocks = ((chunk >> 2) + DPR_THREADS * DPR_UNROLL - 1) / (DPR_THREADS * DPR_UNROLL);
+  return static_cast<int>(blocks < 148 * 8 ? (blocks < 1 ? 1 : blocks) : 148 * 8);
 }
 
 extern "C" int hsb_dp_reduce_adam(void* const* grads, void* const* params, int n, int my_pos, int64_t chunk,

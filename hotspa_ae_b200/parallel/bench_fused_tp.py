@@ -49,7 +49,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=11008)
-    ap.add_argument("--only", default="", help="ag or rs: run only that kernel, fused only (profiling runs)")
+    ap.add_argument("--only", default="", help="ag, rs or dp: run only that kernel")
+    ap.add_argument("--dp_elems", type=int, default=1 << 30, help="parameters in the data-parallel reduce benchmark")
     args = ap.parse_args()
     mesh = M.init_comm_group(8)
     world, rank = mesh.world_size, mesh.rank
@@ -100,6 +101,37 @@ def main():
                 ms_g = timed(lambda: gemm(x, w, b_mn=True), args.iters)
                 line += f" | GEMM + NCCL reduce-scatter {ms_b * 1e3:8.1f} us | GEMM alone {ms_g * 1e3:8.1f} us"
             lines.append(line)
+    if args.only in ("", "dp"):
+        # gradient reduce-scatter + Adam + bf16 parameter all-gather over peer memory vs NCCL + the plain Adam kernel
+        from ..optim.optimizer import AdamOptimizer
+        from . import symm
+        heap = symm.heap()
+        n = (args.dp_elems // (world * 256)) * world * 256
+        chunk = n // world
+        garena, parena = heap.alloc(n, torch.float32), heap.alloc(n, torch.bfloat16)
+        master, m_, v_ = (torch.zeros(chunk, device=dev) for _ in range(3))
+        garena.normal_()
+        opt = AdamOptimizer(lr=1e-4)
+
+        def fused():
+            heap.barrier()
+            heap.dp_reduce_adam(ranks, garena, parena, 0, chunk, master, m_, v_, opt, 1, 1.0)
+            heap.barrier()
+
+        def base():
+            own = garena[rank * chunk:(rank + 1) * chunk]
+            dist.reduce_scatter_tensor(own, garena)
+            opt.apply_flat(master, m_, v_, own, parena[rank * chunk:(rank + 1) * chunk], 1, 1.0)
+            dist.all_gather_into_tensor(parena, parena[rank * chunk:(rank + 1) * chunk].clone())
+
+        ms_f, ms_b = timed(fused, args.iters), timed(base, args.iters)
+        nv_in = (world - 1) * chunk * 4               # gradient chunks pulled from the peers
+        nv_out = (world - 1) * chunk * 2              # bf16 parameters pushed to the peers
+        hbm = chunk * (4 + 4 * 6 + 2)                 # own gradient chunk, master/m/v read+write, bf16 write
+        roof = max(max(nv_in, nv_out) / (NVLINK_GBS * 1e6), hbm / (pk["gbs"] * 1e6))
+        lines.append(f"grad reduce-scatter + Adam + all-gather, {n / 1e6:.0f} M params, dp={world}: fused {ms_f:8.2f} ms "
+                     f"({roof / ms_f:.2f} of roofline {roof:.2f} ms; {nv_in / ms_f / 1e6:.0f} GB/s pulled per GPU) | "
+                     f"NCCL reduce-scatter + Adam + NCCL all-gather {ms_b:8.2f} ms")
     torch.cuda.synchronize()
     _lib.check_status()
     if rank == 0:

@@ -32,16 +32,32 @@ if ROOT not in sys.path:
 
 TOKENS_PER_GPU = 32768
 
-# per world size, Llama-7B: bucket bounds; (dp, tp, pp, zero) per bucket, longest bucket first; the strategies
+# per model and world size: bucket bounds; (dp, tp, pp, zero) per bucket, longest bucket first; the strategies
 # that recompute their blocks in backward (keeping the activations of a 12K-token micro-batch of the 7B model
 # took > 100 GB next to the arenas of three strategies and ran out of memory on 8 GPUs, so all of them recompute);
 # token budget of a micro-batch per strategy
 PLANS = {
-    1: ((32768, 0), [(1, 1, 1, False)], [0], [32768]),
-    2: ((32768, 4096, 0), [(1, 2, 1, False), (2, 1, 1, True)], [0, 1], [32768, 32768]),
-    4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)], [0, 1, 2], [32768, 32768, 32768]),
-    8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)], [0, 1, 2], [16384, 16384, 32768]),
+    "7b": {
+        1: ((32768, 0), [(1, 1, 1, False)], [0], [32768]),
+        2: ((32768, 4096, 0), [(1, 2, 1, False), (2, 1, 1, True)], [0, 1], [32768, 32768]),
+        4: ((32768, 16384, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True), (4, 1, 1, True)], [0, 1, 2],
+            [32768, 32768, 32768]),
+        8: ((32768, 16384, 4096, 0), [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)], [0, 1, 2],
+            [16384, 16384, 32768]),
+    },
+    # 13B: 16 bytes of state per parameter do not fit one GPU; tp8 / tp4pp2 for the long buckets, dp4tp2 for the short
+    "13b": {
+        2: ((32768, 0), [(1, 2, 1, False)], [0], [32768]),
+        4: ((32768, 4096, 0), [(1, 4, 1, False), (2, 2, 1, True)], [0, 1], [32768, 32768]),
+        8: ((32768, 16384, 4096, 0), [(1, 8, 1, False), (1, 4, 2, False), (4, 2, 1, True)], [0, 1, 2],
+            [32768, 16384, 32768]),
+    },
+    # 32B-class (60 layers, hidden 6656, 52 heads): tp8 for the 32K bucket, tp4pp2 for the rest
+    "32b": {
+        8: ((32768, 16384, 0), [(1, 8, 1, False), (1, 4, 2, False)], [0, 1], [32768, 16384]),
+    },
 }
+TOKENS_PER_GPU_BY_MODEL = {"7b": 32768, "13b": 32768, "32b": 16384}
 
 REFERENCE_UNAVAILABLE = (
     "reference is not pip-installable (no setup.py/pyproject.toml; its CMake build needs MPI, the missing "
@@ -55,7 +71,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="7b")
-    ap.add_argument("--tokens_per_gpu", type=int, default=TOKENS_PER_GPU)
+    ap.add_argument("--tokens_per_gpu", type=int, default=0)
     ap.add_argument("--switch_mode", default="auto")
     ap.add_argument("--mb_tokens", type=int, default=0, help="override the token budget of a micro-batch")
     ap.add_argument("--no_e2e", action="store_true", help="skip the end-to-end region (profiling runs)")
@@ -132,7 +148,10 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a GPU")
-    bounds, strategies, recompute, mb_tokens = PLANS[world]
+    if args.model not in PLANS or world not in PLANS[args.model]:
+        raise SystemExit(f"no plan for model {args.model} on {world} GPUs (available: "
+                         f"{ {m: sorted(v) for m, v in PLANS.items()} })")
+    bounds, strategies, recompute, mb_tokens = PLANS[args.model][world]
     overrides = {"vocab_size": 32000}
     if args.layers:
         overrides["num_layers"] = args.layers
@@ -142,7 +161,7 @@ def main():
     trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=recompute,
                                switch_mode=args.switch_mode, micro_batch_tokens=mb_tokens, **overrides)
     vocab = trainer.config.vocab_size
-    tokens = args.tokens_per_gpu * world
+    tokens = (args.tokens_per_gpu or TOKENS_PER_GPU_BY_MODEL[args.model]) * world
     K, W = args.steps, args.warmup
 
     def batch(i):
@@ -233,7 +252,7 @@ def main():
     if rank == 0:
         par = "+".join(f"dp{dp}tp{tp}pp{pp}" + ("z" if z else "") for dp, tp, pp, z in strategies)
         out = {
-            "metric": "Llama-7B varlen hot-switch training throughput", "value": tok_a / (ms_a / 1e3),
+            "metric": f"Llama-{args.model.upper()} varlen hot-switch training throughput", "value": tok_a / (ms_a / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_a / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (lognormal lengths median 800 clipped at 32K, uniform token ids, random-init weights)",

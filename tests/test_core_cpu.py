@@ -1,0 +1,154 @@
+"""Host core (C++): distributed-states algebra, comm classification, reshard planner, schedules, symbols."""
+import itertools
+
+import numpy as np
+import pytest
+
+from hotspa_ae_b200 import core as C
+
+DS = C.DistributedStates
+K = C._C
+
+
+def test_ds_states_order_and_index_maps():
+    ds = DS(8, {0: 2, 1: 2, -1: 2}, [-1, 0, 1])             # weights: dup slow, splits fast
+    assert ds.device_num == 8 and ds.get_dim(0) == 2 and ds.get_dim(1) == 2 and ds.get_dim(-1) == 2
+    assert ds.get_dim(-2) == 1 and not ds.is_pure_duplicate
+    # digits are peeled from the last order entry: device 5 = (dup 1, dim0 0, dim1 1)
+    assert dict(ds.map_device_to_state_index(5)) == {-1: 1, 0: 0, 1: 1}
+    # duplicate-group index counts only the non-negative dims
+    assert [ds.get_dup_group_index(i) for i in range(8)] == [0, 1, 2, 3, 0, 1, 2, 3]
+    # devices that differ only in the dup digit
+    assert list(ds.get_devices_by_dim(-1, 1, list(range(8)))) == [1, 5]
+    assert list(ds.get_devices_by_dim(1, 6, list(range(8)))) == [6, 7]
+    with pytest.raises(Exception):
+        DS(8, {0: 3}, [0])                                    # product must equal device_num
+    assert DS(4, {-1: 4}, [-1]).is_pure_duplicate
+
+
+@pytest.mark.parametrize("shape,states,order", [([16, 12], {0: 2, 1: 2, -1: 2}, [-1, 0, 1]),
+                                                ([24, 8], {0: 4, -1: 2}, [0, -1]),
+                                                ([8, 8], {1: 8}, [1])])
+def test_local_slices_tile_the_tensor_once_per_replica(shape, states, order):
+    n = int(np.prod(list(states.values())))
+    ds = DS(n, states, order)
+    cover = np.zeros(shape, dtype=np.int32)
+    for dev in range(n):
+        sl = ds.local_slice(shape, dev)
+        assert [s for _, s in sl] == list(ds.local_shape(shape))
+        cover[tuple(slice(o, o + s) for o, s in sl)] += 1
+    assert (cover == states.get(-1, 1)).all()
+
+
+def test_collective_pattern_checks_and_classification():
+    ranks = [0, 1, 2, 3]
+    partial = DS(4, {-2: 2, 0: 2}, [0, -2])
+    dup = DS(4, {-1: 2, 0: 2}, [0, -1])
+    split0 = DS(4, {0: 4}, [0])
+    assert partial.check_allreduce(dup) and partial.check_reducescatter(split0) and split0.check_allgather(dup)
+    U = C.DistributedStatesUnion
+    name = lambda a, b, g2=ranks: C.comm_type_name(C.classify_comm(U([a]), ranks, U([b]), g2, 0))  # noqa: E731
+    assert name(partial, dup) == C.comm_type_name(K.COMM_ALL_REDUCE)
+    assert name(partial, split0) == C.comm_type_name(K.COMM_REDUCE_SCATTER)
+    assert name(split0, dup) == C.comm_type_name(K.COMM_ALL_GATHER)
+    assert name(dup, dup) == C.comm_type_name(K.COMM_UNUSED)
+    assert name(dup, dup, [4, 5, 6, 7]) == C.comm_type_name(K.COMM_P2P)
+    assert name(split0, dup, [4, 5, 6, 7]) == C.comm_type_name(K.COMM_BATCHED_SEND_RECV)
+
+
+def test_linear_ds_deduction_column_and_row_parallel():
+    x_dup = DS(4, {0: 2, -1: 2}, [0, -1])                     # activations: dp 2, replicated over tp 2
+    w_col = DS(4, {-1: 2, 0: 2}, [-1, 0])                     # W [out, in] split on out
+    y = C.deduce_linear(x_dup, w_col, False, True)
+    assert y.get_dim(0) == 2 and y.get_dim(1) == 2 and y.get_dim(-2) == 1
+    x_split = DS(4, {0: 2, 1: 2}, [0, 1])                     # activations split on features
+    w_row = DS(4, {-1: 2, 0: 2}, [-1, 0])                     # W [in, out] split on in
+    y2 = C.deduce_linear(x_split, w_row, False, False)
+    assert y2.get_dim(-2) == 2 and y2.get_dim(0) == 2         # partial over tp
+
+
+def _layouts(shape, dp, tp, pp, world):
+    """Column-parallel weight of stage 0 under (dp, tp, pp): ranks of the first stage, dup dp x split0 tp."""
+    width = world // pp
+    ds = DS(width, {-1: dp, 0: tp}, [-1, 0]) if dp * tp > 1 else DS(1, {-1: 1}, [-1])
+    return ds, list(range(width))
+
+
+@pytest.mark.parametrize("src,dst", list(itertools.permutations([(8, 1, 1), (2, 2, 2), (1, 4, 2), (4, 2, 1)], 2)))
+def test_reshard_plan_properties(src, dst):
+    shape, world = [64, 32], 8
+    s_ds, s_ranks = _layouts(shape, *src, world)
+    d_ds, d_ranks = _layouts(shape, *dst, world)
+    s_regs = C.regions_of(shape, s_ds, s_ranks, -1)
+    d_regs = C.regions_of(shape, d_ds, d_ranks, -1)
+    pl = C.ReshardPlanner(world, K.SENDER_BALANCED)
+    pl.add_tensor_regions(0, s_regs, d_regs, False)
+    # execute the plan on numpy shards: every destination shard must come out complete
+    full = np.arange(shape[0] * shape[1], dtype=np.float32).reshape(shape)
+    src_sh = {r: full[r0:r1, c0:c1].copy() for r, r0, r1, c0, c1 in s_regs}
+    dst_sh = {r: np.full((r1 - r0, c1 - c0), -1, np.float32) for r, r0, r1, c0, c1 in d_regs}
+    sent = recv = 0
+    for c in pl.copies():
+        s = src_sh[c.src_rank].reshape(-1)
+        d = dst_sh[c.dst_rank].reshape(-1)
+        for row in range(c.rows):
+            d[c.dst_off + row * c.dst_ld:c.dst_off + row * c.dst_ld + c.row_elems] = \
+                s[c.src_off + row * c.src_ld:c.src_off + row * c.src_ld + c.row_elems]
+        if c.src_rank != c.dst_rank:
+            sent += c.rows * c.row_elems
+            recv += c.rows * c.row_elems
+    for r, r0, r1, c0, c1 in d_regs:
+        np.testing.assert_array_equal(dst_sh[r], full[r0:r1, c0:c1])
+    st = pl.stats
+    assert sum(st.sent_elems) == sum(st.recv_elems) == sent == st.remote_elems
+    # a rank never fetches remotely what it already holds
+    if src == dst:
+        assert st.remote_elems == 0
+
+
+def test_gradient_plan_gathers_every_replica():
+    shape, world = [32, 16], 4
+    s_ds = DS(4, {-1: 4}, [-1])                               # dp4: four replicas hold partial sums of the whole tensor
+    d_ds = DS(4, {0: 4}, [0])                                 # home: split in four
+    s_regs = C.regions_of(shape, s_ds, [0, 1, 2, 3], -1)
+    d_regs = C.regions_of(shape, d_ds, [0, 1, 2, 3], 0)
+    pl = C.ReshardPlanner(world, K.SENDER_BALANCED)
+    pl.add_tensor_regions(0, s_regs, d_regs, True)
+    per_dst = {}
+    for c in pl.copies():
+        per_dst.setdefault(c.dst_rank, set()).add(c.src_rank)
+    assert all(v == {0, 1, 2, 3} for v in per_dst.values()) and len(per_dst) == 4
+
+
+def test_pipeline_schedules():
+    for stages, nmb in [(2, 4), (4, 8), (4, 2), (1, 3)]:
+        for s in range(stages):
+            t = C.schedule_1f1b(stages, s, nmb)
+            fw = [m for f, m in t if f]
+            bw = [m for f, m in t if not f]
+            assert fw == list(range(nmb)) and bw == list(range(nmb))
+            # a backward never precedes its forward, and at most (stages - s) micro-batches are in flight
+            live = peak = 0
+            for f, m in t:
+                live += 1 if f else -1
+                peak = max(peak, live)
+                assert live >= 0
+            assert peak <= min(nmb, stages - s)
+            g = C.schedule_gpipe(stages, s, nmb)
+            assert [m for f, m in g if f] == list(range(nmb)) and all(f for f, _ in g[:nmb])
+
+
+def test_symbols_packer_and_arena():
+    a, b = C.IntSymbol(6), C.IntSymbol(4)
+    c = a * b + a / C.IntSymbol(2) - b % C.IntSymbol(3)
+    assert c.data == 24 + 3 - 1
+    a.set_data(10)
+    assert c.data == 40 + 5 - 1                               # lazy: follows its leaves
+    buckets = C.bucket_and_pack([5, 9, 2, 7, 3, 12], [12, 6, 0], 0, False)
+    assert sorted(i for bk in buckets for i in bk.members) == list(range(6))
+    assert all(sum([5, 9, 2, 7, 3, 12][i] for i in row) <= bk.max_len for bk in buckets for row in bk.rows)
+    assign = C.balance_rows([10, 9, 8, 1, 1, 1], 2)
+    loads = [sum([10, 9, 8, 1, 1, 1][i] for i in a) for a in assign]
+    assert abs(loads[0] - loads[1]) <= 4 and sum(loads) == 30          # longest-processing-time-first
+    offs, total = C.plan_arena([10, 300, 5], 256)
+    assert offs == [0, 256, 768] and total == 1024

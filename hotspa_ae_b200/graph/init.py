@@ -91,3 +91,7 @@ def he_uniform_initializer(gain=2.0): return GeneralizedXavierInitializer(gain, 
 def lecun_normal_initializer(gain=1.0): return GeneralizedXavierInitializer(gain, "fan_in", "normal")
 def lecun_uniform_initializer(gain=1.0): return GeneralizedXavierInitializer(gain, "fan_in", "uniform")
 def provided_initializer(data): return ProvidedInitializer(data)
+
+
+__all__ = sorted(n for n, v in list(globals().items())
+                 if not n.startswith("_") and callable(v) and getattr(v, "__module__", None) == __name__)

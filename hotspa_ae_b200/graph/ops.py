@@ -887,3 +887,9 @@ def ones_like(x, name=None):
 
 def zeros_like(x, name=None):
     return mul(x, 0.0)
+
+
+# public names: the op front-ends defined in this module (not the modules and typing helpers it imports)
+__all__ = sorted(n for n, v in list(globals().items())
+                 if not n.startswith("_") and callable(v) and getattr(v, "__module__", None) == __name__
+                 and n not in ("register", "make_op_front"))

@@ -11,6 +11,8 @@ pipedream-flush schedule, run levels) and define_and_run_graph.cc (plan cache, h
 """
 from __future__ import annotations
 
+import json
+import os
 import time
 from dataclasses import dataclass, field
 
@@ -142,6 +144,8 @@ class Executor:
         self.stats: dict = {"runs": 0}
         self.pipeline_schedule = "1f1b"
         self.fuse_tp_comm = True      # run tensor-parallel comm+linear pairs as one fused kernel on GPUs
+        self.profile_ops = bool(os.environ.get("HETU_STRAGGLER"))   # CUDA events around every forward op
+        self._op_events: list = []
 
     def configure_switch(self, mode: str):
         """'nccl': pack -> grouped send/recv -> unpack.  'fused': one pull kernel over peer-mapped arenas
@@ -474,11 +478,46 @@ class Executor:
         raise RuntimeError(f"{t} has no value on rank {self.mesh.rank} (strategy {sid})")
 
     def _run_ops(self, rt, ops, values, feeds, params, sid):
+        timing = self.profile_ops and self.mesh.torch_device.type == "cuda"
         for op in ops:
             ins = [self._value(t, values, feeds, params, sid) for t in op.inputs]
+            if timing:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
             outs = O.REGISTRY[op.type].compute(rt, op, ins)
+            if timing:
+                e1.record()
+                self._op_events.append((op, e0, e1))
             for t, v in zip(op.outputs, outs):
                 values[t.id] = v
+
+    def op_time_report(self, top: int = 12) -> dict:
+        """Forward device time per op type and per category (compute / tensor-parallel collective / other) of the
+        runs since the last report, from CUDA events around every op (``profile_ops`` or ``HETU_STRAGGLER``).
+        Backward ops run inside autograd and are reported by the caller as the remainder of the step.
+        Reference: the HETU_STRAGGLER analysis of hetu/graph/executable_graph.cc:2085-2260."""
+        if not self._op_events:
+            return {}
+        torch.cuda.synchronize()
+        by_type, by_cat = {}, {"compute": 0.0, "tp_collective": 0.0, "fused_compute_collective": 0.0}
+        for op, e0, e1 in self._op_events:
+            ms = e0.elapsed_time(e1)
+            by_type[op.type] = by_type.get(op.type, 0.0) + ms
+            plan = next((p for p in self.plans.values() if op.id in p.comm or op.id in p.fused_linear), None)
+            if op.type == "comm":
+                by_cat["tp_collective"] += ms
+            elif plan is not None and op.id in plan.fused_linear:
+                by_cat["fused_compute_collective"] += ms
+            else:
+                by_cat["compute"] += ms
+        self._op_events.clear()
+        rows = sorted(by_type.items(), key=lambda kv: -kv[1])[:top]
+        rep = {"forward_ms_by_op": dict(rows), "forward_ms_by_category": by_cat}
+        path = os.environ.get("HETU_STRAGGLER_LOG_FILE")
+        if path:
+            with open(path, "a") as f:
+                f.write(json.dumps(rep) + "\n")
+        return rep
 
     def _forward(self, rt, plan, feeds, params, recv_vals):
         sid = plan.sid

@@ -74,6 +74,8 @@ def parse():
     ap.add_argument("--tokens_per_gpu", type=int, default=0)
     ap.add_argument("--switch_mode", default="auto")
     ap.add_argument("--mb_tokens", type=int, default=0, help="override the token budget of a micro-batch")
+    ap.add_argument("--mb_tokens_pp", type=int, default=0,
+                    help="override the token budget of a micro-batch for the pipelined strategies only")
     ap.add_argument("--no_e2e", action="store_true", help="skip the end-to-end region (profiling runs)")
     ap.add_argument("--breakdown", action="store_true", help="after the timed regions, run one more step with "
                                                              "per-bucket / per-switch CUDA-event timing (stderr)")
@@ -158,6 +160,8 @@ def main():
     # micro-batches are sized by tokens (documents are independent under varlen attention)
     if args.mb_tokens:
         mb_tokens = [args.mb_tokens] * len(strategies)
+    if args.mb_tokens_pp:
+        mb_tokens = [args.mb_tokens_pp if pp > 1 else m for m, (_, _, pp, _) in zip(mb_tokens, strategies)]
     trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=recompute,
                                switch_mode=args.switch_mode, micro_batch_tokens=mb_tokens, **overrides)
     vocab = trainer.config.vocab_size

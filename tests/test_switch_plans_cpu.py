@@ -1,0 +1,59 @@
+"""Hot-switch plans of the Llama-7B layer shapes for every ordered strategy pair of the 8-GPU benchmark, computed
+on a virtual 8-rank mesh (planner only, no data): conservation, sender balance, and the traffic the design
+expects (nothing moves when the destination already holds the data)."""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import hetu as ht
+from hotspa_ae_b200.models.llama import LlamaLMHeadModel, llama_config
+from hotspa_ae_b200.parallel import mesh as M
+from hotspa_ae_b200.parallel.param_store import ParamStore
+from hotspa_ae_b200.parallel.strategy_config import generate_llama_3d_config, propagate_zero
+
+STRATEGIES = [(1, 4, 2, False), (2, 2, 2, True), (8, 1, 1, True)]
+
+
+def _graph(rank):
+    M.reset_mesh()
+    ht.init_comm_group(8, world_size=8, rank=rank, virtual=True)
+    cfg = llama_config("7b", num_layers=2, vocab_size=32000)
+    cfgs = [propagate_zero(generate_llama_3d_config(2, 8, dp, tp, pp, z)) for dp, tp, pp, z in STRATEGIES]
+    with ht.graph("define_and_run", num_strategy=len(cfgs)) as g:
+        with ht.autocast(torch.bfloat16):
+            LlamaLMHeadModel(cfg, cfgs)
+    return g
+
+
+@pytest.mark.parametrize("src,dst", list(itertools.permutations(range(3), 2)))
+def test_parameter_switch_plans_conserve_and_balance(src, dst):
+    g = _graph(0)
+    store = ParamStore(g)
+    plan = store._plan(src, dst, "param")
+    sent, recv = np.array(plan["sent_elems"]), np.array(plan["recv_elems"])
+    assert sent.sum() == recv.sum() == plan["remote_elems"]
+    total = sum(int(np.prod(p.global_shape)) for p in g.parameters)
+    # every rank ends up with exactly its destination shard: received + local = its layout size (without padding)
+    need = [sum(e.numel for e in store.layout(dst, r).entries.values()) for r in range(8)]
+    got = [0] * 8
+    for c in plan["all"]:
+        got[c.dst_rank] += c.rows * c.row_elems
+    assert got == need
+    if STRATEGIES[src][0] == 8:
+        assert plan["remote_elems"] == 0            # every rank already holds everything under dp8
+    else:
+        busy = sent[sent > 0]
+        assert busy.max() <= 1.6 * busy.mean()      # no sender carries much more than its share
+    assert plan["remote_elems"] <= total * 8
+
+
+def test_gradient_plan_into_home_takes_every_replica_once():
+    g = _graph(0)
+    store = ParamStore(g)
+    plan = store._plan(2, 0, "grad")                # dp8 -> tp4pp2 home: 8 partial sums per cell
+    total = sum(int(np.prod(p.global_shape)) for p in g.parameters)
+    moved = plan["remote_elems"] + plan["local_elems"]
+    # each parameter element is sent by its 8 holders to exactly one home holder
+    assert moved == total * 8

@@ -32,6 +32,7 @@ ReshardPlanner = _C.ReshardPlanner
 NvmlProfiler = _C.NvmlProfiler
 classify_comm = _C.classify_comm
 comm_type_name = _C.comm_type_name
+split_comm_groups = _C.split_comm_groups
 deduce_linear = _C.deduce_linear
 regions_of = _C.regions_of
 schedule_1f1b = _C.schedule_1f1b

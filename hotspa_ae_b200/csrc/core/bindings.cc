@@ -70,6 +70,12 @@ PYBIND11_MODULE(_hsb_core, m) {
   m.def("classify_comm", &classify_comm, py::arg("src"), py::arg("src_group"), py::arg("dst"), py::arg("dst_group"),
         py::arg("member") = 0);
   m.def("comm_type_name", &comm_type_name);
+  py::class_<SplitCommPlan>(m, "SplitCommPlan")
+      .def_readonly("split_dim", &SplitCommPlan::split_dim)
+      .def_readonly("micro_blocks", &SplitCommPlan::micro_blocks)
+      .def_readonly("first_micro_block", &SplitCommPlan::first_micro_block)
+      .def_readonly("groups", &SplitCommPlan::groups);
+  m.def("split_comm_groups", &split_comm_groups, py::arg("local_ds"), py::arg("groups"), py::arg("rank"));
   m.def("deduce_linear", &deduce_linear);
   m.attr("COMM_UNUSED") = static_cast<uint32_t>(COMM_UNUSED);
   m.attr("COMM_P2P") = static_cast<uint32_t>(COMM_P2P);

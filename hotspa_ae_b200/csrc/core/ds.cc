@@ -323,6 +323,73 @@ uint32_t classify_comm(const DistributedStatesUnion& src, const std::vector<int>
   return t;
 }
 
+SplitCommPlan split_comm_groups(const std::vector<DistributedStates>& local_ds,
+                                const std::vector<std::vector<int>>& groups, int rank) {
+  if (local_ds.empty() || local_ds.size() != groups.size())
+    throw std::invalid_argument("split_comm_groups: one device group per union member is required");
+  const size_t members = local_ds.size();
+  SplitCommPlan plan;
+  int split_dim = kNoHeteroDim;
+  int finest = 1;
+  for (size_t j = 0; j < members; ++j) {
+    int found = 0;
+    for (const auto& kv : local_ds[j].states()) {
+      if (kv.second == 1 || kv.first == kDup) continue;
+      if (kv.first == kPartial) throw std::invalid_argument("split_comm_groups: a member's local layout is still partial");
+      if (++found > 1) throw std::invalid_argument("split_comm_groups: members may split a single dimension only");
+      if (split_dim == kNoHeteroDim) split_dim = kv.first;
+      if (split_dim != kv.first) throw std::invalid_argument("split_comm_groups: members split different dimensions");
+      finest = std::max(finest, kv.second);
+    }
+    if (local_ds[j].device_num() != static_cast<int>(groups[j].size()))
+      throw std::invalid_argument("split_comm_groups: layout and device group sizes differ");
+  }
+  if (split_dim == kNoHeteroDim) split_dim = 0;
+  plan.split_dim = split_dim;
+
+  // holders[j][block][dup] = rank
+  std::vector<std::vector<std::vector<int>>> holders(members);
+  int my_member = -1, my_block = 0;
+  for (size_t j = 0; j < members; ++j) {
+    const int sj = local_ds[j].get_dim(split_dim), dj = local_ds[j].get_dim(kDup);
+    if (finest % sj) throw std::invalid_argument("split_comm_groups: split counts must divide the finest one");
+    holders[j].assign(sj, std::vector<int>(dj, -1));
+    for (size_t i = 0; i < groups[j].size(); ++i) {
+      const auto idx = local_ds[j].map_device_to_state_index(static_cast<int>(i));
+      auto at = [&](int d) { auto it = idx.find(d); return it == idx.end() ? 0 : it->second; };
+      holders[j][at(split_dim)][at(kDup)] = groups[j][i];
+      if (groups[j][i] == rank) { my_member = static_cast<int>(j); my_block = at(split_dim); }
+    }
+  }
+  if (my_member < 0) throw std::invalid_argument("split_comm_groups: rank is in no member of the union");
+  const int per_block = finest / local_ds[my_member].get_dim(split_dim);
+  plan.micro_blocks = per_block;
+  plan.first_micro_block = my_block * per_block;
+  for (int m = 0; m < per_block; ++m) {
+    const int mb = plan.first_micro_block + m;
+    size_t widest = 0;
+    std::vector<const std::vector<int>*> who(members);
+    for (size_t j = 0; j < members; ++j) {
+      const int per = finest / local_ds[j].get_dim(split_dim);
+      who[j] = &holders[j][mb / per];
+      widest = std::max(widest, who[j]->size());
+    }
+    std::vector<std::vector<int>> mine;
+    for (size_t k = 0; k < widest; ++k) {
+      std::vector<int> g;
+      bool has_me = false;
+      for (size_t j = 0; j < members; ++j) {
+        const int r = (*who[j])[k % who[j]->size()];
+        g.push_back(r);
+        has_me |= r == rank;
+      }
+      if (has_me) mine.push_back(std::move(g));
+    }
+    plan.groups.push_back(std::move(mine));
+  }
+  return plan;
+}
+
 const char* comm_type_name(uint32_t t) {
   switch (t) {
     case COMM_UNUSED: return "UNUSED";

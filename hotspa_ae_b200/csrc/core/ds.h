@@ -120,6 +120,21 @@ uint32_t classify_comm(const DistributedStatesUnion& src, const std::vector<int>
                        const DistributedStatesUnion& dst, const std::vector<int>& dst_group, size_t member = 0);
 const char* comm_type_name(uint32_t t);
 
+// Communication groups of the heterogeneous ("split") collectives for one rank.
+// Member j of the union lives on ranks `groups[j]` with layout `local_ds[j]`; all members split the tensor on the same
+// single dimension (possibly with different counts) and may duplicate it.  The tensor is cut into F = max split count
+// micro-blocks; this rank holds `micro_blocks` consecutive ones, and for each of them `groups[i]` lists the rank groups
+// (one holder per member, duplicates paired round-robin) this rank takes part in.
+// Reference behaviour: hetu/graph/ops/Communication.cc:248-392.
+struct SplitCommPlan {
+  int split_dim = 0;
+  int micro_blocks = 1;
+  int first_micro_block = 0;
+  std::vector<std::vector<std::vector<int>>> groups;
+};
+SplitCommPlan split_comm_groups(const std::vector<DistributedStates>& local_ds,
+                                const std::vector<std::vector<int>>& groups, int rank);
+
 // DS of `linear(a, b)` given the operand layouts (2-D, after resolving transposes):
 // a is [m, k] with states {0: a_row, 1: a_col}, b is [k, n] with {0: b_row, 1: b_col}; needs a_col == b_row.
 DistributedStates deduce_linear(const DistributedStates& a, const DistributedStates& b, bool trans_a, bool trans_b);

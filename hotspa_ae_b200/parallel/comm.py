@@ -119,6 +119,102 @@ class SplitLocal(torch.autograd.Function):
         return _move(all_gather_dim0(_move(g, ctx.dim).contiguous(), ctx.group), ctx.dim), None, None, None, None
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# Heterogeneous ("split") collectives: the members of a DS union shard the tensor with different counts, so a rank's
+# shard is cut into micro-blocks of the finest granularity and every micro-block runs its collective over the group
+# of its holders, one per member (reference: hetu/graph/ops/Communication.cc:990-1202; group construction :248-392,
+# here `_core.split_comm_groups`).  `groups[i]` is the list of process groups of micro-block i that contain this
+# rank; holders that duplicate a block carry identical data (the local pre-collective ran before), so when a
+# micro-block has several groups the last result stands.
+# ---------------------------------------------------------------------------------------------------------------
+
+def split_collective_groups(local_ds_list, rank_groups, rank=None):
+    """Plan of the split collectives for `rank`: (split_dim, micro_blocks, [[ranks...] per group] per micro-block)."""
+    from .. import core as _core
+    from . import mesh as M
+    rank = M.mesh().rank if rank is None else rank
+    plan = _core.split_comm_groups(list(local_ds_list), [list(g) for g in rank_groups], int(rank))
+    return plan.split_dim, plan.micro_blocks, [[tuple(g) for g in gs] for gs in plan.groups]
+
+
+def ensure_split_groups(local_ds_list, rank_groups):
+    """Create, collectively and in one order on all ranks, every process group any member rank will use."""
+    from . import mesh as M
+    every = set()
+    for g in rank_groups:
+        for r in g:
+            for gs in split_collective_groups(local_ds_list, rank_groups, r)[2]:
+                every.update(gs)
+    M.mesh().ensure_groups(sorted(every))
+
+
+def _resolve(groups):
+    from . import mesh as M
+    return [[M.mesh().group(g) if isinstance(g, (tuple, list)) else g for g in gs] for gs in groups]
+
+
+def _split_apply(x, groups, dim, fn):
+    groups = _resolve(groups)
+    parts = _move(x, dim).contiguous().chunk(len(groups), dim=0)
+    outs = []
+    for part, gs in zip(parts, groups):
+        res = part
+        for g in gs:
+            res = fn(part.contiguous(), g)
+        outs.append(res)
+    return _move(torch.cat(outs, dim=0), dim).contiguous()
+
+
+def split_all_reduce(x, groups, dim=0):
+    return _split_apply(x, groups, dim, all_reduce)
+
+
+def split_all_gather(x, groups, dim=0):
+    return _split_apply(x, groups, dim, all_gather_dim0)
+
+
+def split_reduce_scatter(x, groups, dim=0):
+    return _split_apply(x, groups, dim, reduce_scatter_dim0)
+
+
+class SplitAllReduce(torch.autograd.Function):
+    """partial over the union -> duplicate; micro-block i is summed over groups[i]."""
+
+    @staticmethod
+    def forward(ctx, x, groups, dim):
+        return split_all_reduce(x, groups, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, None
+
+
+class SplitAllGather(torch.autograd.Function):
+    """split over the union -> duplicate; micro-block i grows by the size of its group along `dim`."""
+
+    @staticmethod
+    def forward(ctx, x, groups, dim):
+        ctx.groups, ctx.dim = groups, dim
+        return split_all_gather(x, groups, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return split_reduce_scatter(g, ctx.groups, ctx.dim), None, None
+
+
+class SplitReduceScatter(torch.autograd.Function):
+    """partial over the union -> split; micro-block i is summed and scattered over groups[i] along `dim`."""
+
+    @staticmethod
+    def forward(ctx, x, groups, dim):
+        ctx.groups, ctx.dim = groups, dim
+        return split_reduce_scatter(x, groups, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return split_all_gather(g, ctx.groups, ctx.dim), None, None
+
+
 def combine_ce_stats(stats: torch.Tensor, group) -> torch.Tensor:
     """(max, sum-exp, target) per row of every vocab shard -> global (max, sum-exp, target).
     One small all-gather instead of the reference's three all-reduces

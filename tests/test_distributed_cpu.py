@@ -60,3 +60,11 @@ def test_heterogeneous_split_collectives():
     env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
     assert proc.returncode == 0 and "SPLIT_COMM_OK" in proc.stdout, proc.stdout[-4000:]
+
+
+def test_communication_group_verbs():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "comm_group_worker.py")]
+    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
+    assert proc.returncode == 0 and "COMM_GROUP_OK" in proc.stdout, proc.stdout[-4000:]

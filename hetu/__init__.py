@@ -12,6 +12,7 @@ from hotspa_ae_b200.graph.graph import (Graph, autocast, from_numpy, from_numpy_
 from hotspa_ae_b200.graph.gradscaler import GradScaler  # noqa: F401
 from hotspa_ae_b200.utils.dataset import Dataloader  # noqa: F401
 from hotspa_ae_b200.core.stream import Event, Stream, get_stream  # noqa: F401
+from hotspa_ae_b200.core.ndarray import NDArray, numpy_to_NDArray  # noqa: F401
 from hotspa_ae_b200.utils.random import get_seed_status, set_random_seed, set_seed_status  # noqa: F401
 from hotspa_ae_b200.graph.init import *  # noqa: F401,F403
 from hotspa_ae_b200.graph.ops import *  # noqa: F401,F403

@@ -27,6 +27,7 @@ from ..parallel import comm as PC
 from ..parallel import mesh as M
 from ..parallel.param_store import ParamStore
 from . import ops as O
+from ..core.ndarray import NDArray
 from .graph import ALLOC, GRAD, TOPO, UPDATE
 from .tensor import Tensor
 
@@ -549,7 +550,10 @@ class Executor:
         per_mb = [dict() for _ in range(nmb)]
         dev = self.mesh.torch_device
         for t, arr in feed_dict.items():
+            if isinstance(arr, NDArray):
+                arr = arr.data
             if isinstance(arr, (list, tuple)) and len(arr) == nmb and not isinstance(arr[0], (int, float)):
+                arr = [a.data if isinstance(a, NDArray) else a for a in arr]
                 chunks = [torch.as_tensor(np.asarray(a)) if not torch.is_tensor(a) else a for a in arr]
             else:
                 v = arr if torch.is_tensor(arr) else torch.as_tensor(np.asarray(arr))

@@ -9,6 +9,9 @@ from hotspa_ae_b200.core import (DistributedStates, DistributedStatesUnion, IntS
 from hotspa_ae_b200.graph.graph import (Graph, autocast, from_numpy, from_numpy_parallel, graph,  # noqa: F401
                                         merge_strategy, parallel_parameter, parallel_placeholder, placeholder,
                                         recompute, run_level)
+from hotspa_ae_b200.graph.graph import (delete_graph, get_default_define_and_run_graph,  # noqa: F401
+                                        get_default_define_by_run_graph, get_default_eager_graph, get_graph,
+                                        make_new_define_and_run_graph, make_new_eager_graph)
 from hotspa_ae_b200.graph.gradscaler import GradScaler  # noqa: F401
 from hotspa_ae_b200.utils.dataset import Dataloader  # noqa: F401
 from hotspa_ae_b200.core.stream import Event, Stream, get_stream  # noqa: F401

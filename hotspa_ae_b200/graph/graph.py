@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import contextlib
 import itertools
+import weakref
 from typing import Any
 
 import numpy as np
@@ -34,23 +35,97 @@ def run_level(name: str) -> int:
     return RUN_LEVELS[name]
 
 
+# every live graph, by id and by name (reference: Graph::_global_graphs / _name_to_graphs, hetu/graph/graph.h)
+# (weak: a graph and the arenas behind it go away with their last user; the default graphs are pinned below)
+_graphs_by_id: "weakref.WeakValueDictionary[int, Graph]" = weakref.WeakValueDictionary()
+_pinned: dict[str, "Graph"] = {}
+_graph_ids = itertools.count()
+
+
+def get_graph(key) -> "Graph":
+    """Graph by id (int) or by name (str)."""
+    if isinstance(key, int):
+        return _graphs_by_id[key]
+    for g in list(_graphs_by_id.values()):
+        if g.name == key:
+            return g
+    raise KeyError(f"no graph named {key!r}")
+
+
+def delete_graph(key) -> None:
+    g = key if isinstance(key, Graph) else get_graph(key)
+    _graphs_by_id.pop(g.id, None)
+    _pinned.pop(g.name, None)
+    global _default_graph
+    if _default_graph is g:
+        _default_graph = None
+
+
+def _default_of(kind: str, prefix: str = "default") -> "Graph":
+    name = f"{prefix}_{kind}"
+    try:
+        return get_graph(name)
+    except KeyError:
+        _pinned[name] = Graph(kind, 1, name=name)
+        return _pinned[name]
+
+
+def get_default_define_and_run_graph() -> "Graph":
+    return _default_of("define_and_run")
+
+
+def get_default_define_by_run_graph() -> "Graph":
+    return _default_of("define_by_run")
+
+
+def get_default_eager_graph() -> "Graph":
+    return _default_of("eager")
+
+
+def make_new_define_and_run_graph(name: str | None = None) -> "Graph":
+    return Graph("define_and_run", 1, name=name)
+
+
+def make_new_eager_graph(name: str | None = None) -> "Graph":
+    return Graph("eager", 1, name=name)
+
+
 def current_graph() -> "Graph":
     global _default_graph
     if _graph_stack:
         return _graph_stack[-1]
-    if _default_graph is None:
-        _default_graph = Graph("define_and_run", 1, name="default")
+    if _default_graph is None or _default_graph.id not in _graphs_by_id:
+        _default_graph = _default_of("define_and_run")
     return _default_graph
 
 
 @contextlib.contextmanager
-def graph(kind: str = "define_and_run", num_strategy: int = 1, create_new: bool = True, name: str | None = None):
-    g = Graph(kind, num_strategy, name=name) if (create_new or not _graph_stack) else _graph_stack[-1]
-    _graph_stack.append(g)
+def graph(g="define_and_run", num_strategy: int = -1, create_new: bool = True, name: str | None = None,
+          prefix: str = "default", tmp: bool = False):
+    """Make `g` the graph new ops go to.  `g` is a kind ("define_and_run" | "eager" | "define_by_run"), a Graph, or
+    a graph id.  With a kind, `create_new=True` (the default here; the reference defaults to False) builds a fresh
+    graph, `create_new=False` returns the process-wide default graph `<prefix>_<kind>`; `num_strategy >= 1` sets
+    the number of strategies; `tmp=True` deletes the graph on exit (reference: hetu.graph,
+    python_refactor/hetu/__init__.py:64-123)."""
+    if isinstance(g, Graph):
+        gr = g
+    elif isinstance(g, int) and not isinstance(g, bool):
+        gr = get_graph(g)
+    elif isinstance(g, str):
+        if tmp and not create_new:
+            raise ValueError("a temporary graph must be a new graph")
+        gr = Graph(g, max(1, num_strategy), name=name or None) if create_new else _default_of(g, prefix)
+    else:
+        raise ValueError(f"cannot parse {type(g).__name__} as a graph")
+    if num_strategy >= 1 and gr.num_strategy != num_strategy:
+        gr.set_num_strategy(num_strategy)
+    _graph_stack.append(gr)
     try:
-        yield g
+        yield gr
     finally:
         _graph_stack.pop()
+        if tmp:
+            delete_graph(gr)
 
 
 @contextlib.contextmanager
@@ -97,7 +172,9 @@ class Graph:
         if kind not in ("define_and_run", "eager", "define_by_run"):
             raise ValueError(f"unknown graph kind {kind}")
         self.kind = kind
-        self.name = name or kind
+        self.id = next(_graph_ids)
+        self.name = name or f"{kind}_{self.id}"
+        _graphs_by_id[self.id] = self
         self.num_strategy = num_strategy
         self.ops: list[Op] = []
         self.parameters: list[Tensor] = []
@@ -114,6 +191,12 @@ class Graph:
         self._by_name: dict[str, Tensor] = {}
 
     # ---- definition -------------------------------------------------------------------------
+    def set_num_strategy(self, n: int) -> None:
+        """Only before the first op: afterwards strategies are appended with `merge_strategy`."""
+        if self.ops or self.parameters or self.placeholders:
+            raise RuntimeError("set_num_strategy on a graph that already holds ops; use merge_strategy to add strategies")
+        self.num_strategy = int(n)
+
     def current_recompute_scope(self):
         return self._recompute_stack[-1] if self._recompute_stack else None
 

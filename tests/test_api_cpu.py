@@ -3,6 +3,7 @@ streams and events, logging, profiler hooks."""
 import json
 import os
 
+import pytest
 import numpy as np
 import torch
 
@@ -81,3 +82,33 @@ def test_streams_events_logging_profiler(tmp_path, monkeypatch):
     tr = MemoryTrace(str(tmp_path / "mem.json"))
     tr.sample(0, True); tr.flush()
     assert json.load(open(tmp_path / "mem.json"))[0]["micro_batch_id"] == 0
+
+
+def test_graph_registry_and_context_arguments():
+    import gc
+    with ht.graph("define_and_run", num_strategy=2, name="reg_test") as g:
+        assert g.num_strategy == 2
+    assert ht.get_graph(g.id) is g and ht.get_graph("reg_test") is g
+    with ht.graph(g) as again:                      # a Graph object re-enters the same graph
+        assert again is g
+    with ht.graph(g.id) as by_id:
+        assert by_id is g
+    d1 = ht.get_default_define_and_run_graph()
+    with ht.graph("define_and_run", create_new=False) as d2:
+        assert d2 is d1
+    assert ht.get_default_eager_graph().kind == "eager" and ht.get_default_define_by_run_graph().kind == "define_by_run"
+    with ht.graph("eager", tmp=True) as t:
+        tid = t.id
+    with pytest.raises(KeyError):
+        ht.get_graph(tid)
+    gid = g.id
+    del g, again, by_id
+    gc.collect()
+    with pytest.raises(KeyError):                   # the registry does not keep graphs alive
+        ht.get_graph(gid)
+    n = ht.make_new_define_and_run_graph("fresh")
+    n.set_num_strategy(3)
+    with ht.graph(n):
+        ht.placeholder(ht.float32, [2], name="x")
+    with pytest.raises(RuntimeError):
+        n.set_num_strategy(2)

@@ -59,6 +59,10 @@ PLANS = {
 }
 TOKENS_PER_GPU_BY_MODEL = {"7b": 32768, "13b": 32768, "32b": 16384}
 
+# blocks per rank that keep their activations although the strategy recomputes (per model, per world size; an int or
+# one value per strategy); only entries whose peak memory was measured
+KEEP_ACTIVATIONS: dict = {}
+
 REFERENCE_UNAVAILABLE = (
     "reference is not pip-installable (no setup.py/pyproject.toml; its CMake build needs MPI, the missing "
     "cutlass/oneDNN tarballs and compiles sm_80/86 only, and its FlashAttention wrapper asserts sm8x/sm90)")
@@ -74,6 +78,8 @@ def parse():
     ap.add_argument("--tokens_per_gpu", type=int, default=0)
     ap.add_argument("--switch_mode", default="auto")
     ap.add_argument("--mb_tokens", type=int, default=0, help="override the token budget of a micro-batch")
+    ap.add_argument("--keep_layers", default=None,
+                    help="blocks per rank that keep activations instead of recomputing: one int or one per strategy")
     ap.add_argument("--mb_tokens_pp", type=int, default=0,
                     help="override the token budget of a micro-batch for the pipelined strategies only")
     ap.add_argument("--no_e2e", action="store_true", help="skip the end-to-end region (profiling runs)")
@@ -162,8 +168,13 @@ def main():
         mb_tokens = [args.mb_tokens] * len(strategies)
     if args.mb_tokens_pp:
         mb_tokens = [args.mb_tokens_pp if pp > 1 else m for m, (_, _, pp, _) in zip(mb_tokens, strategies)]
+    keep = KEEP_ACTIVATIONS.get(args.model, {}).get(world, 0)
+    if args.keep_layers is not None:
+        keep = [int(k) for k in args.keep_layers.split(",")]
+        keep = keep[0] if len(keep) == 1 else keep
     trainer = HotSwitchTrainer(args.model, strategies, bounds, lr=1e-5, dtype=torch.bfloat16, recompute=recompute,
-                               switch_mode=args.switch_mode, micro_batch_tokens=mb_tokens, **overrides)
+                               switch_mode=args.switch_mode, micro_batch_tokens=mb_tokens, keep_activations=keep,
+                               **overrides)
     vocab = trainer.config.vocab_size
     tokens = (args.tokens_per_gpu or TOKENS_PER_GPU_BY_MODEL[args.model]) * world
     K, W = args.steps, args.warmup
@@ -264,7 +275,7 @@ def main():
             "config": {"model": f"llama-{args.model}" + (f"-{args.layers}layers(not headline)" if args.layers else ""),
                        "global_batch": f"{tokens} tokens/step", "seq_len": f"varlen<= {bounds[0]}",
                        "parallelism": par, "buckets": list(bounds), "optimizer": "Adam fp32 master",
-                       "recompute": f"per block in strategies {recompute}", "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
+                       "recompute": f"per block in strategies {recompute}", "keep_activations": keep, "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
                        "l2": "inputs larger than L2 (weights and activations of several GB stream every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

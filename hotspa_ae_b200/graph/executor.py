@@ -523,8 +523,17 @@ class Executor:
     def _forward(self, rt, plan, feeds, params, recv_vals):
         sid = plan.sid
         values = dict(recv_vals)
+        # the last `keep` recompute segments of this rank (transformer blocks) keep their activations instead: memory
+        # left over after arenas and optimizer state buys back that share of the extra forward pass
+        keep = (getattr(self.graph, "recompute_keep", None) or {}).get(sid, 0)
+        first_kept = sum(1 for s in plan.segments if s.recompute) - keep
+        rc_index = 0
         for seg in plan.segments:
-            if not seg.recompute or not torch.is_grad_enabled() or not self._recompute_on(sid):
+            kept = False
+            if seg.recompute:
+                kept = rc_index >= first_kept
+                rc_index += 1
+            if kept or not seg.recompute or not torch.is_grad_enabled() or not self._recompute_on(sid):
                 self._run_ops(rt, seg.ops, values, feeds, params, sid)
                 continue
             ext = [self._value(t, values, feeds, params, sid) for t in seg.ext_inputs]

@@ -48,7 +48,11 @@ class HotSwitchTrainer:
     def __init__(self, model: str | LlamaConfig = "7b", strategies=((1, 1, 1, False),), bucket_bounds=(32768, 0),
                  lr: float = 1e-4, dtype=torch.bfloat16, recompute: bool | list = True, switch_mode: str = "auto",
                  weight_decay: float = 0.0, ds_parallel_configs: list | None = None, gpus_per_node: int = 8,
-                 pad_id: int = 0, seed: int = 2023, micro_batch_tokens=None, **config_overrides):
+                 pad_id: int = 0, seed: int = 2023, micro_batch_tokens=None, keep_activations=0,
+                 **config_overrides):
+        """`recompute`: True / False, or the list of strategy ids whose blocks recompute.  `keep_activations`: number
+        of blocks per rank (an int, or one per strategy) that keep their activations although their strategy
+        recomputes; spends spare memory to skip that share of the second forward pass."""
         self.mesh = ht.init_comm_group(gpus_per_node)
         world = self.mesh.world_size
         self.config = model if isinstance(model, LlamaConfig) else llama_config(model, **config_overrides)
@@ -100,6 +104,9 @@ class HotSwitchTrainer:
         self.graph = g
         if isinstance(recompute, (list, tuple, set)):
             g.recompute_strategies = set(recompute)
+        if keep_activations:
+            ka = [keep_activations] * len(cfgs) if isinstance(keep_activations, int) else list(keep_activations)
+            g.recompute_keep = {sid: int(k) for sid, k in enumerate(ka) if k}
         store = g.executor.store
         store.seed = seed
         if switch_mode == "auto":

@@ -42,3 +42,34 @@ def test_tiny_llama_one_step_matches_pytorch():
         # elements whose gradient is ~0 have an ill-conditioned Adam direction; compare where |g| is meaningful
         mask = g_ref.abs() > 1e-7
         assert torch.allclose(got[mask], want[mask], rtol=1e-3, atol=2e-5), k
+
+
+def _one_step(recompute, keep):
+    from hotspa_ae_b200.parallel import mesh as M
+    M.reset_mesh()
+    ht.init_comm_group(8)
+    cfg = llama_config("tiny", max_seq_len=512, recompute=recompute)
+    b = build_llama_graph(cfg, [(1, 1, 1, False)], 1, lr=1e-3)
+    g = b["graph"]
+    if keep:
+        g.recompute_keep = {0: keep}
+    _, rows = tiny_batch()
+    cfg.mbs_times_dp_symbol.set_data(1)
+    cfg.seq_len_symbol.set_data(512)
+    feed = {b["input_ids"]: np.stack([r[0] for r in rows]), b["labels"]: np.stack([r[1] for r in rows]),
+            b["position_ids"]: np.stack([r[2] for r in rows]), b["cu_seqlens"]: np.stack([r[3] for r in rows])}
+    out = g.run(b["loss"], [b["loss"], b["train_op"]], feed, len(rows), 0, ht.run_level("update"))
+    n_rc = sum(1 for s in g.executor.plan(0).segments if s.recompute)
+    return out[0].numpy(), {k: np.array(p.get_data()) for k, p in b["model"].named_parameters()}, n_rc
+
+
+def test_recompute_and_kept_blocks_do_not_change_the_step():
+    loss0, p0, n0 = _one_step(False, 0)
+    loss1, p1, n1 = _one_step(True, 0)
+    loss2, p2, n2 = _one_step(True, 1)
+    assert n0 == 0 and n1 == n2 and n1 >= 2
+    np.testing.assert_allclose(loss1, loss0, rtol=1e-6)
+    np.testing.assert_allclose(loss2, loss0, rtol=1e-6)
+    for k in p0:
+        np.testing.assert_allclose(p1[k], p0[k], rtol=1e-5, atol=1e-7, err_msg=k)
+        np.testing.assert_allclose(p2[k], p0[k], rtol=1e-5, atol=1e-7, err_msg=k)

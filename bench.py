@@ -26,6 +26,11 @@ import subprocess
 import sys
 import tempfile
 
+# the caching allocator grows its segments in place instead of holding fixed-size ones: with activations of kept
+# blocks next to recompute working sets the fixed segments stranded ~25 GB per GPU (reserved 85 GB for 59 GB
+# allocated at 4 GPUs), memory that is better spent on keeping more activations
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -61,7 +66,10 @@ TOKENS_PER_GPU_BY_MODEL = {"7b": 32768, "13b": 32768, "32b": 16384}
 
 # blocks per rank that keep their activations although the strategy recomputes (per model, per world size; an int or
 # one value per strategy); only entries whose peak memory was measured
-KEEP_ACTIVATIONS: dict = {}
+KEEP_ACTIVATIONS: dict = {
+    # 7B: one kept block costs 4.0-4.3 GB per 32K-token micro-batch divided by the tensor-parallel degree
+    "7b": {1: 6, 2: [20, 10], 4: [32, 26, 13], 8: [16, 16, 12]},
+}
 
 REFERENCE_UNAVAILABLE = (
     "reference is not pip-installable (no setup.py/pyproject.toml; its CMake build needs MPI, the missing "
@@ -261,6 +269,10 @@ def main():
         alloc = {k: ms1[k] - ms0[k] for k in ("num_alloc_retries", "num_device_alloc", "num_device_free")}
         alloc["reserved_gb"] = ms1["reserved_bytes.all.current"] / 2**30
         alloc["allocated_peak_gb"] = ms1["allocated_bytes.all.peak"] / 2**30
+        alloc["reserved_peak_gb"] = ms1["reserved_bytes.all.peak"] / 2**30
+        free_b, total_b = torch.cuda.mem_get_info()
+        alloc["device_used_gb"] = (total_b - free_b) / 2**30      # allocator cache + peer-mapped arenas + context
+        alloc["device_total_gb"] = total_b / 2**30
         print(f"[rank {rank}] prepare {1e3 * (t1 - t0):.1f} ms host; " + json.dumps(trainer.last_profile) +
               " allocator " + json.dumps(alloc), file=sys.stderr, flush=True)
         trainer.profile = False
@@ -275,7 +287,8 @@ def main():
             "config": {"model": f"llama-{args.model}" + (f"-{args.layers}layers(not headline)" if args.layers else ""),
                        "global_batch": f"{tokens} tokens/step", "seq_len": f"varlen<= {bounds[0]}",
                        "parallelism": par, "buckets": list(bounds), "optimizer": "Adam fp32 master",
-                       "recompute": f"per block in strategies {recompute}", "keep_activations": keep, "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
+                       "recompute": f"per block in strategies {recompute}", "keep_activations": keep,
+                       "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
                        "l2": "inputs larger than L2 (weights and activations of several GB stream every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

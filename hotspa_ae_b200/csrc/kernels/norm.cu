@@ -114,92 +114,146 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
 // dx = d(norm)/dx applied to dy (+ dres);  per-CTA partial dw/db into scratch[blockIdx.x][0|1][H].
-template <bool RMS>
-__global__ void __launch_bounds__(NORM_THREADS)
+// NV = 128-bit chunks of a row per thread (H <= 2048 * NV).  The raw dy / x chunks of the CTA's next row and the
+// residual gradient of the current one are requested before the block-wide reduction of the current row, so the
+// loads are in flight across its two barriers; with NV <= 2 two CTAs fit an SM.
+template <bool RMS, int NV>
+__global__ void __launch_bounds__(NORM_THREADS, (NV <= 2) ? 2 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
                 __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, int rows, int H) {
   __shared__ float red[32];
   const int nvec = H >> 3;
-  float dw_acc[NORM_MAX_VEC][8], db_acc[NORM_MAX_VEC][8], wv[NORM_MAX_VEC][8];
+  float dw_acc[NV][8], db_acc[NV][8], wv[NV][8];
+  uint4 dy_raw[NV], x_raw[NV], r_raw[NV];
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-  for (int c = 0; c < NORM_MAX_VEC; ++c) {
+  for (int c = 0; c < NV; ++c) {
     const int i = threadIdx.x + c * NORM_THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) { dw_acc[c][j] = 0.f; db_acc[c][j] = 0.f; wv[c][j] = 0.f; }
     if (i < nvec) load8(w + i * 8, wv[c]);
+    dy_raw[c] = zero4; x_raw[c] = zero4; r_raw[c] = zero4;
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  int row = blockIdx.x;
+  if (row < rows) {
+    const size_t base = static_cast<size_t>(row) * H;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+      const int i = threadIdx.x + c * NORM_THREADS;
+      if (i < nvec) {
+        dy_raw[c] = *reinterpret_cast<const uint4*>(dy + base + i * 8);
+        x_raw[c] = *reinterpret_cast<const uint4*>(x + base + i * 8);
+      }
+    }
+  }
+  for (; row < rows; row += gridDim.x) {
     const size_t base = static_cast<size_t>(row) * H;
     const float rstd = rstd_in[row];
     const float mean = RMS ? 0.f : mean_in[row];
-    float g[NORM_MAX_VEC][8], xh[NORM_MAX_VEC][8];
+    float g[NV][8], xh[NV][8];
     float sg = 0.f, sgx = 0.f;
 #pragma unroll
-    for (int c = 0; c < NORM_MAX_VEC; ++c) {
+    for (int c = 0; c < NV; ++c) {
+      float dyv[8], xv[8];
+      unpack8(dy_raw[c], dyv);           // chunks past the row end hold zeros and add nothing
+      unpack8(x_raw[c], xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[c][j] = (xv[j] - mean) * rstd;
+        g[c][j] = dyv[j] * wv[c][j];
+        sg += g[c][j];
+        sgx += g[c][j] * xh[c][j];
+        dw_acc[c][j] += dyv[j] * xh[c][j];
+        db_acc[c][j] += dyv[j];
+      }
+    }
+    const int next = row + gridDim.x;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
       const int i = threadIdx.x + c * NORM_THREADS;
       if (i < nvec) {
-        float dyv[8], xv[8];
-        load8(dy + base + i * 8, dyv);
-        load8(x + base + i * 8, xv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[c][j] = (xv[j] - mean) * rstd;
-          g[c][j] = dyv[j] * wv[c][j];
-          sg += g[c][j];
-          sgx += g[c][j] * xh[c][j];
-          dw_acc[c][j] += dyv[j] * xh[c][j];
-          db_acc[c][j] += dyv[j];
+        if (dres) r_raw[c] = *reinterpret_cast<const uint4*>(dres + base + i * 8);
+        if (next < rows) {
+          const size_t nb = static_cast<size_t>(next) * H;
+          dy_raw[c] = *reinterpret_cast<const uint4*>(dy + nb + i * 8);
+          x_raw[c] = *reinterpret_cast<const uint4*>(x + nb + i * 8);
         }
       }
     }
     sgx = block_sum(sgx, red) / H;
     if (!RMS) sg = block_sum(sg, red) / H; else sg = 0.f;
 #pragma unroll
-    for (int c = 0; c < NORM_MAX_VEC; ++c) {
+    for (int c = 0; c < NV; ++c) {
       const int i = threadIdx.x + c * NORM_THREADS;
       if (i < nvec) {
-        float o[8];
+        float o[8], rv[8];
+        unpack8(r_raw[c], rv);            // zeros when there is no residual gradient
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[c][j] - sg - xh[c][j] * sgx);
-        if (dres) {
-          float rv[8];
-          load8(dres + base + i * 8, rv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += rv[j];
-        }
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[c][j] - sg - xh[c][j] * sgx) + rv[j];
         store8(dx + base + i * 8, o);
       }
     }
   }
   float* my = scratch + static_cast<size_t>(blockIdx.x) * 2 * H;
 #pragma unroll
-  for (int c = 0; c < NORM_MAX_VEC; ++c) {
+  for (int c = 0; c < NV; ++c) {
     const int i = threadIdx.x + c * NORM_THREADS;
     if (i < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        my[i * 8 + j] = dw_acc[c][j];
-        if (!RMS) my[H + i * 8 + j] = db_acc[c][j];
+      *reinterpret_cast<float4*>(my + i * 8) = make_float4(dw_acc[c][0], dw_acc[c][1], dw_acc[c][2], dw_acc[c][3]);
+      *reinterpret_cast<float4*>(my + i * 8 + 4) = make_float4(dw_acc[c][4], dw_acc[c][5], dw_acc[c][6], dw_acc[c][7]);
+      if (!RMS) {
+        *reinterpret_cast<float4*>(my + H + i * 8) = make_float4(db_acc[c][0], db_acc[c][1], db_acc[c][2], db_acc[c][3]);
+        *reinterpret_cast<float4*>(my + H + i * 8 + 4) = make_float4(db_acc[c][4], db_acc[c][5], db_acc[c][6], db_acc[c][7]);
       }
     }
   }
 }
 
 // dw[h] (+)= sum_p scratch[p][0][h];  db likewise from scratch[p][1][h].
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ scratch, float* __restrict__ dw,
-                                       float* __restrict__ db, int parts, int H, int accumulate) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
+// A CTA owns 32 columns; its 8 warps each sum every 8th partial row, then combine through shared memory.
+constexpr int NORM_RED_COLS = 32, NORM_RED_WAYS = 8;
+__global__ void __launch_bounds__(NORM_RED_COLS * NORM_RED_WAYS)
+norm_bwd_reduce_kernel(const float* __restrict__ scratch, float* __restrict__ dw, float* __restrict__ db, int parts,
+                       int H, int accumulate) {
+  __shared__ float sa[NORM_RED_WAYS][NORM_RED_COLS], sb[NORM_RED_WAYS][NORM_RED_COLS];
+  const int lane = threadIdx.x & 31, way = threadIdx.x >> 5;
+  const int h = blockIdx.x * NORM_RED_COLS + lane;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < parts; ++p) {
-    a += scratch[static_cast<size_t>(p) * 2 * H + h];
-    if (db) b += scratch[static_cast<size_t>(p) * 2 * H + H + h];
+  if (h < H) {
+#pragma unroll 4
+    for (int p = way; p < parts; p += NORM_RED_WAYS) {
+      a += scratch[static_cast<size_t>(p) * 2 * H + h];
+      if (db) b += scratch[static_cast<size_t>(p) * 2 * H + H + h];
+    }
   }
-  if (accumulate) { dw[h] += a; if (db) db[h] += b; }
-  else            { dw[h] = a;  if (db) db[h] = b; }
+  sa[way][lane] = a;
+  sb[way][lane] = b;
+  __syncthreads();
+  if (way == 0 && h < H) {
+#pragma unroll
+    for (int k = 1; k < NORM_RED_WAYS; ++k) { a += sa[k][lane]; b += sb[k][lane]; }
+    if (accumulate) { dw[h] += a; if (db) db[h] += b; }
+    else            { dw[h] = a;  if (db) db[h] = b; }
+  }
+}
+
+template <bool RMS>
+static void launch_norm_bwd(int parts, cudaStream_t st, const __nv_bfloat16* DY, const __nv_bfloat16* X,
+                            const __nv_bfloat16* W, const float* mean, const float* rstd, const __nv_bfloat16* DR,
+                            __nv_bfloat16* DX, float* scratch, int rows, int H) {
+  const int nv = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  if (nv <= 1)      norm_bwd_kernel<RMS, 1><<<parts, NORM_THREADS, 0, st>>>(DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
+  else if (nv == 2) norm_bwd_kernel<RMS, 2><<<parts, NORM_THREADS, 0, st>>>(DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
+  else if (nv == 3) norm_bwd_kernel<RMS, 3><<<parts, NORM_THREADS, 0, st>>>(DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
+  else              norm_bwd_kernel<RMS, 4><<<parts, NORM_THREADS, 0, st>>>(DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
 }
 
 }  // namespace hsb
@@ -240,9 +294,10 @@ extern "C" int hsb_norm_bwd(const void* dy, const void* x, const void* w, const 
   auto W = reinterpret_cast<const __nv_bfloat16*>(w);
   auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
-  if (is_rms) norm_bwd_kernel<true><<<parts, NORM_THREADS, 0, st>>>(DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
-  else        norm_bwd_kernel<false><<<parts, NORM_THREADS, 0, st>>>(DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
-  norm_bwd_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, is_rms ? nullptr : db, parts, H, accumulate);
+  if (is_rms) launch_norm_bwd<true>(parts, st, DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
+  else        launch_norm_bwd<false>(parts, st, DY, X, W, mean, rstd, DR, DX, scratch, rows, H);
+  norm_bwd_reduce_kernel<<<(H + NORM_RED_COLS - 1) / NORM_RED_COLS, NORM_RED_COLS * NORM_RED_WAYS, 0, st>>>(
+      scratch, dw, is_rms ? nullptr : db, parts, H, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -50,6 +50,9 @@ def parse_args(argv=None):
     ap.add_argument("--adam_weight_decay", type=float, default=0.0)
     ap.add_argument("--bf16", action="store_true")
     ap.add_argument("--no_recompute", action="store_true")
+    ap.add_argument("--keep_activations", default=None,
+                    help="blocks per rank that keep their activations although blocks recompute: one count, or one "
+                         "per strategy (\"16,16,18\")")
     ap.add_argument("--switch_mode", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--vocab_size", type=int, default=0)
     ap.add_argument("--hidden_size", type=int, default=0)

@@ -300,6 +300,14 @@ class HotSwitchTrainer:
         return self.model.state_dict()
 
 
+def _keep_arg(text):
+    """"4" -> 4 blocks in every strategy; "16,16,18" -> one count per strategy; None / "" -> 0."""
+    if not text:
+        return 0
+    vals = [int(v) for v in str(text).replace(" ", ",").split(",") if v != ""]
+    return vals[0] if len(vals) == 1 else vals
+
+
 def build_trainer_from_args(args) -> HotSwitchTrainer:
     bounds = [int(x) for x in str(args.bucket_sizes).split()]
     if args.ds_parallel_config:
@@ -327,6 +335,7 @@ def build_trainer_from_args(args) -> HotSwitchTrainer:
                             dtype=torch.bfloat16 if args.bf16 else torch.float32, recompute=not args.no_recompute,
                             switch_mode=args.switch_mode, weight_decay=args.adam_weight_decay,
                             ds_parallel_configs=cfgs, micro_batch_tokens=getattr(args, "micro_batch_tokens", 0) or None,
+                            keep_activations=_keep_arg(getattr(args, "keep_activations", None)),
                             **overrides)
 
 

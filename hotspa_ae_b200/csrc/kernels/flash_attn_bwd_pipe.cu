@@ -2,18 +2,22 @@
 //
 // Same math and work decomposition as flash_attn_bwd.cu (one work item = kv tile j of a document x head; the
 // CTA keeps K_j, V_j in shared memory and dK_j, dV_j in TMEM while it walks the query tiles of the document),
-// but the query dimension is tiled by 64 and every per-tile resource is double buffered so that the tensor
-// cores, the softmax warps and TMA work on different query tiles at the same time:
+// but the query dimension is tiled by 64 and the per-tile resources are arranged so that the softmax warps never
+// wait for the tensor cores in steady state:
 //
-//   TMA      loads Q_{i+2}, dO_{i+2}                                        (2-stage ring, 64 x 128 tiles)
-//   MMA      S^T_{i+2} = K Q^T,  dP^T_{i+2} = V dO^T    [128 kv x 64 q]     (TMEM, 2 buffers of 64 + 64 columns)
-//            dV += P^T_i dO_i,  dK += dS^T_i Q_i,  dQ^T_i = K^T dS_i         (dQ^T_i overwrites S^T_i's columns)
-//   softmax  drains dQ^T_{i-1} (red.add into the fp32 accumulator), then turns S^T_i, dP^T_i into the bf16
-//            tiles P^T_i, dS^T_i in shared memory (2 buffers)
+//   TMA      loads Q_{i+2}, dO_{i+2}                                        (3-stage ring, 64 x 128 tiles)
+//   MMA      S^T_{i+1} = K Q^T,  dP^T_{i+1} = V dO^T    [128 kv x 64 q]     issued as soon as the softmax warps hold
+//                                                                           S^T_i, dP^T_i in registers
+//            dV += P^T_i dO_i,  dK += dS^T_i Q_i,  dQ^T_i = K^T dS_i         issued when P^T_i, dS^T_i are in shared memory
+//   softmax  reads S^T_i, dP^T_i out of TMEM, writes the bf16 tiles P^T_i, dS^T_i (2 shared-memory buffers), and
+//            only then drains dQ^T_{i-1} (red.add into the fp32 accumulator): its MMAs ran during the softmax of
+//            tile i
 //
-// dQ is produced transposed ([d x q], lanes = d) so that it fits the 64 columns that S^T_i occupied and the
-// 32 lanes of a warp add 32 consecutive floats of one query row at a time.
-// TMEM: S0 dP0 S1 dP1 (4 x 64 columns) | dV (128) | dK (128) = 512 columns.
+// dQ is produced transposed ([d x q], lanes = d) so that the 32 lanes of a warp add 32 consecutive floats of one
+// query row at a time.
+// TMEM: S^T (64 columns) | dP^T (64) | dQ^T buffer 0 (64) | dQ^T buffer 1 (64) | dV (128) | dK (128) = 512 columns.
+// S^T / dP^T need one buffer only because they live in registers from the start of a tile's softmax; dQ^T needs two
+// because tile i's is written while tile i-1's is still being drained.
 #include "common.cuh"
 #include "fa_api.h"
 #include <cuda.h>
@@ -34,11 +38,13 @@ constexpr int SM_WARPS = 8;
 constexpr int KV_TILE_BYTES = KV_T * HD * 2;     // 32 KB
 constexpr int Q_TILE_BYTES = Q_T * HD * 2;       // 16 KB
 constexpr int PT_BYTES = KV_T * Q_T * 2;         // 16 KB
-constexpr int SMEM_BYTES = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 4 * PT_BYTES + 1024 + 1024 + 512;
+constexpr int Q_STAGES = 3;
+constexpr int STAT_BYTES = SM_WARPS * 64 * 4;    // per softmax warp: lse and delta of its 32 query columns
+constexpr int SMEM_BYTES = 2 * KV_TILE_BYTES + 2 * Q_STAGES * Q_TILE_BYTES + 4 * PT_BYTES + STAT_BYTES + 256;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 constexpr int TMEM_COLS = 512;
-constexpr int DV_COL = 256, DK_COL = 384;
+constexpr int S_COL = 0, DP_COL = 64, DQ_COL = 128, DV_COL = 256, DK_COL = 384;
 
-__device__ __forceinline__ void group_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -54,27 +60,31 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
                    const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dqkv,
                    float* __restrict__ dq_acc, int T, int heads, float scale, float scale_log2,
                    int* __restrict__ status) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {            // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(status, ST_OK, ST_BAD_ARGUMENT);
+    return;
+  }
   uint8_t* sK = smem;
   uint8_t* sV = sK + KV_TILE_BYTES;
-  uint8_t* sQ = sV + KV_TILE_BYTES;            // [2] x 16 KB
-  uint8_t* sdO = sQ + 2 * Q_TILE_BYTES;        // [2] x 16 KB
-  uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;       // [2] x 16 KB
-  uint8_t* sdST = sPT + 2 * PT_BYTES;          // [2] x 16 KB
-  float* sLse = reinterpret_cast<float*>(sdST + 2 * PT_BYTES);   // [2][64]
-  float* sDelta = sLse + 2 * Q_T;                                // [2][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sLse) + 1024);
+  uint8_t* sQ = sV + KV_TILE_BYTES;                  // [Q_STAGES] x 16 KB
+  uint8_t* sdO = sQ + Q_STAGES * Q_TILE_BYTES;       // [Q_STAGES] x 16 KB
+  uint8_t* sPT = sdO + Q_STAGES * Q_TILE_BYTES;      // [2] x 16 KB
+  uint8_t* sdST = sPT + 2 * PT_BYTES;                // [2] x 16 KB
+  float* sStat = reinterpret_cast<float*>(sdST + 2 * PT_BYTES);   // [SM_WARPS][lse 32 | delta 32]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStat) + STAT_BYTES);
   uint64_t* kv_full = bars + 0;
   uint64_t* kv_empty = bars + 1;
-  uint64_t* qdo_full = bars + 2;     // [2]
-  uint64_t* qdo_empty = bars + 4;    // [2]  second-phase MMAs of the tile retired (TMA may refill)
-  uint64_t* sdp_full = bars + 6;     // [2]  S^T, dP^T of the tile are in TMEM
-  uint64_t* pds_full = bars + 8;     // [2]  P^T, dS^T of the tile are in shared memory (4 warps arrive)
-  uint64_t* mma2_done = bars + 10;   // [2]  dV, dK, dQ^T MMAs of the tile retired (softmax side: smem free, dQ^T ready)
-  uint64_t* dq_drained = bars + 12;  // [2]  dQ^T of the tile has been read out of TMEM (4 warps arrive)
-  uint64_t* dkv_drained = bars + 14; // dK, dV of the item have been read out (4 warps arrive)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* qdo_full = bars + 2;     // [3]
+  uint64_t* qdo_empty = bars + 5;    // [3]  second-phase MMAs of the tile retired (TMA may refill)
+  uint64_t* sdp_full = bars + 8;     // S^T, dP^T of the tile are in TMEM
+  uint64_t* sdp_read = bars + 9;     // S^T, dP^T of the tile are in the softmax warps' registers (8 warps arrive)
+  uint64_t* pds_full = bars + 10;    // [2]  P^T, dS^T of the tile are in shared memory (8 warps arrive)
+  uint64_t* mma2_done = bars + 12;   // [2]  dV, dK, dQ^T MMAs of the tile retired (smem buffer free, dQ^T ready)
+  uint64_t* dq_drained = bars + 14;  // [2]  dQ^T of the tile has been read out of TMEM (8 warps arrive)
+  uint64_t* dkv_drained = bars + 16; // dK, dV of the item have been read out (8 warps arrive)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -83,8 +93,9 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(kv_empty, 1); mbar_init(dkv_drained, SM_WARPS);
+    mbar_init(sdp_full, 1); mbar_init(sdp_read, SM_WARPS);
+    for (int b = 0; b < Q_STAGES; ++b) { mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1); }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1); mbar_init(&sdp_full[b], 1);
       mbar_init(&pds_full[b], SM_WARPS); mbar_init(&mma2_done[b], 1); mbar_init(&dq_drained[b], SM_WARPS);
     }
     *abort_flag = 0;
@@ -117,9 +128,9 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
         }
         ++n_kv;
         for (int i = 0; i < nq && ok; ++i, ++n_q) {
-          const int b = n_q & 1;
+          const int b = static_cast<int>(n_q % Q_STAGES);
           const int q_start = kv_start + i * Q_T;
-          if (!mbar_wait(&qdo_empty[b], ((n_q >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&qdo_empty[b], ((n_q / Q_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
           mbar_arrive_expect_tx(&qdo_full[b], 2 * Q_TILE_BYTES);
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
@@ -143,14 +154,13 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
       uint32_t n_m = 0;      // second-phase tiles issued so far
       bool ok = true;
       auto issue_sdp = [&](uint32_t idx) -> bool {
-        const int b = idx & 1;
-        const uint32_t ph = (idx >> 1) & 1;
-        if (!mbar_wait(&qdo_full[b], ph, abort_flag)) return false;
-        // the buffer's previous tenant (tile idx - 2) left its dQ^T in the S columns: it must have been read out
-        if (!mbar_wait(&dq_drained[b], ph ^ 1, abort_flag)) return false;
+        const int st = static_cast<int>(idx % Q_STAGES);
+        if (!mbar_wait(&qdo_full[st], (idx / Q_STAGES) & 1, abort_flag)) return false;
+        // the single S^T / dP^T buffer: the previous tile must be in the softmax warps' registers
+        if (!mbar_wait(sdp_read, (idx & 1) ^ 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t q = aQ + b * Q_TILE_BYTES, d_o = adO + b * Q_TILE_BYTES;
-        const uint32_t s_col = tmem_base + b * 128, dp_col = s_col + 64;
+        const uint32_t q = aQ + st * Q_TILE_BYTES, d_o = adO + st * Q_TILE_BYTES;
+        const uint32_t s_col = tmem_base + S_COL, dp_col = tmem_base + DP_COL;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t ka = (kk / 4) * (KV_T * 128) + (kk % 4) * 32;
@@ -165,7 +175,7 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
           umma_bf16_ss(dp_col, make_smem_desc_sw128(aV + va, 16, 1024), make_smem_desc_sw128(d_o + ob, 16, 1024),
                        idesc_st, kk != 0 ? 1u : 0u);
         }
-        umma_commit(&sdp_full[b]);
+        umma_commit(sdp_full);
         return true;
       };
       for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
@@ -174,16 +184,23 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
         const int kv_start = t[0], doc_end = t[2];
         const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;
         if (!mbar_wait(kv_full, n_kv & 1, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(dkv_drained, (n_item & 1) ^ 1, abort_flag)) { ok = false; break; }
-        // prologue: two tiles of S^T / dP^T in flight
-        uint32_t issued = 0;
-        for (; issued < 2u && issued < static_cast<uint32_t>(nq) && ok; ++issued, ++n_s) ok = issue_sdp(n_s);
+        if (nq > 0) { ok = issue_sdp(n_s); ++n_s; }
         for (int i = 0; i < nq && ok; ++i, ++n_m) {
+          // next tile's S^T / dP^T first: they run while the softmax warps work on tile i
+          if (i + 1 < nq) {
+            if (!issue_sdp(n_s)) { ok = false; break; }
+            ++n_s;
+          }
           const int b = n_m & 1;
           const uint32_t ph = (n_m >> 1) & 1;
+          const int st = static_cast<int>(n_m % Q_STAGES);
           if (!mbar_wait(&pds_full[b], ph, abort_flag)) { ok = false; break; }
+          // dQ^T buffer b still holds tile n_m - 2 until the softmax warps have read it out
+          if (!mbar_wait(&dq_drained[b], ph ^ 1, abort_flag)) { ok = false; break; }
+          // the first tile of an item overwrites dK, dV: the previous item's must have been read out
+          if (i == 0) { if (!mbar_wait(dkv_drained, (n_item & 1) ^ 1, abort_flag)) { ok = false; break; } }
           tc_fence_after();
-          const uint32_t q = aQ + b * Q_TILE_BYTES, d_o = adO + b * Q_TILE_BYTES;
+          const uint32_t q = aQ + st * Q_TILE_BYTES, d_o = adO + st * Q_TILE_BYTES;
           const uint32_t pt = aPT + b * PT_BYTES, dst = adST + b * PT_BYTES;
           const uint32_t acc = i > 0 ? 1u : 0u;
 #pragma unroll
@@ -195,16 +212,11 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
             umma_bf16_ss(tmem_base + DK_COL, make_smem_desc_sw128(dst + kk * 32, 16, 1024),
                          make_smem_desc_sw128(q + kk * 2048, Q_T * 128, 1024), idesc_kn, (acc | (kk != 0)) ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < KV_T / 16; ++kk)     // dQ^T[d, q] = K^T[d, kv] dS^T[kv, q]   (over S^T's columns)
-            umma_bf16_ss(tmem_base + b * 128, make_smem_desc_sw128(aK + kk * 2048, KV_T * 128, 1024),
+          for (int kk = 0; kk < KV_T / 16; ++kk)     // dQ^T[d, q] = K^T[d, kv] dS^T[kv, q]
+            umma_bf16_ss(tmem_base + DQ_COL + b * 64, make_smem_desc_sw128(aK + kk * 2048, KV_T * 128, 1024),
                          make_smem_desc_sw128(dst + kk * 2048, Q_T * 128, 1024), idesc_qt, kk != 0 ? 1u : 0u);
           umma_commit(&mma2_done[b]);
-          umma_commit(&qdo_empty[b]);
-          // keep two S^T / dP^T tiles ahead of the softmax warps
-          if (issued < static_cast<uint32_t>(nq)) {
-            if (!issue_sdp(n_s)) { ok = false; break; }
-            ++n_s; ++issued;
-          }
+          umma_commit(&qdo_empty[st]);
         }
         if (!ok) break;
         umma_commit(kv_empty);
@@ -219,8 +231,9 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;                    // which half of the columns this warp handles
     const int row = quarter * 32 + lane;                 // kv row (softmax) or d index (dQ^T drain) == TMEM lane
-    const int tid256 = threadIdx.x - 64;
+    const int c = half * 32;                             // first query column of this warp
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    float* stat = sStat + (warp - 2) * 64;               // this warp's lse[32] | delta[32]
     uint32_t n_t = 0;                                    // tiles processed so far (global counter)
     bool ok = true;
     auto drain_dq = [&](uint32_t idx, int q_start, int doc_end, int h) -> bool {
@@ -230,9 +243,8 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
       const int q_lim = min(doc_end, T) - q_start;       // query rows of this tile inside the document
       float* base = dq_acc + (static_cast<size_t>(q_start) * heads + h) * HD + row;
       {
-        const int c = half * 32;
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + c, r);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + DQ_COL + b * 64 + c, r);
         tmem_ld_wait();
         const size_t qstride = static_cast<size_t>(heads) * HD;
         float* pq = base + static_cast<size_t>(c) * qstride;
@@ -255,46 +267,57 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
       const int* t = table + 2 + 4 * item;
       const int kv_start = t[0], doc_end = t[2];
       const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;
+      // lse / delta of this lane's query column, fetched one tile ahead
+      float nxt_l = 0.f, nxt_d = 0.f;
+      {
+        const int qi = kv_start + c + lane;
+        if (qi < doc_end && qi < T) {
+          nxt_l = lse[static_cast<size_t>(h) * T + qi];
+          nxt_d = delta[static_cast<size_t>(h) * T + qi];
+        }
+      }
       for (int i = 0; i < nq && ok; ++i, ++n_t) {
         const int b = n_t & 1;
         const uint32_t ph = (n_t >> 1) & 1;
         const int q_start = kv_start + i * Q_T;
-        // the previous tile's dQ^T first: it frees its S columns for the MMA warp's look-ahead
-        if (i > 0) { if (!drain_dq(n_t - 1, q_start - Q_T, doc_end, h)) { ok = false; break; } }
-        {
-          const int c = tid256 & 63;
-          const int qi = q_start + c;
-          const bool v = qi < doc_end && qi < T;
-          if (tid256 < 64) sLse[b * Q_T + c] = v ? lse[static_cast<size_t>(h) * T + qi] : 0.f;
-          else if (tid256 < 128) sDelta[b * Q_T + c] = v ? delta[static_cast<size_t>(h) * T + qi] : 0.f;
+        stat[lane] = nxt_l;
+        stat[32 + lane] = nxt_d;
+        __syncwarp();
+        nxt_l = 0.f; nxt_d = 0.f;
+        if (i + 1 < nq) {
+          const int qi = q_start + Q_T + c + lane;
+          if (qi < doc_end && qi < T) {
+            nxt_l = lse[static_cast<size_t>(h) * T + qi];
+            nxt_d = delta[static_cast<size_t>(h) * T + qi];
+          }
         }
-        group_sync();
-        if (!mbar_wait(&sdp_full[b], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(sdp_full, n_t & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + S_COL + c, rs);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + DP_COL + c, rp);
+        tmem_ld_wait();
+        // S^T, dP^T now live in registers: the MMA warp may start the next tile's
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_read);
         // P^T / dS^T buffer b was read by the MMAs of tile n_t - 2
         if (n_t >= 2) { if (!mbar_wait(&mma2_done[b], ph ^ 1, abort_flag)) { ok = false; break; } }
-        tc_fence_after();
         const int q_valid = min(Q_T, doc_end - q_start);
         const bool diag = q_start < kv_start + KV_T;          // tile touches the causal diagonal
         const int shift = q_start - kv_start;                 // keep (row, col) iff col + shift >= row
         uint8_t* prow = sPT + b * PT_BYTES + row * 128;
         uint8_t* drow = sdST + b * PT_BYTES + row * 128;
-        const float* lse_b = sLse + b * Q_T;
-        const float* del_b = sDelta + b * Q_T;
         {
-          const int c = half * 32;
-          uint32_t rs[32], rp[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + c, rs);
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * 128 + 64 + c, rp);
-          tmem_ld_wait();
           // tiles away from the diagonal and inside the document (the common case) need no masking at all
           const bool need_mask = diag || q_valid < Q_T;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float p[8], ds[8];
-            const float4 l0 = *reinterpret_cast<const float4*>(lse_b + c + g * 8);
-            const float4 l1 = *reinterpret_cast<const float4*>(lse_b + c + g * 8 + 4);
-            const float4 d0 = *reinterpret_cast<const float4*>(del_b + c + g * 8);
-            const float4 d1 = *reinterpret_cast<const float4*>(del_b + c + g * 8 + 4);
+            const float4 l0 = *reinterpret_cast<const float4*>(stat + g * 8);
+            const float4 l1 = *reinterpret_cast<const float4*>(stat + g * 8 + 4);
+            const float4 d0 = *reinterpret_cast<const float4*>(stat + 32 + g * 8);
+            const float4 d1 = *reinterpret_cast<const float4*>(stat + 32 + g * 8 + 4);
             const float lv[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
             const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
@@ -323,9 +346,10 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
           }
         }
         fence_proxy_async_smem();
-        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pds_full[b]);
+        // the previous tile's dQ^T: its MMAs ran while this tile's softmax was computed
+        if (i > 0) { if (!drain_dq(n_t - 1, q_start - Q_T, doc_end, h)) { ok = false; break; } }
       }
       if (!ok) break;
       // last tile's dQ^T, then the finished dK_j, dV_j (their last MMAs retired with that tile's commit)

@@ -88,6 +88,9 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // work items are head-major: the CTAs running at one time walk the kv tiles of the same head, so the Q / dO tiles
+  // they stream and the dQ rows they add into are shared through L2 (item-major order gave every CTA its own head:
+  // a working set of ~300 MB, 11 GB of DRAM traffic for 16K tokens)
   const int n_items = table[0];
   const long n_work = static_cast<long>(n_items) * heads;
 
@@ -114,7 +117,7 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
       uint32_t n_kv = 0, n_q = 0;
       bool ok = true;
       for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int item = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+        const int item = static_cast<int>(w % n_items), h = static_cast<int>(w / n_items);
         const int* t = table + 2 + 4 * item;
         const int kv_start = t[0], doc_end = t[2];
         const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;        // query tiles from the diagonal to the end
@@ -179,7 +182,7 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
         return true;
       };
       for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int item = static_cast<int>(w / heads);
+        const int item = static_cast<int>(w % n_items);
         const int* t = table + 2 + 4 * item;
         const int kv_start = t[0], doc_end = t[2];
         const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;
@@ -263,7 +266,7 @@ fa_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_const
       return true;
     };
     for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-      const int item = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+      const int item = static_cast<int>(w % n_items), h = static_cast<int>(w / n_items);
       const int* t = table + 2 + 4 * item;
       const int kv_start = t[0], doc_end = t[2];
       const int nq = (doc_end - kv_start + Q_T - 1) / Q_T;

@@ -113,6 +113,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
   float* x_sum = x_max + 2 * FA_BM;                          // [2 halves][128 rows] partial row sums (epilogue)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // work items are head-major: the CTAs running at one time walk the tiles of the same head, so the K / V tiles
+  // they stream are shared through L2 (tile-major order gave every CTA a different head: a 300 MB working set)
   const int n_tiles = table[0];
   const long n_work = static_cast<long>(n_tiles) * heads;
 
@@ -140,7 +142,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
       uint32_t n_q = 0, n_k = 0, n_v = 0;
       bool ok = true;
       for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int tile = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+        const int tile = static_cast<int>(w % n_tiles), h = static_cast<int>(w / n_tiles);
         const int* t = table + 2 + 4 * tile;
         const int q_start = t[0], doc_start = t[1], qt = t[3];
         const int col_q = h * 3 * HD, col_k = col_q + HD, col_v = col_q + 2 * HD;
@@ -202,7 +204,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
         return true;
       };
       for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int tile = static_cast<int>(w / heads);
+        const int tile = static_cast<int>(w % n_tiles);
         const int qt = table[2 + 4 * tile + 3];
         if (!mbar_wait(q_full, n_q & 1, abort_flag)) { ok = false; break; }
         // the previous work item's epilogue must have drained O before PV_0 overwrites it
@@ -245,7 +247,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict_
     bool ok = true;
     auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory"); };
     for (long w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-      const int tile = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
+      const int tile = static_cast<int>(w % n_tiles), h = static_cast<int>(w / n_tiles);
       const int* t = table + 2 + 4 * tile;
       const int q_start = t[0], doc_end = t[2], qt = t[3];
       const int q_idx = q_start + row;

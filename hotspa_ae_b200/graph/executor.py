@@ -69,11 +69,15 @@ class ExecPlan:
     fused_linear: dict = field(default_factory=dict)    # linear op id -> ("ag" | "rs", group ranks)
 
 
+SIDE_EFFECT_OPS = {"sgd_update"}
+
+
 class Runtime:
     """What op implementations see while they compute."""
 
     def __init__(self, ex: "Executor", plan: ExecPlan):
         self.ex, self.plan = ex, plan
+        self.wanted_side_effects: set = set()
         self.strategy_id = plan.sid
         self.training = True
         self.mesh = ex.mesh
@@ -481,6 +485,10 @@ class Executor:
     def _run_ops(self, rt, ops, values, feeds, params, sid):
         timing = self.profile_ops and self.mesh.torch_device.type == "cuda"
         for op in ops:
+            # ops that change persistent state run only when a fetch depends on them (everything else in the graph
+            # runs every time: it is the training program of this rank)
+            if op.type in SIDE_EFFECT_OPS and op.id not in rt.wanted_side_effects:
+                continue
             ins = [self._value(t, values, feeds, params, sid) for t in op.inputs]
             if timing:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -550,6 +558,22 @@ class Executor:
                 values[i] = v
         return values
 
+    def _side_effects_behind(self, fetches) -> set:
+        """Ids of the state-changing ops that the fetched tensors depend on."""
+        if not any(op.type in SIDE_EFFECT_OPS for op in self.graph.ops):
+            return set()
+        found, seen = set(), set()
+        stack = [f.producer for f in fetches if getattr(f, "producer", None) is not None]
+        while stack:
+            op = stack.pop()
+            if op.id in seen:
+                continue
+            seen.add(op.id)
+            if op.type in SIDE_EFFECT_OPS:
+                found.add(op.id)
+            stack += [t.producer for t in op.inputs if t.producer is not None]
+        return found
+
     def _recompute_on(self, sid: int) -> bool:
         rs = getattr(self.graph, "recompute_strategies", None)
         return rs is None or sid in rs
@@ -586,10 +610,12 @@ class Executor:
         if run_level == ALLOC:
             return []
         rt = Runtime(self, plan)
+        rt.wanted_side_effects = self._side_effects_behind(fetches)
         params = self.store.param_views(sid)
         feeds = self._split_feeds(feed_dict, nmb) if nmb > 0 else []
         wants_train = any(getattr(f, "is_train_op", False) for f in fetches) or loss is not None
-        loss_t = loss if loss is not None else next((f for f in fetches if not getattr(f, "is_train_op", False)), None)
+        loss_t = loss if loss is not None else next(
+            (f for f in fetches if not getattr(f, "is_train_op", False) and not getattr(f, "is_grad_handle", False)), None)
         n_stage = len(plan.stages)
         stage = plan.my_stage
         if stage < 0:
@@ -599,7 +625,8 @@ class Executor:
             (C.schedule_1f1b if self.pipeline_schedule == "1f1b" else C.schedule_gpipe)(n_stage, stage, nmb)
         live: dict[int, dict] = {}
         losses: dict[int, torch.Tensor] = {}
-        fetched: dict[int, list] = {f.id: [None] * nmb for f in fetches if not getattr(f, "is_train_op", False)}
+        fetched: dict[int, list] = {f.id: [None] * nmb for f in fetches
+                                    if not getattr(f, "is_train_op", False) and not getattr(f, "is_grad_handle", False)}
         pending_sends: list = []
         dev = self.mesh.torch_device
 
@@ -669,6 +696,13 @@ class Executor:
         if pending_sends:
             PC.p2p_exchange(pending_sends, [])
 
+        # gradient handles: this rank's accumulator as it stands after backward (before any reduction / update)
+        grad_fetch = {}
+        for f in fetches:
+            if getattr(f, "is_grad_handle", False):
+                gv = self.store.local_grad(f.var, sid)
+                grad_fetch[f.id] = None if gv is None else gv.detach().clone()
+
         if wants_train and run_level == GRAD:
             self.store.hand_grads_home(sid)
         if wants_train and run_level == UPDATE:
@@ -695,6 +729,9 @@ class Executor:
         for f in fetches:
             if getattr(f, "is_train_op", False):
                 out.append(None)
+                continue
+            if getattr(f, "is_grad_handle", False):
+                out.append(grad_fetch.get(f.id))
                 continue
             vals = [v for v in fetched.get(f.id, []) if v is not None]
             if not vals:

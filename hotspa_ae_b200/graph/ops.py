@@ -830,6 +830,30 @@ def group(tensors, name=None):
     return make_op_front("group", list(tensors), {}, name)[0]
 
 
+@register("sgd_update")
+class _SGDUpdate:
+    """param -= lr * grad, in place on the parameter's storage (master and compute copies); the output is the
+    updated parameter (reference: SGDUpdateOp, hetu/graph/ops/optimizer_update.cc:58-80)."""
+
+    @staticmethod
+    def infer(inputs, attrs):
+        return [(inputs[0].symbolic_shape, inputs[0].dtype)]
+    deduce = _same_as_input(0)
+
+    @staticmethod
+    def compute(rt, op, vals):
+        param = op.inputs[0]
+        if not param.is_parameter:
+            raise ValueError("sgd_update: the first input must be a parameter")
+        with torch.no_grad():
+            rt.ex.store.apply_local_update(param, vals[1].detach(), -float(op.attrs["lr"]))
+        return [vals[0]]
+
+
+def sgd_update(param, grad, lr, name=None):
+    return make_op_front("sgd_update", [param, grad], {"lr": float(lr)}, name)[0]
+
+
 @register("where")
 class _Where:
     @staticmethod

@@ -10,17 +10,53 @@ from ..graph import ops as O
 from ..ops import _lib
 
 
+class GradHandle:
+    """Fetchable stand-in for "the gradient of the loss with respect to `var`"."""
+    is_grad_handle = True
+    is_train_op = False
+
+    def __init__(self, var):
+        self.var = var
+        self.graph = var.graph
+        self.id = ("grad", var.id)
+        self.name = f"grad({var.name})"
+
+    def __repr__(self):
+        return f"GradHandle({self.var.name})"
+
+
 class Optimizer:
     def __init__(self, lr: float):
         self.lr = lr
         self.loss = None
 
     def minimize(self, loss, var_list=None, name=None):
+        """compute_gradients + apply_gradients (reference: Optimizer::Minimize, hetu/graph/optim/optimizer.cc)."""
+        return self.apply_gradients(self.compute_gradients(loss, var_list), name=name)
+
+    def compute_gradients(self, loss, var_list=None):
+        """[(gradient handle, variable)] for the trainable parameters `loss` depends on (or `var_list`).  A handle
+        can be fetched in the same `graph.run` as the train op: it yields this rank's fp32 gradient accumulator of
+        the variable as it stands after the backward pass (before the data-parallel reduction and the update)."""
         g = loss.graph
         self.loss = loss
-        self.var_list = var_list
+        params = [p for p in (var_list if var_list is not None else g.parameters) if p.requires_grad]
+        self.var_list = None if var_list is None else list(params)
+        return [(GradHandle(p), p) for p in params]
+
+    def apply_gradients(self, grads_and_vars, name=None):
+        """The train op that reduces the gradients and updates the variables at run level "update"."""
+        pairs = list(grads_and_vars)
+        if not pairs:
+            raise ValueError("apply_gradients: no variables")
+        if self.loss is None:
+            raise RuntimeError("apply_gradients needs the pairs returned by compute_gradients")
+        for gh, v in pairs:
+            if not isinstance(gh, GradHandle) or gh.var is not v:
+                raise ValueError("apply_gradients takes the (gradient, variable) pairs made by compute_gradients")
+        g = self.loss.graph
         g.optimizer = self
-        train_op = O.group([loss], name=name or "train_op")
+        train_op = O.group([self.loss], name=name or "train_op")
         train_op.is_train_op = True
         g.train_op = train_op
         return train_op

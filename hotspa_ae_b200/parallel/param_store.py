@@ -451,6 +451,40 @@ class ParamStore:
             return None
         return self.arena(sid)[e.offset:e.offset + e.numel].view(e.local_shape)
 
+    def local_grad(self, p, sid: int | None = None) -> torch.Tensor | None:
+        """This rank's fp32 gradient accumulator of parameter `p` (a view; before the data-parallel reduction it
+        holds this rank's partial sum only)."""
+        sid = self.home if sid is None else self.canonical(sid)
+        e = self.layout(sid).entries.get(p.id)
+        if e is None or sid not in self.grads:
+            return None
+        return self.grad_arena(sid)[e.offset:e.offset + e.numel].view(e.local_shape)
+
+    def apply_local_update(self, p, delta: torch.Tensor, alpha: float) -> None:
+        """param += alpha * delta on this rank's shard of `p` in the home layout: the fp32 master range this rank
+        owns and the compute copy (every replica applies the same `delta`, so replicas stay equal)."""
+        sid = self.home
+        lay = self.layout(sid)
+        e = lay.entries.get(p.id)
+        if e is None:
+            return
+        flat = delta.reshape(-1).to(self.device, torch.float32)
+        seg = self.arena(sid)[e.offset:e.offset + e.numel]
+        c = lay.classes[e.cls]
+        lo, hi = self._owned_range(c, self.zero_enabled(sid))
+        a, b = max(lo, e.offset), min(hi, e.offset + e.numel)
+        if a < b:
+            m = self.master[e.cls][a - lo:b - lo]
+            m.add_(flat[a - e.offset:b - e.offset], alpha=alpha)
+            seg[a - e.offset:b - e.offset].copy_(m)
+        else:
+            a = b = e.offset
+        for x, y in ((e.offset, a), (b, e.offset + e.numel)):       # ranges whose master lives on another rank
+            if x < y:
+                part = seg[x - e.offset:y - e.offset]
+                part.copy_(part.float().add_(flat[x - e.offset:y - e.offset], alpha=alpha))
+        self.valid = {sid}
+
     def load_global(self, p, array: torch.Tensor) -> None:
         """Overwrite parameter `p` from its global value (home layout; master and compute copies)."""
         sid = self.home

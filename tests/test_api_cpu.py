@@ -112,3 +112,37 @@ def test_graph_registry_and_context_arguments():
         ht.placeholder(ht.float32, [2], name="x")
     with pytest.raises(RuntimeError):
         n.set_num_strategy(2)
+
+
+def test_compute_apply_gradients_and_sgd_update_op():
+    from hotspa_ae_b200.graph import init as I
+    from hotspa_ae_b200.parallel import mesh as M
+    M.reset_mesh()
+    ht.init_comm_group(8)
+    rng = np.random.default_rng(0)
+    xs = rng.standard_normal((4, 3)).astype(np.float32)
+    with ht.graph("define_and_run") as g:
+        x = ht.placeholder(ht.float32, [4, 3], name="x")
+        w = ht.parallel_parameter(I.normal_initializer(0.0, 0.5), [2, 3], [ht.DistributedStatesUnion(
+            [ht.DistributedStates(1, {-1: 1}, [-1])])], None, name="w")
+        y = ht.linear(x, w, trans_b=True)
+        loss = ht.reduce_sum(y * y)
+        opt = ht.SGDOptimizer(lr=0.1)
+        pairs = opt.compute_gradients(loss)
+        assert len(pairs) == 1 and pairs[0][1] is w
+        train_op = opt.apply_gradients(pairs)
+        stepped = ht.sgd_update(w, w * 0.0 + 1.0, 0.25)        # w -= 0.25 * ones, as a graph op
+    g.run(loss, [loss, train_op], {x: xs}, 1, 0, ht.run_level("alloc"))
+    w0 = np.array(w.get_data())
+    out = g.run(loss, [loss, pairs[0][0], train_op], {x: xs}, 1, 0, ht.run_level("update"))
+    wt = torch.tensor(w0, requires_grad=True)
+    ref = ((torch.tensor(xs) @ wt.T) ** 2).sum()
+    ref.backward()
+    np.testing.assert_allclose(np.asarray(out[0]).reshape(-1)[0], float(ref.detach()), rtol=1e-5)
+    np.testing.assert_allclose(out[1].numpy(), wt.grad.numpy(), rtol=1e-5, atol=1e-6)      # fetched gradient
+    w1 = np.array(w.get_data())
+    np.testing.assert_allclose(w1, w0 - 0.1 * wt.grad.numpy(), rtol=1e-5, atol=1e-6)        # applied update
+    g.run(None, [stepped], {x: xs}, 1, 0, ht.run_level("grad"))     # the whole program runs; only now with the update op
+    np.testing.assert_allclose(np.array(w.get_data()), w1 - 0.25, rtol=1e-6, atol=1e-6)
+    with pytest.raises(ValueError):
+        opt.apply_gradients([(loss, w)])

@@ -33,6 +33,9 @@ NvmlProfiler = _C.NvmlProfiler
 classify_comm = _C.classify_comm
 comm_type_name = _C.comm_type_name
 split_comm_groups = _C.split_comm_groups
+run_barrier_model = _C.run_barrier_model
+run_reduce_scatter_model = _C.run_reduce_scatter_model
+run_all_gather_model = _C.run_all_gather_model
 deduce_linear = _C.deduce_linear
 regions_of = _C.regions_of
 schedule_1f1b = _C.schedule_1f1b

@@ -5,6 +5,7 @@
 #include "ds.h"
 #include "nvml_profiler.h"
 #include "planner.h"
+#include "signal_model.h"
 #include "symbol.h"
 
 namespace py = pybind11;
@@ -70,6 +71,30 @@ PYBIND11_MODULE(_hsb_core, m) {
   m.def("classify_comm", &classify_comm, py::arg("src"), py::arg("src_group"), py::arg("dst"), py::arg("dst_group"),
         py::arg("member") = 0);
   m.def("comm_type_name", &comm_type_name);
+  // host model of the cross-GPU flag protocols (threads + atomics); the GIL is released while the ranks run
+  auto as_dict = [](const ModelResult& r) {
+    py::dict d;
+    d["checks"] = r.checks; d["violations"] = r.violations; d["timeouts"] = r.timeouts;
+    return d;
+  };
+  m.def("run_barrier_model", [as_dict](int n, int calls, uint32_t first_epoch, uint64_t seed) {
+    ModelResult r;
+    { py::gil_scoped_release rel; r = run_barrier_model(n, calls, first_epoch, seed); }
+    return as_dict(r);
+  }, py::arg("n"), py::arg("calls"), py::arg("first_epoch") = 1u, py::arg("seed") = 0);
+  m.def("run_reduce_scatter_model", [as_dict](int n, int calls, int counter_sets, int recv_buffers, int row_blocks,
+                                              int parts, uint64_t seed) {
+    ModelResult r;
+    { py::gil_scoped_release rel;
+      r = run_reduce_scatter_model(n, calls, counter_sets, recv_buffers, row_blocks, parts, seed); }
+    return as_dict(r);
+  }, py::arg("n"), py::arg("calls"), py::arg("counter_sets") = 3, py::arg("recv_buffers") = 2,
+     py::arg("row_blocks") = 4, py::arg("parts") = 4, py::arg("seed") = 0);
+  m.def("run_all_gather_model", [as_dict](int n, int calls, int stage_buffers, int chunks, uint64_t seed) {
+    ModelResult r;
+    { py::gil_scoped_release rel; r = run_all_gather_model(n, calls, stage_buffers, chunks, seed); }
+    return as_dict(r);
+  }, py::arg("n"), py::arg("calls"), py::arg("stage_buffers") = 2, py::arg("chunks") = 8, py::arg("seed") = 0);
   py::class_<SplitCommPlan>(m, "SplitCommPlan")
       .def_readonly("split_dim", &SplitCommPlan::split_dim)
       .def_readonly("micro_blocks", &SplitCommPlan::micro_blocks)

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from ..core import ReshardPlanner, regions_of
+from . import guards
 from . import mesh as M
 
 ALIGN = 256  # elements; keeps every tensor 512-byte aligned in bf16 and 16-byte rules for TMA trivially true
@@ -111,6 +112,7 @@ class ParamStore:
         self.sender_policy = 3
         self.seed = 2023
         self.symm = None
+        self._guards = None
         self._canon: dict[int, int] = {}
 
     # ---- layouts / arenas ------------------------------------------------------------------------
@@ -131,7 +133,18 @@ class ParamStore:
     def _alloc(self, numel: int, dtype) -> torch.Tensor:
         if self.symm is not None:
             return self.symm.alloc(numel, dtype)
+        if guards.enabled():
+            if self._guards is None:
+                self._guards = guards.GuardedAlloc()
+            return self._guards.alloc(f"arena #{len(self._guards.guards)} ({numel} x {dtype})", numel, dtype, self.device)
         return torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+
+    def check_canaries(self) -> None:
+        """Debug mode (HSB_DEBUG_CANARIES=1): raise if anything wrote past the end of an arena."""
+        if self._guards is not None:
+            self._guards.check()
+        if self.symm is not None:
+            self.symm.check_canaries()
 
     def canonical(self, sid: int) -> int:
         """Strategies whose parameters have identical distributed states and device groups share arenas

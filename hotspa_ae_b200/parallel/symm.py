@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
+from . import guards
 from . import mesh as M
 
 c_void_p, c_int, c_u32, c_u64, c_i64, c_float = (ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64,
@@ -77,6 +78,7 @@ class SymmHeap:
         self.rank, self.world = self.mesh.rank, self.mesh.world_size
         self.device = self.mesh.torch_device
         self.buffers: list[SymmBuffer] = []
+        self._guards = guards.GuardedAlloc()
         self._by_ptr: dict[int, SymmBuffer] = {}
         self._epoch: dict[tuple, int] = {}
         self._slots: dict[tuple, int] = {}
@@ -90,7 +92,8 @@ class SymmHeap:
         nbytes = (nbytes + 255) // 256 * 256
         ranks = list(range(self.world)) if ranks is None else list(ranks)
         ptr = c_void_p()
-        _lib.check(_lib.lib().hsb_symm_malloc(nbytes, ctypes.byref(ptr)), "hsb_symm_malloc")
+        guard = guards.GUARD_BYTES if guards.enabled() else 0      # debug mode: a painted tail behind every buffer
+        _lib.check(_lib.lib().hsb_symm_malloc(nbytes + guard, ctypes.byref(ptr)), "hsb_symm_malloc")
         handle = (ctypes.c_ubyte * 64)()
         _lib.check(_lib.lib().hsb_ipc_get_handle(ptr, handle), "hsb_ipc_get_handle")
         mine = (bytes(handle), nbytes)
@@ -109,11 +112,17 @@ class SymmHeap:
             buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
             _lib.check(_lib.lib().hsb_ipc_open_handle(buf, ctypes.byref(out)), "hsb_ipc_open_handle")
             bases[r] = out.value
-        t = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=self.device)
+        t = torch.as_tensor(_RawCuda(ptr.value, nbytes + guard), device=self.device)
+        if guard:
+            t = self._guards.wrap_bytes(f"symmetric buffer #{len(self.buffers)} ({nbytes} bytes)", t, nbytes)
         sb = SymmBuffer(t, ptr.value, nbytes, bases, sizes)
         self.buffers.append(sb)
         self._by_ptr[ptr.value] = sb
         return sb
+
+    def check_canaries(self) -> None:
+        """Debug mode (HSB_DEBUG_CANARIES=1): raise if anything, a peer included, wrote past the end of a buffer."""
+        self._guards.check()
 
     def alloc_group(self, nbytes: int, ranks) -> SymmBuffer:
         """Collective over `ranks` only: a byte buffer visible to those ranks."""
@@ -220,6 +229,13 @@ class SymmHeap:
             arr[i] = (s_ptr, d_ptr, r, rb, sld, dld)
             unit_rows[i] = ur
             prefix[i + 1] = prefix[i] + (r + ur - 1) // ur
+        if guards.enabled():
+            sbuf = self.buffer_of(s_arena)
+            extents = {r: (sbuf.peer_bases[r], sbuf.sizes[r]) for r in sbuf.peer_bases}
+            errs = guards.validate_descriptors(arr, extents, (d_arena.data_ptr(), d_arena.numel() * esz), esz,
+                                               copy=(kind == "param"))
+            if errs:
+                raise RuntimeError(f"reshard descriptors {src}->{dst} ({kind}) are invalid:\n  " + "\n  ".join(errs))
         out = dict(descs=torch.from_numpy(arr).to(self.device), prefix=torch.from_numpy(prefix).to(self.device),
                    unit_rows=torch.from_numpy(unit_rows).to(self.device), n_desc=nd, n_units=int(prefix[-1]))
         self._desc_cache[key] = out

@@ -30,6 +30,7 @@ import hetu as ht
 
 from ..models.llama import LlamaConfig, LlamaLMHeadModel, llama_config
 from ..parallel import mesh as M
+from ..parallel import guards
 from ..parallel.strategy_config import generate_llama_3d_config, propagate_zero, read_ds_parallel_config
 from ..utils import data as D
 
@@ -266,6 +267,8 @@ class HotSwitchTrainer:
             self.last_profile = dict(bucket_ms=spans, switches=sw)
         del store.switch_log[:max(0, len(store.switch_log) - 64)]
         self.step_count += 1
+        if guards.enabled():
+            store.check_canaries()       # debug mode: nothing may have written past the end of an arena
         t_h = time.perf_counter()
         loss = self._collect_loss(total_targets) if read_loss else float("nan")
         if prof:

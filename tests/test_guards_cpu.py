@@ -1,0 +1,70 @@
+"""Debug-mode memory checks: arena canaries and reshard descriptor validation (host side)."""
+import numpy as np
+import pytest
+import torch
+
+from hotspa_ae_b200.parallel import guards
+
+
+def test_guarded_allocation_detects_a_write_past_the_end():
+    ga = guards.GuardedAlloc()
+    a = ga.alloc("arena a", 1000, torch.float32, "cpu")
+    b = ga.alloc("arena b", 7, torch.bfloat16, "cpu")
+    assert a.numel() == 1000 and b.numel() == 7 and float(a.abs().sum()) == 0
+    a.fill_(3.0)
+    b.fill_(1.0)
+    ga.check()
+    raw = torch.as_strided(b.view(torch.uint8), (b.numel() * 2 + 40,), (1,))   # a stray write 20-odd bytes past the end
+    raw[-1] = 0
+    with pytest.raises(RuntimeError, match="arena b"):
+        ga.check()
+
+
+def test_trainer_checks_canaries_every_step(monkeypatch):
+    monkeypatch.setenv("HSB_DEBUG_CANARIES", "1")
+    from hotspa_ae_b200.parallel import mesh as M
+    from hotspa_ae_b200.train.trainer import HotSwitchTrainer
+    from hotspa_ae_b200.utils import data as D
+    M.reset_mesh()
+    tr = HotSwitchTrainer("tiny", [(1, 1, 1, False)], (256, 0), lr=1e-3, dtype=torch.float32, recompute=False,
+                          max_seq_len=256)
+    seqs = D.synthetic_sequences(D.lognormal_lengths(1024, seed=0, max_len=256), tr.config.vocab_size, seed=0)
+    tr.step(seqs)                                            # clean step: guards intact
+    store = tr.graph.executor.store
+    assert store._guards is not None and len(store._guards.guards) >= 2
+    name, guard = store._guards.guards[0]
+    guard[5] = 0
+    with pytest.raises(RuntimeError, match="memory guard"):
+        tr.step(seqs)
+
+
+def _desc(sp, dp, rows, rb, sld=0, dld=0):
+    return [sp, dp, rows, rb, sld, dld]
+
+
+def test_descriptor_validation():
+    src = {0: (0x10000, 4096), 1: (0x90000, 8192)}
+    dst = (0x200000, 16384)
+    good = np.array([
+        _desc(0x10000, 0x200000, 1, 4096),                       # one long row
+        _desc(0x90000, 0x201000, 4, 512, 2048, 1024),            # strided rectangle: 4 rows of 512 bytes
+        _desc(0x90200, 0x201200, 4, 512, 2048, 1024),            # its neighbour columns: rows interleave, no overlap
+    ], dtype=np.int64)
+    assert guards.validate_descriptors(good, src, dst, 2, copy=True) == []
+    # source runs off the end of rank 0's arena
+    errs = guards.validate_descriptors(np.array([_desc(0x10800, 0x200000, 1, 4096)]), src, dst, 2, True)
+    assert len(errs) == 1 and "no source arena" in errs[0]
+    # destination leaves the arena
+    errs = guards.validate_descriptors(np.array([_desc(0x90000, 0x203f00, 1, 512)]), src, dst, 2, True)
+    assert len(errs) == 1 and "leaves the arena" in errs[0]
+    # misaligned for fp32 gradients
+    errs = guards.validate_descriptors(np.array([_desc(0x10002, 0x200000, 1, 64)]), src, dst, 4, False)
+    assert len(errs) == 1 and "multiple of 4" in errs[0]
+    # two copies that write the same bytes; adds may (several partial sums land on one holder)
+    clash = np.array([_desc(0x10000, 0x200000, 1, 1024), _desc(0x90000, 0x200200, 1, 1024)], dtype=np.int64)
+    errs = guards.validate_descriptors(clash, src, dst, 2, copy=True)
+    assert len(errs) == 1 and "overlap" in errs[0]
+    assert guards.validate_descriptors(clash, src, dst, 2, copy=False) == []
+    # leading dimension shorter than the row
+    errs = guards.validate_descriptors(np.array([_desc(0x90000, 0x200000, 2, 512, 256, 512)]), src, dst, 2, True)
+    assert any("leading dimension" in e for e in errs)

@@ -19,6 +19,7 @@ parallel/symm.py).  Reference policy for what lives where: hetu/graph/define_and
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 
@@ -109,7 +110,14 @@ class ParamStore:
         self.switch_mode = "nccl"
         self.plans: dict = {}
         self.switch_log: list[dict] = []
-        self.sender_policy = 3
+        # who sends a slice that several ranks hold (reference: HETU_SWITCH_ALGORITHM, switch_exec_graph.h:511-530).
+        # On one NVSwitch box every peer is equally near, so both round-robin spellings and both greedy spellings of
+        # the reference map onto one policy each; the default balances the bytes sent per rank.
+        names = {"FCFS": 0, "ROUND_ROBIN": 1, "MULTI_NODE_ROUND_ROBIN": 1, "GREEDY": 2, "NEW_GREEDY": 3, "BALANCED": 3}
+        algo = os.environ.get("HETU_SWITCH_ALGORITHM", "NEW_GREEDY").upper()
+        if algo not in names:
+            raise ValueError(f"HETU_SWITCH_ALGORITHM={algo}: expected one of {sorted(names)}")
+        self.sender_policy = names[algo]
         self.seed = 2023
         self.symm = None
         self._guards = None

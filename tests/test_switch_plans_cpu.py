@@ -57,3 +57,19 @@ def test_gradient_plan_into_home_takes_every_replica_once():
     moved = plan["remote_elems"] + plan["local_elems"]
     # each parameter element is sent by its 8 holders to exactly one home holder
     assert moved == total * 8
+
+
+@pytest.mark.parametrize("algo", ["FCFS", "ROUND_ROBIN", "GREEDY", "NEW_GREEDY"])
+def test_switch_algorithm_env_selects_the_sender_policy(algo, monkeypatch):
+    monkeypatch.setenv("HETU_SWITCH_ALGORITHM", algo)
+    g = _graph(0)
+    store = ParamStore(g)
+    plan = store._plan(0, 1, "param")                      # tp4pp2 -> dp2tp2pp2: several holders per slice
+    sent = np.array(plan["sent_elems"])
+    assert sent.sum() == plan["remote_elems"] > 0
+    if algo == "NEW_GREEDY":
+        busy = sent[sent > 0]
+        assert busy.max() <= 1.6 * busy.mean()
+    monkeypatch.setenv("HETU_SWITCH_ALGORITHM", "nonsense")
+    with pytest.raises(ValueError):
+        ParamStore(g)

@@ -89,8 +89,12 @@ class Mesh:
             self.torch_device = torch.device("cpu")
 
     def device_of(self, rank: int) -> Device:
-        return Device(index=rank, local_index=rank % max(1, self.gpus_per_node),
-                      type="cuda" if self.use_cuda else "cpu")
+        # one node per `gpus_per_node` ranks; this node's name comes from HETU_LOCAL_HOSTNAME like the reference's
+        # (hetu/core/device.h:137), the other nodes are numbered
+        per = max(1, self.gpus_per_node)
+        node, my_node = rank // per, self.rank // per
+        host = os.environ.get("HETU_LOCAL_HOSTNAME", "localhost") if node == my_node else f"node{node}"
+        return Device(index=rank, local_index=rank % per, hostname=host, type="cuda" if self.use_cuda else "cpu")
 
     def local_device(self) -> Device:
         return self.device_of(self.rank)

@@ -14,7 +14,6 @@ space of one node with exact dynamic programming for the layer split and proport
 """
 from __future__ import annotations
 
-import itertools
 from dataclasses import dataclass, field
 
 import numpy as np

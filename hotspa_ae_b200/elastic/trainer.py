@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import time
 
-import numpy as np
 import torch
 
 import hetu as ht

@@ -13,7 +13,6 @@ from __future__ import annotations
 
 import json
 import os
-import time
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -21,7 +20,6 @@ import torch
 import torch.utils.checkpoint as ckpt
 
 from .. import core as C
-from ..ops import _lib
 from ..ops.gemm import linear as gemm_linear
 from ..parallel import comm as PC
 from ..parallel import mesh as M

@@ -18,10 +18,10 @@ from typing import Any
 import numpy as np
 import torch
 
-from ..core import DistributedStates, DistributedStatesUnion, IntSymbol, classify_comm, sym_value
+from ..core import DistributedStates, DistributedStatesUnion
 from ..parallel import mesh as M
 from . import ops as O
-from .tensor import Op, Tensor, as_symbol
+from .tensor import Op, Tensor
 
 RUN_LEVELS = {"update": 0, "grad": 1, "alloc": 2, "topo": 3}
 UPDATE, GRAD, ALLOC, TOPO = 0, 1, 2, 3

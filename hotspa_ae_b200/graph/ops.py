@@ -18,7 +18,7 @@ from typing import Any, Callable
 import numpy as np
 import torch
 
-from ..core import DistributedStates, DistributedStatesUnion, IntSymbol, deduce_linear, sym_value
+from ..core import DistributedStates, IntSymbol, deduce_linear, sym_value
 from ..ops import functional as Fn
 from ..ops.attention import attention_varlen
 from .tensor import Tensor, as_symbol

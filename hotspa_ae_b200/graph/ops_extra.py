@@ -16,7 +16,6 @@ import torch.nn.functional as F
 from ..core import DistributedStates, IntSymbol
 from . import ops as O
 from .ops import make_op_front, register
-from .tensor import Tensor
 
 
 def _batch_only_ds(ds: DistributedStates, out_ndim: int) -> DistributedStates:

@@ -10,7 +10,6 @@ from __future__ import annotations
 
 import numbers
 
-import numpy as np
 
 from .. import core as C
 from ..graph import graph as G

@@ -15,8 +15,6 @@ import math
 
 import torch
 
-from . import _lib
-
 
 def _attn_torch_fwd(qkv, cu, heads, hd, scale):
     T = qkv.shape[0]

@@ -16,11 +16,7 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 import sys
-
-import numpy as np
-import torch
 
 from ..parallel import mesh as M
 from ..utils import data as D

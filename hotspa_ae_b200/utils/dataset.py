@@ -13,7 +13,6 @@ from __future__ import annotations
 import json
 import os
 import pickle
-from types import SimpleNamespace
 
 import numpy as np
 

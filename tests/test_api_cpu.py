@@ -1,10 +1,9 @@
 """API surface on one CPU process: eager / define-by-run graphs, plain nn layers with an optimizer, GradScaler,
 streams and events, logging, profiler hooks."""
 import json
-import os
 
-import pytest
 import numpy as np
+import pytest
 import torch
 
 import hetu as ht

@@ -18,13 +18,24 @@ def _free_port():
     return p
 
 
-def run_workers(world, strategies, plan, extra=()):
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"),
-           "--strategies", json.dumps(strategies), "--plan", json.dumps(plan), *extra]
+def _torchrun(script, world, args=(), marker=None, timeout=900):
+    """Run tests/<script> on `world` gloo ranks.  The rendezvous port is picked by binding port 0 and releasing it, so
+    another process can take it before torchrun binds: a failed launch is repeated once on a fresh port, and the
+    output of both attempts is shown if the second one fails too."""
     env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
-    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900, env=env)
-    assert proc.returncode == 0, proc.stdout[-4000:]
+    outputs = []
+    for _ in range(2):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, script), *args]
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env)
+        if proc.returncode == 0 and (marker is None or marker in proc.stdout):
+            return proc.stdout
+        outputs.append(proc.stdout[-3000:])
+    raise AssertionError("\n======== second attempt ========\n".join(outputs))
+
+
+def run_workers(world, strategies, plan, extra=()):
+    _torchrun("dist_worker.py", world, ["--strategies", json.dumps(strategies), "--plan", json.dumps(plan), *extra])
 
 
 @pytest.mark.parametrize("world,strategy", [
@@ -47,24 +58,12 @@ def test_hot_switch_three_strategies():
 
 
 def test_activation_repartition_between_groups_with_different_layouts():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
-           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "repartition_worker.py")]
-    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
-    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
-    assert proc.returncode == 0, proc.stdout[-3000:]
+    _torchrun("repartition_worker.py", 4, timeout=600)
 
 
 def test_heterogeneous_split_collectives():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
-           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "split_comm_worker.py")]
-    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
-    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
-    assert proc.returncode == 0 and "SPLIT_COMM_OK" in proc.stdout, proc.stdout[-4000:]
+    _torchrun("split_comm_worker.py", 4, marker="SPLIT_COMM_OK", timeout=600)
 
 
 def test_communication_group_verbs():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
-           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "comm_group_worker.py")]
-    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
-    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
-    assert proc.returncode == 0 and "COMM_GROUP_OK" in proc.stdout, proc.stdout[-4000:]
+    _torchrun("comm_group_worker.py", 4, marker="COMM_GROUP_OK", timeout=600)

@@ -6,7 +6,6 @@ import subprocess
 import sys
 import time
 
-import numpy as np
 import pytest
 
 from hotspa_ae_b200.elastic.straggler import Heartbeat, StepTimeWindow, Straggler, WorkloadInfo

@@ -1,5 +1,4 @@
 """Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op (needs a B200)."""
-import math
 
 import pytest
 import torch

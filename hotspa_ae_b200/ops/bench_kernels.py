@@ -157,6 +157,9 @@ def bench_bandwidth(args):
     dy = torch.randn_like(y)
     report("rmsnorm bwd", time_ms(lambda: torch.autograd.grad(y, xr, dy, retain_graph=True), args.iters),
            3 * x.numel() * 2)
+    if args.only == "norm":          # small working set for profiler captures
+        _lib.check_status()
+        return
     gu = torch.randn(rows, 2 * F_, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     report("swiglu fwd", time_ms(lambda: Fn.swiglu(gu.detach()), args.iters), 3 * rows * F_ * 2)
     so = Fn.swiglu(gu)
@@ -194,6 +197,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--only", default="", choices=["", "norm"], help="bandwidth: run only this group of kernels")
     ap.add_argument("--no_torch", action="store_true", help="skip the library comparison (profiling runs)")
     args = ap.parse_args()
     {"gemm": bench_gemm, "attn": bench_attn, "bandwidth": bench_bandwidth}[args.what](args)

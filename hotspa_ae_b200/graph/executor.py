@@ -42,6 +42,7 @@ class CommInfo:
     dst_peer: int = -1      # for P2P: the rank we send to
     fused: bool = False     # the neighbouring linear op performs this collective inside its GEMM kernel
     repartition: bool = False   # boundary op whose pieces come from the reshard planner (layouts differ)
+    split_groups: list = field(default_factory=list)    # hetero collectives: rank groups per micro-block
 
 
 @dataclass
@@ -134,6 +135,12 @@ class Runtime:
             return PC.AllReduce.apply(x, group)
         if k in (C._C.COMM_SPLIT, C._C.COMM_SCATTER):
             return PC.SplitLocal.apply(x, group, info.dim, info.index, info.count)
+        if k == C._C.COMM_SPLIT_ALL_REDUCE:
+            return PC.SplitAllReduce.apply(x, info.split_groups, info.dim)
+        if k == C._C.COMM_SPLIT_ALL_GATHER:
+            return PC.SplitAllGather.apply(x, info.split_groups, info.dim)
+        if k == C._C.COMM_SPLIT_REDUCE_SCATTER:
+            return PC.SplitReduceScatter.apply(x, info.split_groups, info.dim)
         raise NotImplementedError(f"comm type {info.name} inside a stage is not implemented")
 
 
@@ -170,7 +177,8 @@ class Executor:
 
     # ---- planning ---------------------------------------------------------------------------------------
     def _placement(self, op, sid):
-        return op.outputs[0].dg_hierarchy[sid]
+        groups = op.outputs[0].dg_hierarchy[sid]
+        return groups if len(groups) <= 1 else [op.outputs[0].group(sid)]
 
     def _on_me(self, groups) -> bool:
         return any(g.contains(self.mesh.rank) for g in groups)
@@ -180,8 +188,13 @@ class Executor:
             return self.plans[sid]
         g, rank = self.graph, self.mesh.rank
         stages: list[tuple] = []
+        self._note_pipelines(sid)
+        my_pipe = g.pipeline_of.get((sid, rank), 0)
 
         def note(groups):
+            # the members of a heterogeneous union are separate pipelines: this rank's stages come from its own
+            if len(groups) > 1:
+                groups = [groups[min(my_pipe, len(groups) - 1)]]
             for grp in groups:
                 r = tuple(grp.ranks())
                 if r not in stages:
@@ -202,9 +215,16 @@ class Executor:
                 continue
             if op.type == "comm":
                 x, y = op.inputs[0], op.outputs[0]
-                sg, dg = x.dg_hierarchy[sid], y.dg_hierarchy[sid]
-                s_ranks, d_ranks = sg[0].ranks(), dg[0].ranks()
-                kind = C.classify_comm(x.ds_hierarchy[sid], s_ranks, y.ds_hierarchy[sid], d_ranks, 0)
+                s_ranks, d_ranks = x.group(sid).ranks(), y.group(sid).ranks()
+                su, du = x.ds_hierarchy[sid], y.ds_hierarchy[sid]
+                if su.hetero_dim != du.hetero_dim:
+                    # the hetero dimension changes: a collective across the members of the union
+                    comm[op.id] = self._plan_split_comm(op, sid, needed)
+                    if rank in s_ranks:
+                        my_ops.append(op)
+                    continue
+                one = C.DistributedStatesUnion
+                kind = C.classify_comm(one([x.ds(sid)]), s_ranks, one([y.ds(sid)]), d_ranks, 0)
                 name = C.comm_type_name(kind)
                 if kind == C._C.COMM_UNSUPPORTED:
                     raise RuntimeError(f"{op}: no collective realises {x.ds(sid)} -> {y.ds(sid)}")
@@ -233,12 +253,20 @@ class Executor:
                     comm[op.id] = info
                     continue
                 # every rank computes every rank's collective group so that groups are created collectively
-                sds, dds = x.ds(sid), y.ds(sid)
-                for idx in range(len(s_ranks)):
-                    ranks_i, dim, index, count = self._collective_group(kind, sds, dds, idx, s_ranks)
-                    needed.append(ranks_i)
-                    if s_ranks[idx] == rank:
-                        comm[op.id] = CommInfo(kind, name, ranks_i, dim, index, count)
+                # (for a heterogeneous union: the groups of every member, each under its own layout)
+                for m, grp_m in enumerate(x.dg_hierarchy[sid]):
+                    ranks_m = grp_m.ranks()
+                    sds, dds = x.ds(sid, m), y.ds(sid, m)
+                    kind_m = kind if ranks_m == s_ranks else C.classify_comm(one([sds]), ranks_m, one([dds]), ranks_m, 0)
+                    if kind_m in (C._C.COMM_UNUSED, C._C.COMM_P2P, C._C.COMM_BATCHED_SEND_RECV, C._C.COMM_UNSUPPORTED):
+                        continue
+                    for idx in range(len(ranks_m)):
+                        ranks_i, dim, index, count = self._collective_group(kind_m, sds, dds, idx, ranks_m)
+                        needed.append(ranks_i)
+                        if ranks_m[idx] == rank:
+                            comm[op.id] = CommInfo(kind, name, ranks_i, dim, index, count)
+                if kind == C._C.COMM_UNUSED and rank in s_ranks:
+                    comm.setdefault(op.id, CommInfo(kind, name))
                 if rank in s_ranks:
                     my_ops.append(op)
                 continue
@@ -246,22 +274,23 @@ class Executor:
                 my_ops.append(op)
             if op.type == "vocab_parallel_cross_entropy":
                 lt = op.inputs[0]
-                lds = lt.ds(sid)
-                if lds.get_dim(1) > 1:
-                    for grp in lt.dg_hierarchy[sid]:
+                for m, grp in enumerate(lt.dg_hierarchy[sid]):
+                    lds = lt.ds(sid, m)
+                    if lds.get_dim(1) > 1:
                         for idx in range(grp.num_devices):
                             needed.append(tuple(lds.get_devices_by_dim(1, idx, grp.ranks())))
             if op.type == "linear":
                 a = op.inputs[0]
-                ads = a.ds(sid)
-                if ads.get_dim(-1) > 1:
-                    for grp in a.dg_hierarchy[sid]:
+                for m, grp in enumerate(a.dg_hierarchy[sid]):
+                    ads = a.ds(sid, m)
+                    if ads.get_dim(-1) > 1:
                         for idx in range(grp.num_devices):
                             needed.append(tuple(ads.get_devices_by_dim(-1, idx, grp.ranks())))
         # gradient reduce classes of every rank
         for r in range(self.mesh.world_size):
             for c in self.store.layout(sid, r).classes:
                 needed.append(tuple(c.ranks))
+        needed += self.store.hetero_sync_groups(sid)
         self.mesh.ensure_groups(needed)
 
         dp = 1
@@ -272,7 +301,11 @@ class Executor:
         # split over replicas (e.g. behind a gather) is not averaged over them
         loss_op_out = getattr(g, "train_op", None)
         if loss_op_out is not None and loss_op_out.producer is not None and loss_op_out.producer.inputs:
-            dp = max(1, loss_op_out.producer.inputs[0].ds(sid).get_dim(0))
+            loss_in = loss_op_out.producer.inputs[0]
+            dp = max(1, loss_in.ds(sid).get_dim(0))
+            lu = loss_in.ds_hierarchy[sid]
+            if lu.is_hetero() and lu.hetero_dim == 0:
+                dp *= lu.size()
         segments = self._segments(my_ops, sid, send_ops)
         loss_local = False
         plan = ExecPlan(sid, stages, my_stage, my_ops, segments, recv_ops, send_ops, comm, dp, loss_local)
@@ -280,6 +313,48 @@ class Executor:
             self._fuse_linear_comm(plan, my_ops)
         self.plans[sid] = plan
         return plan
+
+    def _note_pipelines(self, sid: int) -> None:
+        """graph.pipeline_of[(sid, rank)] = index of the union member (pipeline) `rank` works in under `sid`."""
+        g = self.graph
+        if not hasattr(g, "pipeline_of"):
+            g.pipeline_of = {}
+        if (sid, "done") in g.pipeline_of:
+            return
+        tensors = list(g.parameters) + list(g.placeholders) + [t for op in g.ops for t in op.outputs]
+        for t in tensors:
+            groups = t.dg_hierarchy[sid] if sid < len(t.dg_hierarchy) else []
+            if len(groups) > 1:
+                for m, grp in enumerate(groups):
+                    for r in grp.ranks():
+                        g.pipeline_of.setdefault((sid, r), m)
+        g.pipeline_of[(sid, "done")] = True
+
+    def _plan_split_comm(self, op, sid: int, needed: list) -> CommInfo:
+        """A comm op whose source and destination unions differ in their hetero dimension: partial -> duplicate is a
+        split all-reduce, partial -> split a split reduce-scatter, split -> duplicate a split all-gather, each over the
+        micro-block groups of the union (reference: hetu/graph/ops/Communication.cc:990-1202)."""
+        x, y = op.inputs[0], op.outputs[0]
+        su, du = x.ds_hierarchy[sid], y.ds_hierarchy[sid]
+        kind = C.classify_comm(su, x.group(sid).ranks(), du, y.group(sid).ranks(), x.member_index(sid))
+        base = kind & (C._C.COMM_SPLIT_ALL_REDUCE | C._C.COMM_SPLIT_REDUCE_SCATTER | C._C.COMM_SPLIT_ALL_GATHER)
+        if kind == C._C.COMM_UNSUPPORTED or base == 0 or kind != base:
+            raise NotImplementedError(f"{op}: {su} -> {du} needs a local collective next to the split one")
+        # groups follow the layout that is split finest: the destination for gather / all-reduce, the source's data
+        # layout otherwise; the hetero dimension itself is taken out (that is what the collective resolves)
+        ref_u, ref_t = (du, y) if base != C._C.COMM_SPLIT_REDUCE_SCATTER else (su, x)
+        locals_ = [ref_u.get_local(m) for m in range(ref_u.size())]
+        rank_groups = [grp.ranks() for grp in ref_t.dg_hierarchy[sid]]
+        every = set()
+        for grp in rank_groups:
+            for r in grp:
+                every.update(g for gs in PC.split_collective_groups(locals_, rank_groups, r)[2] for g in gs)
+        needed += sorted(every)
+        info = CommInfo(base, C.comm_type_name(base))
+        if self.mesh.rank in {r for grp in rank_groups for r in grp}:
+            dim, _, groups = PC.split_collective_groups(locals_, rank_groups, self.mesh.rank)
+            info.dim, info.split_groups = dim, groups
+        return info
 
     def _fuse_linear_comm(self, plan: ExecPlan, my_ops) -> None:
         """comm(all-gather rows) -> linear(x, W^T) and linear(x, W) -> comm(reduce-scatter rows) pairs become one

@@ -313,7 +313,20 @@ class Graph:
             outs = impl.deduce(in_ds, attrs, inputs)
             for k in range(n_out):
                 members[k].append(outs[k])
-        return [DistributedStatesUnion(members[k], hetero) for k in range(n_out)]
+        if hetero == -3 or size == 1:
+            return [DistributedStatesUnion(members[k], -3 if size == 1 else hetero) for k in range(n_out)]
+        # the dimension that is shared out over the members follows the op: a reduction over the hetero dimension
+        # leaves partial sums per member (-2), a gather leaves duplicates (-1)
+        cands = []
+        for d in [u.hetero_dim for u in unions if u.is_hetero()] + [0, -2, -1]:
+            if d not in cands:
+                cands.append(d)
+        outs = []
+        for k in range(n_out):
+            dim = next((d for d in cands
+                        if all(ds.get_dim(d) >= size and ds.get_dim(d) % size == 0 for ds in members[k])), hetero)
+            outs.append(DistributedStatesUnion(members[k], dim))
+        return outs
 
     def _deduce_groups(self, inputs, s, explicit):
         if explicit is not None and explicit[s] is not None:

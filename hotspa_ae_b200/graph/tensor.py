@@ -65,8 +65,14 @@ class Tensor:
     def global_shape(self) -> list[int]:
         return [sym_value(s) for s in self.symbolic_shape]
 
-    def local_shape(self, strategy_id: int | None = None, member: int = 0) -> list[int]:
-        ds = self.ds(strategy_id, member)
+    def local_shape(self, strategy_id: int | None = None, member: int | None = None) -> list[int]:
+        """Shape of one device's shard.  The global shape spans the whole union, so the split counts are the union
+        member's own (for a heterogeneous batch dimension: including its division among the members)."""
+        sid = self.graph.cur_strategy_id if strategy_id is None else strategy_id
+        union = self.ds_hierarchy[sid]
+        if member is None:
+            member = self.member_index(sid)
+        ds = union.get(min(member, union.size() - 1))
         return [g // ds.get_dim(d) for d, g in enumerate(self.global_shape)]
 
     @property
@@ -74,10 +80,40 @@ class Tensor:
         return self.local_shape()
 
     # ---- distributed states ----------------------------------------------------------------
-    def ds(self, strategy_id: int | None = None, member: int = 0) -> DistributedStates:
+    def member_index(self, strategy_id: int | None = None, rank: int | None = None) -> int:
+        """Which member of a heterogeneous union `rank` (default: this process) belongs to.  Members are the
+        pipelines of a hetero strategy, so a rank that holds no shard of this tensor (another stage of its
+        pipeline) answers with its pipeline's index; homogeneous unions have the single member 0."""
+        sid = self.graph.cur_strategy_id if strategy_id is None else strategy_id
+        groups = self.dg_hierarchy[sid]
+        if len(groups) <= 1:
+            return 0
+        if rank is None:
+            from ..parallel import mesh as M
+            rank = M.mesh().rank
+        for m, g in enumerate(groups):
+            if g.contains(rank):
+                return m
+        return getattr(self.graph, "pipeline_of", {}).get((sid, rank), 0)
+
+    def ds(self, strategy_id: int | None = None, member: int | None = None) -> DistributedStates:
+        """Layout of this tensor under a strategy, as the devices of one union member see it (default: the member
+        this process belongs to).  For a heterogeneous union that is `get_local`: the member's own device count,
+        with the hetero dimension's count divided by the number of members."""
         sid = self.graph.cur_strategy_id if strategy_id is None else strategy_id
         union = self.ds_hierarchy[sid]
-        return union.get(min(member, union.size() - 1))
+        if member is None:
+            member = self.member_index(sid)
+        member = min(member, union.size() - 1)
+        return union.get_local(member) if union.is_hetero() else union.get(member)
+
+    def group(self, strategy_id: int | None = None, member: int | None = None):
+        """Device group of the union member (default: this process's) that holds this tensor."""
+        sid = self.graph.cur_strategy_id if strategy_id is None else strategy_id
+        groups = self.dg_hierarchy[sid]
+        if member is None:
+            member = self.member_index(sid)
+        return groups[min(member, len(groups) - 1)]
 
     @property
     def distributed_states(self) -> DistributedStates:

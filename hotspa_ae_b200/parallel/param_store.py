@@ -345,6 +345,41 @@ class ParamStore:
         self.grad_arena(sid).zero_()
 
     # ---- optimizer step (home strategy) ------------------------------------------------------------------
+    # ---- heterogeneous unions: gradient sync across the members (pipelines) -----------------------------------
+    def _hetero_params(self, sid: int):
+        """(parameter, [local DS per member], [ranks per member]) of every parameter whose union has several
+        members under `sid`: its members are replicas with possibly different tensor-parallel degrees."""
+        out = []
+        for p in self.graph.parameters:
+            groups = p.dg_hierarchy[sid]
+            if len(groups) > 1 and p.requires_grad:
+                out.append((p, [p.ds(sid, m) for m in range(len(groups))], [g.ranks() for g in groups]))
+        return out
+
+    def hetero_sync_groups(self, sid: int) -> list:
+        """Every process group any rank needs for the split all-reduces of `sid` (for collective creation)."""
+        from . import comm as PC
+        every = set()
+        for _, locals_, rank_groups in self._hetero_params(sid):
+            for grp in rank_groups:
+                for r in grp:
+                    every.update(g for gs in PC.split_collective_groups(locals_, rank_groups, r)[2] for g in gs)
+        return sorted(every)
+
+    def _hetero_grad_sync(self, sid: int) -> None:
+        """Sum the gradient of every hetero parameter over the union: each micro-block of this rank's shard is
+        all-reduced with its holders in the other members (reference: SplitAllReduce for the hetero data-parallel
+        gradient reduction, hetu/graph/ops/Communication.cc:1100-1140)."""
+        from . import comm as PC
+        lay = self.layout(sid)
+        for p, locals_, rank_groups in self._hetero_params(sid):
+            e = lay.entries.get(p.id)
+            if e is None:
+                continue
+            dim, _, groups = PC.split_collective_groups(locals_, rank_groups, self.rank)
+            view = self.grad_arena(sid)[e.offset:e.offset + e.numel].view(e.local_shape)
+            view.copy_(PC.split_all_reduce(view, groups, dim))
+
     def reduce_and_step(self, opt, grad_scale: float = 1.0) -> None:
         sid = self.home
         lay, arena, garena = self.layout(sid), self.arena(sid), self.grad_arena(sid)
@@ -352,8 +387,18 @@ class ParamStore:
         self.step_count += 1
         fused = self.symm is not None and self.switch_mode == "fused" and arena.dtype == torch.bfloat16 \
             and hasattr(opt, "beta1")
+        hetero = bool(self._hetero_params(sid))
+        if hetero:
+            # replicas of different shape: first finish the sum inside each member (its duplicates then hold equal
+            # values, which the split all-reduce relies on), then sum over the members; the state is not sharded
+            if zero:
+                raise NotImplementedError("ZeRO over a heterogeneous union is not supported")
+            for c in lay.classes:
+                if len(c.ranks) > 1 and self.mesh.group(c.ranks) is not None:
+                    dist.all_reduce(garena[c.start:c.end], group=self.mesh.group(c.ranks))
+            self._hetero_grad_sync(sid)
         for ci, c in enumerate(lay.classes):
-            group = self.mesh.group(c.ranks)
+            group = None if hetero else self.mesh.group(c.ranks)
             seg = garena[c.start:c.end]
             lo, hi = self._owned_range(c, zero)
             n = hi - lo

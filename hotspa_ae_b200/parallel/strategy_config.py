@@ -69,6 +69,70 @@ def generate_llama_3d_config(num_layers: int = 32, num_gpus: int = 8, dp: int = 
 generate_gpt_3d_config = generate_llama_3d_config
 
 
+def generate_llama_hetero_3d_config(num_layers: int, pipelines: list, zero: bool = False) -> dict:
+    """Heterogeneous strategy: the data-parallel replicas are pipelines of different shape.
+
+    ``pipelines`` has one entry per replica; an entry lists the replica's stages in order, each stage a dict
+    ``{"ranks": [...], "layers": n}``: the ranks are the stage's tensor-parallel group (the degree may differ between
+    stages and between replicas), ``layers`` sums to ``num_layers`` inside every replica.  The result uses the
+    reference's union form (hotspa/ds_parallel_config/generate_gpt_hetero_3d_config.py:6-112): every list-valued field
+    has one element per replica, and blocks are listed one by one because their device groups differ per layer."""
+    dp = len(pipelines)
+    if dp < 2:
+        raise ValueError("a heterogeneous strategy needs at least two pipelines")
+    seen: set = set()
+    per_layer = []                                  # per pipeline: the tp group of every layer
+    for stages in pipelines:
+        if sum(int(st["layers"]) for st in stages) != num_layers or any(int(st["layers"]) < 1 for st in stages):
+            raise ValueError(f"the stages of every pipeline must split the {num_layers} layers")
+        groups = []
+        for st in stages:
+            ranks = [int(r) for r in st["ranks"]]
+            if not ranks or seen & set(ranks):
+                raise ValueError("every rank belongs to exactly one stage of one pipeline")
+            seen |= set(ranks)
+            groups += [ranks] * int(st["layers"])
+        per_layer.append(groups)
+    var, ph = "variable", "placeholder"
+    dp_union = [dp] * dp
+
+    def leaf(split_dim, layer, kind):
+        union = [per_layer[k][layer] for k in range(dp)]
+        tps = [len(g) for g in union]
+        if kind == ph:
+            return {"split": {"0": dp_union}, "dup": tps, "device_group_union": union, "type": ph}
+        if split_dim is None:
+            return {"split": {}, "dup": [t * dp for t in tps], "device_group_union": union, "type": var}
+        return {"split": {str(split_dim): tps}, "dup": dp_union, "device_group_union": union, "type": var}
+
+    last = num_layers - 1
+    cfg = {
+        "zero": bool(zero),
+        "devices": sorted(seen),
+        "input": leaf(None, 0, ph),
+        "llama": {
+            "wte": leaf(0, 0, var),
+            "wpe": leaf(None, 0, var),
+            "blocks": {},
+            "layernorm_final": leaf(None, last, var),
+        },
+        "lm_head": leaf(1, last, var),
+        "label": leaf(None, last, ph),
+    }
+    for i in range(num_layers):
+        cfg["llama"]["blocks"][f"blocks{i}"] = {
+            "range": [i, i],
+            "layernorm1": leaf(None, i, var),
+            "attn": {"qkv": leaf(1, i, var), "dense": leaf(0, i, var)},
+            "layernorm2": leaf(None, i, var),
+            "mlp": {"dense_h_to_4h": leaf(1, i, var), "dense_4h_to_h": leaf(0, i, var)},
+        }
+    return cfg
+
+
+generate_gpt_hetero_3d_config = generate_llama_hetero_3d_config
+
+
 def propagate_zero(cfg: dict) -> dict:
     """Copy the top-level ``zero`` flag onto every variable leaf that does not set its own."""
     zero = cfg.get("zero", False)

@@ -10,10 +10,14 @@ from hotspa_ae_b200.parallel.strategy_config import generate_llama_3d_config, pr
 from hotspa_ae_b200.utils import data as D
 
 
-def build_llama_graph(config: LlamaConfig, strategies, world: int, lr=1e-3, autocast=None, reduction="mean"):
-    """strategies: list of (dp, tp, pp, zero).  Returns dict with graph, model, placeholders, loss, train_op."""
-    cfgs = [propagate_zero(generate_llama_3d_config(config.num_layers, world, dp, tp, pp, zero))
-            for dp, tp, pp, zero in strategies]
+def build_llama_graph(config: LlamaConfig, strategies, world: int, lr=1e-3, autocast=None, reduction="mean",
+                      cfgs=None):
+    """strategies: list of (dp, tp, pp, zero), or ready-made strategy dicts in `cfgs`.  Returns dict with graph,
+    model, placeholders, loss, train_op."""
+    if cfgs is None:
+        cfgs = [propagate_zero(generate_llama_3d_config(config.num_layers, world, dp, tp, pp, zero))
+                for dp, tp, pp, zero in strategies]
+    cfgs = [propagate_zero(c) for c in cfgs]
     ctx = ht.graph("define_and_run", num_strategy=len(cfgs))
     g = ctx.__enter__()
     ac = ht.autocast(autocast) if autocast is not None else None

@@ -1,0 +1,90 @@
+"""Worker: tiny Llama under one heterogeneous strategy.  3 ranks: replica A is ranks (0, 1) with tensor and sequence
+parallelism 2, replica B is rank 2 alone.  4 ranks: replica A is a two-stage pipeline (ranks 0 | 1), replica B is
+ranks (2, 3) with tensor parallelism 2.  One Adam step on a global batch whose rows alternate between the replicas
+must match a single-process PyTorch run."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.models.llama import llama_config  # noqa: E402
+from hotspa_ae_b200.parallel.strategy_config import generate_llama_hetero_3d_config  # noqa: E402
+from hotspa_ae_b200.utils import data as D  # noqa: E402
+from helpers import build_llama_graph, torch_llama_loss  # noqa: E402
+
+
+def main():
+    ht.init_comm_group(8)
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    cfg = llama_config("tiny", max_seq_len=128, num_layers=2)
+    if world == 3:      # replica A: tensor parallel 2; replica B: one device
+        pipes = [[{"ranks": [0, 1], "layers": 2}], [{"ranks": [2], "layers": 2}]]
+    else:               # replica A: two pipeline stages of one device; replica B: tensor parallel 2
+        pipes = [[{"ranks": [0], "layers": 1}, {"ranks": [1], "layers": 1}], [{"ranks": [2, 3], "layers": 2}]]
+    member = next(m for m, stages in enumerate(pipes) if any(rank in st["ranks"] for st in stages))
+    my_stages = [tuple(st["ranks"]) for st in pipes[member]]
+    strat = generate_llama_hetero_3d_config(2, pipes)
+    b = build_llama_graph(cfg, None, world, lr=1e-3, cfgs=[strat])
+    g = b["graph"]
+    rng = np.random.default_rng(7)
+    seq_len, n_rows, dp = 128, 4, 2
+    rows = []
+    for _ in range(n_rows):
+        n1, n2 = int(rng.integers(30, 60)), int(rng.integers(30, 60))
+        rows.append(D.build_row([rng.integers(0, cfg.vocab_size, size=n1), rng.integers(0, cfg.vocab_size, size=n2)],
+                                seq_len, 0, 3))
+    mine = rows[member::dp]
+    nmb = len(mine)
+    cfg.mbs_times_dp_symbol.set_data(dp)
+    cfg.seq_len_symbol.set_data(seq_len)
+    feed = {b["input_ids"]: np.stack([r[0] for r in mine]), b["labels"]: np.stack([r[1] for r in mine]),
+            b["position_ids"]: np.stack([r[2] for r in mine]), b["cu_seqlens"]: np.stack([r[3] for r in mine])}
+    g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, 0, ht.run_level("alloc"))
+    plan = g.executor.plan(0)
+    assert plan.stages == my_stages, (plan.stages, my_stages)
+    assert plan.dp == 2, plan.dp
+    store = g.executor.store
+    weights = {}
+    for k, p in b["model"].named_parameters():
+        gen = torch.Generator(device=store.device)
+        gen.manual_seed(store.seed + 7919 * g.parameters.index(p))
+        weights[k] = g.param_inits[p.id].fill(list(p.global_shape), gen, store.device).cpu().requires_grad_(True)
+    g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, 0, ht.run_level("update"))
+    total = 0.0
+    for r in rows:
+        total = total + (1.0 / n_rows) * torch_llama_loss(weights, cfg, torch.tensor(r[0]), torch.tensor(r[1]),
+                                                          torch.tensor(r[2]), torch.tensor(r[3]))
+    total.backward()
+    worst = 0.0
+    for k, p in b["model"].named_parameters():
+        e = store.layout(store.home).entries.get(p.id)
+        if e is None:
+            continue                                  # lives on another stage of this rank's pipeline
+        gr = weights[k].grad
+        want = weights[k].detach() - 1e-3 * gr / (gr.abs() + 1e-8)
+        sl = p.ds(store.home).local_slice(p.global_shape, e.device_index)
+        idx = tuple(slice(o, o + n) for o, n in sl)
+        got = store.local_value(p).detach().float().cpu()
+        mask = gr[idx].abs() > 1e-6
+        diff = (got - want[idx]).abs()[mask]
+        if diff.numel():
+            worst = max(worst, float(diff.max()))
+            if float(diff.max()) > 2e-4 and os.environ.get("HSB_TEST_VERBOSE"):
+                print(f"rank {rank}: {k} diff {float(diff.max()):.3e} bad {int((diff > 2e-4).sum())}/{diff.numel()}", flush=True)
+    ok = worst < 2e-4
+    print(f"rank {rank}: worst param diff {worst:.3e} ok={ok}", flush=True)
+    t = torch.tensor([0 if ok else 1])
+    torch.distributed.all_reduce(t)
+    if rank == 0 and int(t.item()) == 0:
+        print("HETERO_LLAMA_OK")
+    sys.exit(0 if int(t.item()) == 0 else 3)
+
+
+if __name__ == "__main__":
+    main()

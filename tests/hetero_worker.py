@@ -1,0 +1,91 @@
+"""Worker (3 gloo ranks): one heterogeneous strategy - pipeline A is ranks (0, 1) with tensor parallelism 2,
+pipeline B is rank 2 alone; each trains on its own half of the batch, gradients meet in split all-reduces.
+Loss, gradients and the SGD step must equal a single-process run over the whole batch."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.graph import init as I  # noqa: E402
+
+UNION = [[0, 1], [2]]
+
+
+def leaf(kind, split, dup, zero=False):
+    d = {"type": kind, "split": split, "dup": dup, "device_group_union": UNION}
+    if kind == "variable":
+        d["zero"] = zero
+    return d
+
+
+def main():
+    ht.init_comm_group(8)
+    rank = int(os.environ["RANK"])
+    member = 0 if rank < 2 else 1
+    rows, h, f = 4, 8, 16                                     # rows per pipeline
+    x_u, x_g = ht.nn.config2ds(leaf("placeholder", {"0": [2, 2]}, [2, 1]))
+    w1_u, w_g = ht.nn.config2ds(leaf("variable", {"0": [2, 1]}, [2, 2]))          # [f, h], rows over tp
+    w2_u, _ = ht.nn.config2ds(leaf("variable", {"1": [2, 1]}, [2, 2]))            # [h, f], columns over tp
+    assert x_u.hetero_dim == 0 and w1_u.hetero_dim == -1 and x_u.get_local(0).device_num == 2
+    with ht.graph("define_and_run", num_strategy=1) as g:
+        x = ht.parallel_placeholder(ht.float32, [rows, h], [x_u], [x_g], name="x")
+        w1 = ht.parallel_parameter(I.normal_initializer(0.0, 0.3), [f, h], [w1_u], None,
+                                   device_group_hierarchy=[w_g], name="w1")
+        w2 = ht.parallel_parameter(I.normal_initializer(0.0, 0.3), [h, f], [w2_u], None,
+                                   device_group_hierarchy=[w_g], name="w2")
+        y1 = ht.relu(ht.linear(x, w1, trans_b=True))
+        y2 = ht.linear(y1, w2, trans_b=True)                  # partial over tp inside pipeline A
+        y2 = ht.comm(y2, [x_u], [x_g], name="tp_sum")
+        loss = ht.reduce_sum(y2 * y2)
+        opt = ht.SGDOptimizer(lr=0.05)
+        pairs = opt.compute_gradients(loss)
+        train_op = opt.apply_gradients(pairs)
+    assert y1.ds_hierarchy[0].hetero_dim == 0 and loss.ds_hierarchy[0].hetero_dim == -2
+    assert w1.ds(0).device_num == (2 if member == 0 else 1) and w1.member_index(0) == member
+    data = np.random.default_rng(0).standard_normal((2, rows, h)).astype(np.float32)
+    feed = {x: data[member]}
+    g.run(loss, [loss, train_op], feed, 1, 0, ht.run_level("alloc"))
+    plan = g.executor.plan(0)
+    assert len(plan.stages) == 1 and plan.stages[0] == tuple(UNION[member]), plan.stages
+    store = g.executor.store
+
+    def full(p):                                               # global value from this member's shards
+        return store._global_state(p, "master") if hasattr(store, "_global_state") else None
+
+    def gather_param(p):
+        v = torch.tensor(np.array(p.get_data()))
+        if member == 1:
+            return v
+        parts = [torch.zeros_like(v), torch.zeros_like(v)]
+        torch.distributed.all_gather(parts, v, group=g.executor.mesh.group((0, 1)))
+        return torch.cat(parts, dim=0 if p is w1 else 1)
+
+    W1, W2 = gather_param(w1), gather_param(w2)
+    both = [torch.zeros_like(W1) for _ in range(3)]
+    torch.distributed.all_gather(both, W1)
+    assert torch.equal(both[0], both[2]), "replicas of a hetero parameter must start equal"
+    out = g.run(loss, [loss, pairs[0][0], pairs[1][0], train_op], feed, 1, 0, ht.run_level("update"))
+
+    # single-process reference over both halves of the batch
+    W1r, W2r = W1.clone().requires_grad_(True), W2.clone().requires_grad_(True)
+    X = torch.tensor(data.reshape(2 * rows, h))
+    ref = ((torch.relu(X @ W1r.T) @ W2r.T) ** 2).sum()
+    ref.backward()
+    mine = torch.tensor(float(np.asarray(out[0]).reshape(-1)[0]))
+    total = mine.clone() if rank != 1 else torch.zeros(())     # pipeline A's loss is replicated on its two ranks
+    torch.distributed.all_reduce(total)
+    assert abs(float(total) - float(ref)) < 1e-3 * abs(float(ref)), (float(total), float(ref))
+    W1n, W2n = gather_param(w1), gather_param(w2)
+    assert torch.allclose(W1n, W1 - 0.05 * W1r.grad, rtol=1e-4, atol=1e-5), (W1n - (W1 - 0.05 * W1r.grad)).abs().max()
+    assert torch.allclose(W2n, W2 - 0.05 * W2r.grad, rtol=1e-4, atol=1e-5)
+    torch.distributed.barrier()
+    if rank == 0:
+        print("HETERO_OK")
+
+
+if __name__ == "__main__":
+    main()

@@ -152,3 +152,29 @@ def test_symbols_packer_and_arena():
     assert abs(loads[0] - loads[1]) <= 4 and sum(loads) == 30          # longest-processing-time-first
     offs, total = C.plan_arena([10, 300, 5], 256)
     assert offs == [0, 256, 768] and total == 1024
+
+
+def test_hetero_strategy_config_and_unions():
+    import hetu as ht
+    from hotspa_ae_b200.parallel.strategy_config import find_config, generate_llama_hetero_3d_config
+    pipes = [[{"ranks": [0, 1, 2, 3], "layers": 4}], [{"ranks": [4, 5], "layers": 2}, {"ranks": [6, 7], "layers": 2}]]
+    cfg = generate_llama_hetero_3d_config(4, pipes, zero=False)
+    assert cfg["devices"] == list(range(8)) and len(cfg["llama"]["blocks"]) == 4
+    qkv0 = find_config(cfg, "qkv", 0)
+    qkv3 = find_config(cfg, "qkv", 3)
+    assert qkv0["device_group_union"] == [[0, 1, 2, 3], [4, 5]] and qkv3["device_group_union"] == [[0, 1, 2, 3], [6, 7]]
+    assert qkv0["split"] == {"1": [4, 2]} and qkv0["dup"] == [2, 2]
+    qkv0["zero"] = False
+    u, groups = ht.nn.config2ds(qkv0)
+    assert u.hetero_dim == -1 and [g.ranks() for g in groups] == [[0, 1, 2, 3], [4, 5]]
+    a, b = u.get_local(0), u.get_local(1)
+    assert (a.device_num, a.get_dim(1), a.get_dim(-1)) == (4, 4, 1) and (b.device_num, b.get_dim(1)) == (2, 2)
+    # gradient sync of this parameter: rank 4 holds columns [0, 1/2) = micro-blocks 0 and 1 of the 4-way split
+    plan = C.split_comm_groups([a, b], [[0, 1, 2, 3], [4, 5]], 4)
+    assert plan.split_dim == 1 and plan.micro_blocks == 2 and plan.groups == [[[0, 4]], [[1, 4]]]
+    plan = C.split_comm_groups([a, b], [[0, 1, 2, 3], [4, 5]], 3)
+    assert plan.micro_blocks == 1 and plan.groups == [[[3, 5]]]
+    u_in, _ = ht.nn.config2ds(cfg["input"])
+    assert u_in.hetero_dim == 0 and u_in.get_local(1).get_dim(0) == 1 and u_in.get(1).get_dim(0) == 2
+    with pytest.raises(ValueError):
+        generate_llama_hetero_3d_config(4, [[{"ranks": [0], "layers": 4}], [{"ranks": [0], "layers": 4}]])

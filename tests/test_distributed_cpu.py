@@ -67,3 +67,15 @@ def test_heterogeneous_split_collectives():
 
 def test_communication_group_verbs():
     _torchrun("comm_group_worker.py", 4, marker="COMM_GROUP_OK", timeout=600)
+
+
+def test_heterogeneous_strategy_mlp_with_gradient_handles():
+    # replica A = ranks (0, 1) tensor parallel, replica B = rank 2; split all-reduce of the gradients across them
+    _torchrun("hetero_worker.py", 3, marker="HETERO_OK", timeout=600)
+
+
+@pytest.mark.parametrize("world", [3, 4])
+def test_heterogeneous_strategy_tiny_llama(world):
+    # 3 ranks: tp2 (+ sequence parallel) replica next to a single-device replica;
+    # 4 ranks: a two-stage pipeline replica next to a tp2 replica
+    _torchrun("hetero_llama_worker.py", world, marker="HETERO_LLAMA_OK", timeout=900)

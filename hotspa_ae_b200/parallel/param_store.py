@@ -257,6 +257,8 @@ class ParamStore:
             for member, group in enumerate(p.dg_hierarchy[src]):
                 s_regs += regions_of(shape, p.ds(src, member), group.ranks(), -1)
             for member, group in enumerate(p.dg_hierarchy[dst]):
+                if kind == "grad" and member != i % len(p.dg_hierarchy[dst]):
+                    continue      # gradients land on ONE holder per cell: the members of a union are replicas too
                 d_regs += regions_of(shape, p.ds(dst, member), group.ranks(), i if kind == "grad" else -1)
             planner.add_tensor_regions(i, s_regs, d_regs, kind == "grad")
         sends: dict[int, list] = {}

@@ -13,7 +13,8 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import hetu as ht  # noqa: E402
 from hotspa_ae_b200.models.llama import llama_config  # noqa: E402
-from hotspa_ae_b200.parallel.strategy_config import generate_llama_hetero_3d_config  # noqa: E402
+from hotspa_ae_b200.parallel.strategy_config import (generate_llama_3d_config,  # noqa: E402
+                                                     generate_llama_hetero_3d_config)
 from hotspa_ae_b200.utils import data as D  # noqa: E402
 from helpers import build_llama_graph, torch_llama_loss  # noqa: E402
 
@@ -30,21 +31,31 @@ def main():
     member = next(m for m, stages in enumerate(pipes) if any(rank in st["ranks"] for st in stages))
     my_stages = [tuple(st["ranks"]) for st in pipes[member]]
     strat = generate_llama_hetero_3d_config(2, pipes)
-    b = build_llama_graph(cfg, None, world, lr=1e-3, cfgs=[strat])
+    switch = "--switch" in sys.argv          # second strategy: homogeneous dp2 x tp2; gradients hot-switch home
+    cfgs = [strat] + ([generate_llama_3d_config(2, 4, 2, 2, 1, False)] if switch else [])
+    b = build_llama_graph(cfg, None, world, lr=1e-3, cfgs=cfgs)
     g = b["graph"]
     rng = np.random.default_rng(7)
     seq_len, n_rows, dp = 128, 4, 2
-    rows = []
-    for _ in range(n_rows):
-        n1, n2 = int(rng.integers(30, 60)), int(rng.integers(30, 60))
-        rows.append(D.build_row([rng.integers(0, cfg.vocab_size, size=n1), rng.integers(0, cfg.vocab_size, size=n2)],
-                                seq_len, 0, 3))
+
+    def make_rows():
+        out = []
+        for _ in range(n_rows):
+            n1, n2 = int(rng.integers(30, 60)), int(rng.integers(30, 60))
+            out.append(D.build_row([rng.integers(0, cfg.vocab_size, size=n1), rng.integers(0, cfg.vocab_size, size=n2)],
+                                   seq_len, 0, 3))
+        return out
+
+    def feed_of(mine):
+        return {b["input_ids"]: np.stack([r[0] for r in mine]), b["labels"]: np.stack([r[1] for r in mine]),
+                b["position_ids"]: np.stack([r[2] for r in mine]), b["cu_seqlens"]: np.stack([r[3] for r in mine])}
+
+    rows = make_rows()
     mine = rows[member::dp]
     nmb = len(mine)
     cfg.mbs_times_dp_symbol.set_data(dp)
     cfg.seq_len_symbol.set_data(seq_len)
-    feed = {b["input_ids"]: np.stack([r[0] for r in mine]), b["labels"]: np.stack([r[1] for r in mine]),
-            b["position_ids"]: np.stack([r[2] for r in mine]), b["cu_seqlens"]: np.stack([r[3] for r in mine])}
+    feed = feed_of(mine)
     g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, 0, ht.run_level("alloc"))
     plan = g.executor.plan(0)
     assert plan.stages == my_stages, (plan.stages, my_stages)
@@ -55,7 +66,18 @@ def main():
         gen = torch.Generator(device=store.device)
         gen.manual_seed(store.seed + 7919 * g.parameters.index(p))
         weights[k] = g.param_inits[p.id].fill(list(p.global_shape), gen, store.device).cpu().requires_grad_(True)
+    all_rows = list(rows)
+    if switch:
+        # a bucket under the homogeneous strategy first: dp index = rank // 2 (ranks (0, 1) and (2, 3) are tp pairs)
+        rows1 = make_rows()
+        g.run(b["loss"], [b["loss"], b["train_op"]], feed_of(rows1[rank // 2::dp]), n_rows // dp, 1,
+              ht.run_level("grad"))
+        all_rows += rows1
     g.run(b["loss"], [b["loss"], b["train_op"]], feed, nmb, 0, ht.run_level("update"))
+    if switch:
+        kinds = [(e["src"], e["dst"], e["kind"]) for e in store.switch_log]
+        assert (0, 1, "param") in kinds and (1, 0, "grad") in kinds, kinds
+    rows = all_rows
     total = 0.0
     for r in rows:
         total = total + (1.0 / n_rows) * torch_llama_loss(weights, cfg, torch.tensor(r[0]), torch.tensor(r[1]),

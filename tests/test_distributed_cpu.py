@@ -79,3 +79,9 @@ def test_heterogeneous_strategy_tiny_llama(world):
     # 3 ranks: tp2 (+ sequence parallel) replica next to a single-device replica;
     # 4 ranks: a two-stage pipeline replica next to a tp2 replica
     _torchrun("hetero_llama_worker.py", world, marker="HETERO_LLAMA_OK", timeout=900)
+
+
+def test_hot_switch_between_heterogeneous_home_and_homogeneous_strategy():
+    # home = pipeline replica + tp2 replica; a second bucket runs under dp2 x tp2: parameters are copied out of the
+    # union (any member may serve a slice), its gradients are added into one holder per cell and then synchronised
+    _torchrun("hetero_llama_worker.py", 4, ["--switch"], marker="HETERO_LLAMA_OK", timeout=900)

@@ -152,3 +152,17 @@ def to_config_args(plan: Plan) -> dict:
                 order[s * width + rep * plan.tp + t] = next(it)
     return {"dp": plan.dp, "tp": plan.tp, "pp": plan.pp, "layers_per_stage": plan.layers_per_stage[0],
             "rank_order": order, "hetero": not same}
+
+
+def to_hetero_pipelines(plan: Plan) -> list:
+    """The plan as the pipelines argument of ``generate_llama_hetero_3d_config``: one pipeline per replica, each a
+    list of stages ``{"ranks": tensor-parallel group, "layers": count}`` (replicas may split the layers
+    differently, which the homogeneous config form cannot express)."""
+    it = iter(plan.rank_order)
+    pipes = []
+    for rep in range(plan.dp):
+        stages = []
+        for s in range(plan.pp):
+            stages.append({"ranks": [next(it) for _ in range(plan.tp)], "layers": int(plan.layers_per_stage[rep][s])})
+        pipes.append(stages)
+    return pipes

@@ -21,10 +21,10 @@ import hetu as ht
 
 from ..models.llama import LlamaLMHeadModel
 from ..parallel import mesh as M
-from ..parallel.strategy_config import generate_llama_3d_config, propagate_zero
+from ..parallel.strategy_config import generate_llama_3d_config, generate_llama_hetero_3d_config, propagate_zero
 from ..train.trainer import HotSwitchTrainer
 from .straggler import SLIDING_WINDOW, StepTimeWindow, Straggler, WorkloadInfo, gather_times
-from .strategy import Plan, StrategyModel, to_config_args
+from .strategy import Plan, StrategyModel, to_config_args, to_hetero_pipelines
 
 
 class ElasticTrainer(HotSwitchTrainer):
@@ -163,8 +163,13 @@ class ElasticTrainer(HotSwitchTrainer):
             a = to_config_args(plan)
             if plan.unused:
                 raise NotImplementedError("plans that drop devices need a new process group; restart from a checkpoint")
-            cfg = generate_llama_3d_config(self.config.num_layers, self.mesh.world_size, a["dp"], a["tp"], a["pp"],
-                                           self.zero, layers_per_stage=a["layers_per_stage"], rank_order=a["rank_order"])
+            if a["hetero"] and plan.dp > 1:
+                # replicas with different layer splits: one pipeline per replica (a heterogeneous union; no ZeRO)
+                cfg = generate_llama_hetero_3d_config(self.config.num_layers, to_hetero_pipelines(plan), zero=False)
+            else:
+                cfg = generate_llama_3d_config(self.config.num_layers, self.mesh.world_size, a["dp"], a["tp"],
+                                               a["pp"], self.zero, layers_per_stage=a["layers_per_stage"],
+                                               rank_order=a["rank_order"])
             sid = self.add_strategy(cfg)
             self.pool[key] = sid
             while len(self.plans) <= sid:

@@ -139,6 +139,8 @@ def init_comm_group(gpus_per_node: int = 8, *, world_size: int | None = None, ra
     if virtual:
         _MESH = Mesh(int(world_size or 1), int(rank or 0), gpus_per_node, True)
         return _MESH
+    if _MESH is not None and _MESH.virtual:
+        return _MESH            # a virtual mesh (planning without processes) stays until reset_mesh()
     env_ws = int(os.environ.get("WORLD_SIZE", "1"))
     if env_ws > 1:
         if not dist.is_initialized():

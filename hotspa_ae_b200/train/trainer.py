@@ -136,14 +136,21 @@ class HotSwitchTrainer:
         return self.in_ds[sid].get(0).get_dim(0)
 
     def tp_of(self, sid: int) -> int:
-        return self.in_ds[sid].get(0).get_dim(-1)
+        """Tensor-parallel degree of the replica this rank works in (replicas of a heterogeneous strategy differ)."""
+        return self.input_ids.ds(sid).get_dim(-1)
 
     def _my_dp_index(self, sid: int) -> int:
+        """Which data-parallel share of a bucket this rank works on.  Under a heterogeneous strategy the replicas
+        are the members of the union (each possibly data-parallel inside as well)."""
         rank = self.mesh.rank
+        local = 0
         for st in self.graph.executor.plan(sid).stages:
             if rank in st:
-                return int(self.input_ids.ds(sid).get_dup_group_index(list(st).index(rank)))
-        return 0
+                local = int(self.input_ids.ds(sid).get_dup_group_index(list(st).index(rank)))
+                break
+        if self.input_ids.ds_hierarchy[sid].is_hetero():
+            return self.input_ids.member_index(sid) * self.input_ids.ds(sid).get_dim(0) + local
+        return local
 
     def _on_micro_batch(self, mb: int) -> None:
         if self._row_lens:

@@ -63,7 +63,8 @@ def gather_global(graph, p) -> torch.Tensor | None:
         groups = [g for g in p.dg_hierarchy[sid] if g.contains(mesh.rank)]
         idx = groups[0].get_index(mesh.rank)
         dup_ranks = ds.get_devices_by_dim(-1, idx, groups[0].ranks())
-        if mesh.rank == min(dup_ranks):
+        # the members of a heterogeneous union are replicas: only the first one contributes
+        if mesh.rank == min(dup_ranks) and p.member_index(sid) == 0:
             sl = ds.local_slice(p.global_shape, e.device_index)
             view = full[tuple(slice(o, o + n) for o, n in sl)]
             view.copy_(store.local_value(p, sid).float())

@@ -85,3 +85,7 @@ def test_hot_switch_between_heterogeneous_home_and_homogeneous_strategy():
     # home = pipeline replica + tp2 replica; a second bucket runs under dp2 x tp2: parameters are copied out of the
     # union (any member may serve a slice), its gradients are added into one holder per cell and then synchronised
     _torchrun("hetero_llama_worker.py", 4, ["--switch"], marker="HETERO_LLAMA_OK", timeout=900)
+
+
+def test_trainer_under_a_heterogeneous_strategy_matches_the_homogeneous_run():
+    _torchrun("hetero_trainer_worker.py", 4, marker="HETERO_TRAINER_OK", timeout=900)

@@ -110,8 +110,11 @@ class ElasticTrainer(HotSwitchTrainer):
         packed = D.bucket_and_pack([len(s) for s in sequences], self.bounds, 1, False)[0]
         members = [i for row in packed.rows for i in row]
         budget = self.micro_batch_tokens[sid] or packed.max_len
+        plan = self.plans[sid] if sid < len(self.plans) else None
+        shares = plan.work_share if plan is not None and len(plan.work_share) == self.dp_of(sid) else None
         mb = D.token_budget_micro_batches(sequences, members, self.dp_of(sid), self._dp_index[sid], budget,
-                                          self.pad_id, (256 if self.device.type == "cuda" else 8) * self.tp_of(sid))
+                                          self.pad_id, (256 if self.device.type == "cuda" else 8) * self.tp_of(sid),
+                                          shares=shares)
         feed = {}
         for ph, key in ((self.input_ids, "input_ids"), (self.labels, "labels"), (self.position_ids, "position_ids"),
                         (self.cu_seqlens, "cu_seqlens")):

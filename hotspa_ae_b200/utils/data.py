@@ -109,8 +109,21 @@ def micro_batches_for_rank(seqs, packed: PackedRows, dp: int, dp_rank: int, pad_
             "cu_seqlens": np.stack(cus), "num_micro_batches": n_mb, "valid_tokens": ntok}
 
 
+def balance_by_share(lens, shares) -> list:
+    """Indices of `lens` per replica so that replica r carries about `shares[r]` of the tokens: longest first, each to
+    the replica whose load relative to its share stays smallest."""
+    shares = [max(float(s), 1e-9) for s in shares]
+    loads = [0.0] * len(shares)
+    out = [[] for _ in shares]
+    for k in sorted(range(len(lens)), key=lambda i: -lens[i]):
+        r = min(range(len(shares)), key=lambda q: ((loads[q] + lens[k]) / shares[q], q))
+        out[r].append(k)
+        loads[r] += lens[k]
+    return out
+
+
 def token_budget_micro_batches(seqs, members, dp: int, dp_rank: int, tokens_per_mb: int, pad_id: int = 0,
-                               multiple: int = 256):
+                               multiple: int = 256, shares=None):
     """Micro-batches of one bucket for data-parallel rank `dp_rank`, sized by tokens instead of by rows.
 
     Attention is per document (cu_seqlens), so a micro-batch may hold any number of documents: the bucket's
@@ -120,7 +133,16 @@ def token_budget_micro_batches(seqs, members, dp: int, dp_rank: int, tokens_per_
     fewer get all-padding ones).  Returns per-micro-batch lists of arrays (lengths differ between micro-batches).
     """
     lens = [int(len(seqs[i])) for i in members]
-    assign = C.balance_rows(lens, dp) if members else [[] for _ in range(dp)]
+    if not members:
+        assign = [[] for _ in range(dp)]
+    elif shares is not None:
+        # replicas of unequal speed: `shares` is the fraction of the tokens each should carry (every token weighs the
+        # same in the loss, so an uneven split changes the schedule, not the gradient)
+        if len(shares) != dp:
+            raise ValueError(f"{len(shares)} shares for {dp} replicas")
+        assign = balance_by_share(lens, shares)
+    else:
+        assign = C.balance_rows(lens, dp)
     per_rank = []
     for r in range(dp):
         mine = sorted((members[k] for k in assign[r]), key=lambda i: -len(seqs[i]))

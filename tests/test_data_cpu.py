@@ -66,3 +66,24 @@ def test_bucketing_and_token_budget_micro_batches():
             assert ids.shape == (1, L) and L % 256 == 0 and cu[0, -1] == L
             seen.append(int((lab != -1).sum()))
     assert sum(seen) == sum(lens[i] - 1 for i in short)         # every target token appears exactly once
+
+
+def test_token_budget_micro_batches_follow_replica_shares():
+    from hotspa_ae_b200.utils import data as D
+    lens = D.lognormal_lengths(20000, seed=3, median=200, max_len=2048)
+    seqs = D.synthetic_sequences(lens, 1000, seed=3)
+    members = list(range(len(seqs)))
+    tok = []
+    for r in range(2):
+        mb = D.token_budget_micro_batches(seqs, members, 2, r, 4096, 0, 8, shares=[0.75, 0.25])
+        tok.append(sum(int((a != 0).sum()) for a in mb["position_ids"]) + len(mb["position_ids"]))
+        nmb = mb["num_micro_batches"]
+    total = sum(len(s) for s in seqs)
+    carried = [sum(len(seqs[i]) for i in part) for part in D.balance_by_share([len(s) for s in seqs], [0.75, 0.25])]
+    assert sum(carried) == total and abs(carried[0] / total - 0.75) < 0.03
+    assert nmb >= 3                      # the heavy replica needs ~15000 / 4096 micro-batches; the light one pads up
+    even = D.balance_by_share([len(s) for s in seqs], [0.5, 0.5])
+    assert abs(sum(len(seqs[i]) for i in even[0]) / total - 0.5) < 0.03
+    import pytest
+    with pytest.raises(ValueError):
+        D.token_budget_micro_batches(seqs, members, 2, 0, 4096, 0, 8, shares=[1.0])

@@ -43,6 +43,7 @@ schedule_gpipe = _C.schedule_gpipe
 bucket_and_pack = _C.bucket_and_pack
 balance_rows = _C.balance_rows
 plan_arena = _C.plan_arena
+build_reshard_descriptors = _C.build_reshard_descriptors
 
 NULL_HETERO_DIM = -3
 

@@ -1,4 +1,5 @@
 // pybind11 surface of the host-side core (module `_hsb_core`).
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -183,6 +184,24 @@ PYBIND11_MODULE(_hsb_core, m) {
   m.def("bucket_and_pack", &bucket_and_pack, py::arg("lengths"), py::arg("bucket_bounds"), py::arg("shift") = 0,
         py::arg("drop_short") = false);
   m.def("balance_rows", &balance_rows);
+  // rects: int64 [n, 7] = src, dst, rows, row_bytes, src_ld_bytes, dst_ld_bytes, src_rank
+  m.def("build_reshard_descriptors", [](py::array_t<int64_t, py::array::c_style | py::array::forcecast> rects,
+                                        int64_t unit_bytes, int rank, int world) {
+    if (rects.ndim() != 2 || rects.shape(1) != 7) throw std::invalid_argument("rects must be [n, 7] int64");
+    const auto r = rects.unchecked<2>();
+    std::vector<RectBytes> in(static_cast<size_t>(r.shape(0)));
+    for (py::ssize_t i = 0; i < r.shape(0); ++i)
+      in[i] = {r(i, 0), r(i, 1), r(i, 2), r(i, 3), r(i, 4), r(i, 5), static_cast<int>(r(i, 6))};
+    DescTable t;
+    { py::gil_scoped_release rel; t = build_reshard_descriptors(in, unit_bytes, rank, world); }
+    const py::ssize_t n = static_cast<py::ssize_t>(t.unit_rows.size());
+    py::array_t<int64_t> descs({n, static_cast<py::ssize_t>(6)});
+    std::copy(t.descs.begin(), t.descs.end(), descs.mutable_data());
+    py::array_t<int32_t> unit_rows(n), prefix(n + 1);
+    std::copy(t.unit_rows.begin(), t.unit_rows.end(), unit_rows.mutable_data());
+    std::copy(t.prefix.begin(), t.prefix.end(), prefix.mutable_data());
+    return py::make_tuple(descs, unit_rows, prefix);
+  }, py::arg("rects"), py::arg("unit_bytes"), py::arg("rank"), py::arg("world"));
   m.def("plan_arena", [](const std::vector<int64_t>& numels, int64_t align) {
     std::vector<int64_t> offs;
     const int64_t total = plan_arena(numels, align, &offs);

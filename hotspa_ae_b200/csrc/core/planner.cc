@@ -1,5 +1,7 @@
 #include "planner.h"
 
+#include <map>
+
 #include <algorithm>
 #include <numeric>
 #include <stdexcept>
@@ -262,6 +264,59 @@ std::vector<std::vector<int>> balance_rows(const std::vector<int64_t>& row_token
       if (load[r] < load[best] || (load[r] == load[best] && out[r].size() < out[best].size())) best = r;
     out[best].push_back(i);
     load[best] += row_tokens[i];
+  }
+  return out;
+}
+
+DescTable build_reshard_descriptors(const std::vector<RectBytes>& rects, int64_t unit_bytes, int rank, int world) {
+  if (unit_bytes <= 0 || world <= 0) throw std::invalid_argument("build_reshard_descriptors: bad unit or world size");
+  struct Unit { int64_t src, dst, rows, row_bytes, src_ld, dst_ld; int32_t unit_rows; };
+  std::map<int, std::vector<Unit>> by_src;
+  for (const RectBytes& in : rects) {
+    int64_t r = in.rows, rb = in.row_bytes, sld = in.src_ld, dld = in.dst_ld;
+    if (r < 1 || rb < 1) throw std::invalid_argument("build_reshard_descriptors: empty rectangle");
+    // full-width rectangles are one long row: fewer, larger units
+    if (sld == rb && dld == rb) { rb *= r; sld = dld = rb; r = 1; }
+    std::vector<Unit>& bucket = by_src[in.src_rank];
+    if (r == 1 && rb > unit_bytes) {
+      const int64_t chunks = (rb + unit_bytes - 1) / unit_bytes;
+      for (int64_t k = 0; k < chunks; ++k) {
+        const int64_t b0 = k * unit_bytes;
+        bucket.push_back({in.src + b0, in.dst + b0, 1, std::min(unit_bytes, rb - b0), 0, 0, 1});
+      }
+    } else {
+      const int64_t ur = std::max<int64_t>(1, unit_bytes / std::max<int64_t>(rb, 1));
+      const int64_t units = (r + ur - 1) / ur;
+      for (int64_t k = 0; k < units; ++k) {
+        const int64_t r0 = k * ur;
+        bucket.push_back({in.src + r0 * sld, in.dst + r0 * dld, std::min(ur, r - r0), rb, sld, dld,
+                          static_cast<int32_t>(ur)});
+      }
+    }
+  }
+  std::vector<int> order;
+  for (const auto& kv : by_src) order.push_back(kv.first);
+  auto dist = [&](int q) { return ((q - rank - 1) % world + world) % world; };
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return dist(a) < dist(b); });
+  size_t left = 0;
+  for (const auto& kv : by_src) left += kv.second.size();
+  DescTable out;
+  out.descs.reserve(left * 6);
+  out.unit_rows.reserve(left);
+  out.prefix.reserve(left + 1);
+  out.prefix.push_back(0);
+  std::map<int, size_t> cursor;
+  while (left) {
+    for (int q : order) {
+      size_t& i = cursor[q];
+      const std::vector<Unit>& b = by_src[q];
+      if (i >= b.size()) continue;
+      const Unit& u = b[i++];
+      out.descs.insert(out.descs.end(), {u.src, u.dst, u.rows, u.row_bytes, u.src_ld, u.dst_ld});
+      out.unit_rows.push_back(u.unit_rows);
+      out.prefix.push_back(out.prefix.back() + static_cast<int32_t>((u.rows + u.unit_rows - 1) / u.unit_rows));
+      --left;
+    }
   }
   return out;
 }

@@ -102,6 +102,21 @@ std::vector<PackedBucket> bucket_and_pack(const std::vector<int64_t>& lengths,
 // Split packed rows over dp ranks balancing tokens (longest-processing-time first).
 std::vector<std::vector<int>> balance_rows(const std::vector<int64_t>& row_tokens, int dp);
 
+// Descriptor table of the reshard kernel (csrc/runtime/symm.cu: reshard_kernel).
+// Input: one rectangle per planned copy as addresses in this process (peer mappings resolved), in bytes.
+// Output: the rectangles cut into work units of about `unit_bytes` (single-row rectangles by bytes, multi-row ones
+// by rows, one descriptor per unit so that units can be interleaved), ordered round-robin over the source ranks
+// starting with rank + 1, so that at any moment the ranks of a node pull from different peers.
+//   descs     [n, 6] = src, dst, rows, row_bytes, src_ld_bytes, dst_ld_bytes   (ld = 0 for single-row units)
+//   unit_rows [n]      rows per unit of the descriptor
+//   prefix    [n + 1]  first unit index of every descriptor
+struct RectBytes { int64_t src, dst, rows, row_bytes, src_ld, dst_ld; int src_rank; };
+struct DescTable {
+  std::vector<int64_t> descs;
+  std::vector<int32_t> unit_rows, prefix;
+};
+DescTable build_reshard_descriptors(const std::vector<RectBytes>& rects, int64_t unit_bytes, int rank, int world);
+
 // Flat arena: assigns aligned offsets to tensors in order; returns total size.
 int64_t plan_arena(const std::vector<int64_t>& numels, int64_t align_elems, std::vector<int64_t>* offsets);
 

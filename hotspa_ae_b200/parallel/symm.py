@@ -21,6 +21,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
+from .. import core as C
 from ..ops import _lib
 from . import guards
 from . import mesh as M
@@ -181,54 +182,16 @@ class SymmHeap:
             d_entry = d_lay.entries[p.id]
             s_ptr = self.peer_ptr(s_arena, c.src_rank, (s_entry.offset + c.src_off) * esz)
             d_ptr = d_arena.data_ptr() + (d_entry.offset + c.dst_off) * esz
-            row_bytes = c.row_elems * esz
-            # full-width rectangles are one long row: fewer, larger units
-            r, rb, sld, dld = c.rows, row_bytes, c.src_ld * esz, c.dst_ld * esz
-            if sld == rb and dld == rb:
-                r, rb, sld, dld = 1, rb * c.rows, rb * c.rows, rb * c.rows
-            rows.append((s_ptr, d_ptr, r, rb, sld, dld, c.src_rank))
+            rows.append((s_ptr, d_ptr, c.rows, c.row_elems * esz, c.src_ld * esz, c.dst_ld * esz, c.src_rank))
         n = len(rows)
         if n == 0:
             self._desc_cache[key] = None
             return None
-        # split single-row rectangles into units by bytes, multi-row ones by rows
-        descs = []
-        by_src: dict[int, list] = {}
-        for s_ptr, d_ptr, r, rb, sld, dld, src_rank in rows:
-            bucket = by_src.setdefault(src_rank, [])
-            if r == 1 and rb > UNIT_BYTES:
-                nchunk = (rb + UNIT_BYTES - 1) // UNIT_BYTES
-                for k in range(nchunk):
-                    b0 = k * UNIT_BYTES
-                    bucket.append((s_ptr + b0, d_ptr + b0, 1, min(UNIT_BYTES, rb - b0), 0, 0, 1))
-            else:
-                unit_rows = max(1, UNIT_BYTES // max(rb, 1))
-                n_units = (r + unit_rows - 1) // unit_rows
-                # strided rectangles are cut into one descriptor per unit so that they can be interleaved too
-                for k in range(n_units):
-                    r0 = k * unit_rows
-                    bucket.append((s_ptr + r0 * sld, d_ptr + r0 * dld, min(unit_rows, r - r0), rb, sld, dld,
-                                   unit_rows))
-        # Interleave the sources round-robin, starting with the next rank: at any moment the ranks of the node pull
-        # from different peers instead of all hammering the owner of the same parameter.
-        order = sorted(by_src, key=lambda q: (q - self.rank - 1) % self.world)
-        cursors = {q: 0 for q in order}
-        left = sum(len(v) for v in by_src.values())
-        while left:
-            for q in order:
-                i = cursors[q]
-                if i < len(by_src[q]):
-                    descs.append(by_src[q][i])
-                    cursors[q] = i + 1
-                    left -= 1
-        nd = len(descs)
-        arr = np.zeros((nd, 6), dtype=np.int64)
-        unit_rows = np.zeros(nd, dtype=np.int32)
-        prefix = np.zeros(nd + 1, dtype=np.int32)
-        for i, (s_ptr, d_ptr, r, rb, sld, dld, ur) in enumerate(descs):
-            arr[i] = (s_ptr, d_ptr, r, rb, sld, dld)
-            unit_rows[i] = ur
-            prefix[i + 1] = prefix[i] + (r + ur - 1) // ur
+        # units, interleaving over the source ranks and the unit prefix come from the native builder
+        # (csrc/core/planner.cc: build_reshard_descriptors)
+        arr, unit_rows, prefix = C.build_reshard_descriptors(np.array(rows, dtype=np.int64), UNIT_BYTES, self.rank,
+                                                             self.world)
+        nd = int(arr.shape[0])
         if guards.enabled():
             sbuf = self.buffer_of(s_arena)
             extents = {r: (sbuf.peer_bases[r], sbuf.sizes[r]) for r in sbuf.peer_bases}

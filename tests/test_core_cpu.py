@@ -178,3 +178,58 @@ def test_hetero_strategy_config_and_unions():
     assert u_in.hetero_dim == 0 and u_in.get_local(1).get_dim(0) == 1 and u_in.get(1).get_dim(0) == 2
     with pytest.raises(ValueError):
         generate_llama_hetero_3d_config(4, [[{"ranks": [0], "layers": 4}], [{"ranks": [0], "layers": 4}]])
+
+
+def _descriptors_oracle(rows, unit_bytes, rank, world):
+    """Plain-Python statement of the descriptor rules (what the C++ builder must reproduce exactly)."""
+    by_src = {}
+    for s_ptr, d_ptr, r, rb, sld, dld, src_rank in rows:
+        if sld == rb and dld == rb:
+            r, rb, sld, dld = 1, rb * r, rb * r, rb * r
+        bucket = by_src.setdefault(src_rank, [])
+        if r == 1 and rb > unit_bytes:
+            for k in range((rb + unit_bytes - 1) // unit_bytes):
+                b0 = k * unit_bytes
+                bucket.append((s_ptr + b0, d_ptr + b0, 1, min(unit_bytes, rb - b0), 0, 0, 1))
+        else:
+            ur = max(1, unit_bytes // max(rb, 1))
+            for k in range((r + ur - 1) // ur):
+                r0 = k * ur
+                bucket.append((s_ptr + r0 * sld, d_ptr + r0 * dld, min(ur, r - r0), rb, sld, dld, ur))
+    order = sorted(by_src, key=lambda q: (q - rank - 1) % world)
+    cursors, descs = {q: 0 for q in order}, []
+    left = sum(len(v) for v in by_src.values())
+    while left:
+        for q in order:
+            if cursors[q] < len(by_src[q]):
+                descs.append(by_src[q][cursors[q]])
+                cursors[q] += 1
+                left -= 1
+    arr = np.array([d[:6] for d in descs], dtype=np.int64).reshape(-1, 6)
+    ur = np.array([d[6] for d in descs], dtype=np.int32)
+    prefix = np.concatenate([[0], np.cumsum([(d[2] + d[6] - 1) // d[6] for d in descs])]).astype(np.int32)
+    return arr, ur, prefix
+
+
+@pytest.mark.parametrize("rank,world,seed", [(0, 8, 0), (5, 8, 1), (1, 2, 2), (3, 4, 3)])
+def test_reshard_descriptor_builder_matches_the_rules(rank, world, seed):
+    rng = np.random.default_rng(seed)
+    rows = []
+    for _ in range(200):
+        src_rank = int(rng.integers(0, world))
+        rb = int(rng.choice([64, 1024, 8192, 300000, 1 << 20]))
+        r = int(rng.integers(1, 400))
+        full = bool(rng.integers(0, 2))
+        sld = rb if full else rb * int(rng.integers(1, 4))
+        dld = rb if full else rb * int(rng.integers(1, 4))
+        rows.append((int(rng.integers(1, 1 << 40)) * 16, int(rng.integers(1, 1 << 40)) * 16, r, rb, sld, dld, src_rank))
+    want = _descriptors_oracle(rows, 256 * 1024, rank, world)
+    got = C.build_reshard_descriptors(np.array(rows, dtype=np.int64), 256 * 1024, rank, world)
+    for g, w in zip(got, want):
+        assert g.dtype == w.dtype and np.array_equal(g, w)
+    # every byte of every rectangle is covered exactly once
+    total = sum(r * rb for _, _, r, rb, _, _, _ in rows)
+    assert int((got[0][:, 2] * got[0][:, 3]).sum()) == total
+    assert got[2][-1] == sum((d[2] + u - 1) // u for d, u in zip(got[0], got[1]))
+    with pytest.raises(ValueError):
+        C.build_reshard_descriptors(np.array([[16, 32, 0, 64, 64, 64, 0]], dtype=np.int64), 1024, 0, 2)

@@ -73,3 +73,40 @@ def test_switch_algorithm_env_selects_the_sender_policy(algo, monkeypatch):
     monkeypatch.setenv("HETU_SWITCH_ALGORITHM", "nonsense")
     with pytest.raises(ValueError):
         ParamStore(g)
+
+
+def test_descriptor_tables_of_a_real_plan_are_valid(monkeypatch):
+    """The heap's descriptor construction, run on CPU against a stand-in for the peer mappings: every rectangle of a
+    tp4pp2 -> dp8 parameter switch must lie inside the arena of the rank it reads and inside the destination arena,
+    and destinations must not overlap (debug-mode validation switched on)."""
+    import types
+    from hotspa_ae_b200.parallel import symm
+    monkeypatch.setenv("HSB_DEBUG_CANARIES", "1")
+    M.reset_mesh()
+    rank = 3
+    ht.init_comm_group(8, world_size=8, rank=rank, virtual=True)
+    cfg = llama_config("tiny", num_layers=4)
+    cfgs = [propagate_zero(generate_llama_3d_config(4, 8, dp, tp, pp, z)) for dp, tp, pp, z in STRATEGIES]
+    with ht.graph("define_and_run", num_strategy=len(cfgs)) as g:
+        LlamaLMHeadModel(cfg, cfgs)
+    store = ParamStore(g)
+    for kind, src, dst in (("param", 0, 2), ("grad", 2, 0), ("param", 0, 1)):
+        plan = store._plan(src, dst, kind)
+        arena = (store.arena if kind == "param" else store.grad_arena)
+        s_arena, d_arena = arena(src), arena(dst)
+        esz = s_arena.element_size()
+        # stand-in peer mapping: rank r's copy of the source arena "lives" at base_r
+        bases = {r: (r + 1) << 40 for r in range(8)}
+        bases[rank] = s_arena.data_ptr()
+        sizes = {r: store.layout(src, r).total * esz for r in range(8)}
+        fake = types.SimpleNamespace(rank=rank, world=8, device=torch.device("cpu"), _desc_cache={})
+        fake.peer_ptr = lambda t, r, off=0: bases[r] + off
+        fake.buffer_of = lambda t: types.SimpleNamespace(peer_bases=bases, sizes=sizes)
+        out = symm.SymmHeap._descriptors(fake, store, plan, src, dst, kind)
+        if out is None:
+            continue
+        descs = out["descs"].numpy()
+        assert out["n_desc"] == len(descs) and out["n_units"] == int(out["prefix"][-1]) >= out["n_desc"]
+        moved = int((descs[:, 2] * descs[:, 3]).sum())
+        mine = [c for c in plan["all"] if c.dst_rank == rank]
+        assert moved == sum(c.rows * c.row_elems for c in mine) * esz

@@ -1,37 +1,17 @@
 """Parallel strategies and hot switching on CPU ranks (gloo): parity with a single-process PyTorch model."""
 import json
 import os
-import socket
-import subprocess
 import sys
 
 import pytest
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-
-
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+sys.path.insert(0, HERE)
+from launch import torchrun_cpu  # noqa: E402
 
 
 def _torchrun(script, world, args=(), marker=None, timeout=900):
-    """Run tests/<script> on `world` gloo ranks.  The rendezvous port is picked by binding port 0 and releasing it, so
-    another process can take it before torchrun binds: a failed launch is repeated once on a fresh port, and the
-    output of both attempts is shown if the second one fails too."""
-    env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
-    outputs = []
-    for _ in range(2):
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, script), *args]
-        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env)
-        if proc.returncode == 0 and (marker is None or marker in proc.stdout):
-            return proc.stdout
-        outputs.append(proc.stdout[-3000:])
-    raise AssertionError("\n======== second attempt ========\n".join(outputs))
+    return torchrun_cpu(script, world, args, marker, timeout)
 
 
 def run_workers(world, strategies, plan, extra=()):

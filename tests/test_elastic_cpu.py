@@ -1,8 +1,6 @@
 """Elastic engine on the host: re-planner, straggler profile protocol, heartbeat liveness, and a 4-rank run whose
 slowed-down rank triggers a re-plan and a hot switch of the whole training state."""
 import os
-import socket
-import subprocess
 import sys
 import time
 
@@ -13,6 +11,8 @@ from hotspa_ae_b200.elastic.strategy import StrategyModel, split_layers, to_conf
 from hotspa_ae_b200.parallel.strategy_config import generate_llama_3d_config
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+from launch import torchrun_cpu  # noqa: E402
 
 
 def test_split_layers_balances_slow_stages():
@@ -68,25 +68,8 @@ def test_heartbeat_reports_a_rank_that_stopped(tmp_path):
     assert hb[0].dead_ranks() == [2] and hb[1].dead_ranks() == [2]
 
 
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
-
-
 def _run_elastic_worker(*args):
-    outputs = []
-    for _ in range(2):          # the rendezvous port is released before torchrun binds it: one retry on a fresh port
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
-               "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "elastic_worker.py"), *args]
-        env = dict(os.environ, OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
-        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900, env=env)
-        if proc.returncode == 0:
-            return
-        outputs.append(proc.stdout[-3000:])
-    raise AssertionError("\n======== second attempt ========\n".join(outputs))
+    torchrun_cpu("elastic_worker.py", 4, args)
 
 
 def test_replan_and_switch_keeps_training_state():

@@ -157,6 +157,7 @@ def main():
     from hotspa_ae_b200.ops import _lib
     from hotspa_ae_b200.train.trainer import HotSwitchTrainer
     from hotspa_ae_b200.utils import data as D
+    from hotspa_ae_b200.utils import roofline
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -278,6 +279,11 @@ def main():
         trainer.profile = False
     if rank == 0:
         par = "+".join(f"dp{dp}tp{tp}pp{pp}" + ("z" if z else "") for dp, tp, pp, z in strategies)
+        try:
+            mfu = {"value": roofline.mfu(tok_a / (ms_a / 1e3), trainer.config, world),
+                   "of": f"{roofline.peaks()['source']} sustained library bf16 GEMM x {world}"}
+        except Exception as exc:            # an explanatory figure must never cost the benchmark line
+            mfu = {"value": None, "error": str(exc)}
         out = {
             "metric": f"Llama-{args.model.upper()} varlen hot-switch training throughput", "value": tok_a / (ms_a / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_a / K,
@@ -291,6 +297,9 @@ def main():
                        "micro_batch_tokens": mb_tokens, "switch_mode": trainer.switch_mode,
                        "l2": "inputs larger than L2 (weights and activations of several GB stream every step)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            # model FLOPs (6 x matmul parameters x tokens; recompute not counted) over the measured sustained
+            # library bf16 GEMM rate of all GPUs
+            "mfu": mfu,
         }
         print(json.dumps(out))
     if world > 1:

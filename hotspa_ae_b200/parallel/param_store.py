@@ -301,6 +301,7 @@ class ParamStore:
             t_dev1.record()
         self.switch_log.append({"src": src, "dst": dst, "kind": kind, "mode": self.switch_mode,
                                 "remote_elems": plan["remote_elems"], "local_elems": plan["local_elems"],
+                                "max_recv_elems": max(plan["recv_elems"], default=0),
                                 "host_ms": (time.perf_counter() - t0) * 1e3, "events": (t_dev0, t_dev1)})
 
     def _switch_nccl(self, plan, src: int, dst: int, kind: str) -> None:

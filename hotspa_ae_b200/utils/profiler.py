@@ -15,6 +15,7 @@ import time
 import torch
 
 from ..core import NvmlProfiler
+from . import roofline
 
 _nvml = None
 
@@ -94,9 +95,12 @@ class StepLogger:
     def __init__(self, path: str):
         self.f = open(path, "a")
 
-    def log(self, step: int, result, seconds: float, profile: dict | None = None) -> None:
+    def log(self, step: int, result, seconds: float, profile: dict | None = None, config=None,
+            n_gpus: int = 1) -> None:
         rec = {"step": step, "time": time.time(), "loss": result.loss, "tokens": result.tokens, "step_s": seconds,
                "tokens_per_s": result.tokens / max(seconds, 1e-9), "buckets": result.buckets}
+        if config is not None:
+            rec["mfu_of_measured"] = roofline.mfu(rec["tokens_per_s"], config, n_gpus)
         if profile:
             rec["bucket_ms"] = profile.get("bucket_ms")
             rec["switches"] = profile.get("switches")
@@ -115,8 +119,13 @@ def switch_report(store, file=None) -> list:
         e0, e1 = x["events"]
         ms = e0.elapsed_time(e1) if e0 is not None else x["host_ms"]
         nbytes = x["remote_elems"] * (4 if x["kind"] == "grad" else 2)
+        esz = 4 if x["kind"] == "grad" else 2
+        busiest = x.get("max_recv_elems", 0) * esz
         out.append({"src": x["src"], "dst": x["dst"], "kind": x["kind"], "mode": x["mode"], "ms": ms,
-                    "remote_bytes_total": nbytes, "local_elems": x["local_elems"]})
+                    "remote_bytes_total": nbytes, "local_elems": x["local_elems"],
+                    "busiest_receiver_bytes": busiest,
+                    # share of the measured NVLink peer-copy rate on the receiver that takes in the most
+                    "link_fraction": roofline.switch_link_fraction(busiest, ms)})
     level = os.environ.get("HETU_SWITCH_PROFILE", "INFO").upper()
     if level in ("TRACE", "MEMORY", "NVLINK", "TIME"):
         for r in out:

@@ -1,0 +1,69 @@
+"""Roofline arithmetic against the peaks measured on the machine.
+
+The denominators are a plain copy and a library bf16 GEMM measured on the same GPUs (``MEASURED_PEAKS.json`` at the
+repository root when present, otherwise an earlier measurement of the same GPU type, reported as "fallback"); NVLink
+uses the measured peer-copy rate.  Every fraction produced here therefore reads "of measured" (or "of fallback"), and
+a good kernel can come out slightly above 1.0.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+NVLINK_PEER_COPY_GBS = 770.0          # measured peer copy, per direction and GPU (nominal 900)
+_FALLBACK = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def peaks(path: str | None = None) -> dict:
+    path = path or os.path.join(_ROOT, "MEASURED_PEAKS.json")
+    src, p = "fallback", dict(_FALLBACK)
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        src = "measured"
+    return {"tflops": float(p["bf16_tflops"]),
+            "tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+            "gbs": float(p["hbm_gbs"]), "nvlink_gbs": NVLINK_PEER_COPY_GBS, "source": src}
+
+
+def model_flops_per_token(config, seq_len: float | None = None, vocab_size: int | None = None) -> float:
+    """Training FLOPs per token of a Llama config: 6 x the matmul parameters (forward + backward) plus, when an
+    average attended length is given, the attention score / value products (12 x layers x hidden x length, halved for
+    the causal mask).  Recomputation is not counted: this is model FLOPs, not hardware FLOPs."""
+    h, f, layers = config.hidden_size, config.ffn_hidden_size, config.num_layers
+    v = vocab_size or config.vocab_size
+    matmul_params = layers * (4 * h * h + 3 * h * f) + v * h          # qkv + o, gate/up + down, lm_head
+    flops = 6.0 * matmul_params
+    if seq_len:
+        flops += 12.0 * layers * h * float(seq_len) * 0.5
+    return flops
+
+
+def mfu(tokens_per_s: float, config, n_gpus: int = 1, seq_len: float | None = None, sustained: bool = True,
+        pk: dict | None = None) -> float:
+    """Model FLOPs utilisation: achieved model FLOP/s over the measured library GEMM rate of all GPUs."""
+    pk = pk or peaks()
+    peak = (pk["tflops_sustained"] if sustained else pk["tflops"]) * 1e12 * max(1, n_gpus)
+    return tokens_per_s * model_flops_per_token(config, seq_len) / peak
+
+
+def fused_roofline_s(flops: float, nvlink_bytes_per_gpu: float, hbm_bytes: float = 0.0, pk: dict | None = None) -> float:
+    """Target time of a compute + collective kernel: the slowest of the GEMM at the measured peak, the bytes that
+    must cross NVLink at the measured peer-copy rate, and the HBM traffic at the measured copy rate."""
+    pk = pk or peaks()
+    return max(flops / (pk["tflops"] * 1e12), nvlink_bytes_per_gpu / (pk["nvlink_gbs"] * 1e9),
+               hbm_bytes / (pk["gbs"] * 1e9))
+
+
+def fraction(achieved_s: float, roofline_s: float) -> float:
+    return roofline_s / achieved_s if achieved_s > 0 else 0.0
+
+
+def switch_link_fraction(recv_bytes_per_gpu: float, ms: float, pk: dict | None = None) -> float:
+    """Share of the measured NVLink peer-copy rate a hot switch reached on the busiest receiver."""
+    pk = pk or peaks()
+    if ms <= 0:
+        return 0.0
+    return recv_bytes_per_gpu / (ms * 1e-3) / (pk["nvlink_gbs"] * 1e9)

@@ -145,3 +145,24 @@ def test_compute_apply_gradients_and_sgd_update_op():
     np.testing.assert_allclose(np.array(w.get_data()), w1 - 0.25, rtol=1e-6, atol=1e-6)
     with pytest.raises(ValueError):
         opt.apply_gradients([(loss, w)])
+
+
+def test_roofline_helpers(tmp_path):
+    from hotspa_ae_b200.models.llama import llama_config
+    from hotspa_ae_b200.utils import roofline as R
+    p = tmp_path / "peaks.json"
+    p.write_text(json.dumps({"bf16_tflops": 1000.0, "bf16_tflops_sustained": 800.0, "hbm_gbs": 5000.0}))
+    pk = R.peaks(str(p))
+    assert pk["source"] == "measured" and pk["tflops_sustained"] == 800.0
+    assert R.peaks(str(tmp_path / "absent.json"))["source"] == "fallback"
+    c = llama_config("7b", vocab_size=32000)
+    per_tok = R.model_flops_per_token(c)
+    assert 38e9 < per_tok < 42e9                                     # ~6 x 6.6e9 matmul parameters
+    assert R.model_flops_per_token(c, seq_len=4096) > per_tok
+    assert abs(R.mfu(800e12 / per_tok, c, 1, pk=pk) - 1.0) < 1e-9
+    assert abs(R.mfu(800e12 / per_tok, c, 8, pk=pk) - 0.125) < 1e-9
+    # a GEMM of 1e12 FLOPs that ships 7.7e8 bytes: compute bound (1 ms against 1 ms of link time -> equal)
+    assert abs(R.fused_roofline_s(1e12, 7.7e8, pk=pk) - 1e-3) < 1e-9
+    assert abs(R.fused_roofline_s(1e11, 7.7e8, pk=pk) - 1e-3) < 1e-9     # link bound
+    assert abs(R.switch_link_fraction(7.7e9, 20.0, pk=pk) - 0.5) < 1e-9
+    assert R.fraction(2e-3, 1e-3) == 0.5

@@ -718,6 +718,14 @@ class Executor:
                 o += n
             return vals
 
+        # parameters whose replicas compute identical gradients: what this run adds is divided by the replica count
+        same_grad = []
+        if wants_train:
+            for p, n in self.store._replicated_grad_params(sid):
+                self.store.grad_arena(sid)            # allocated on first use
+                view = self.store.local_grad(p, sid)
+                if view is not None:
+                    same_grad.append((view, view.clone(), n))
         hook = getattr(self.graph, "micro_batch_hook", None)
         for is_fwd, mb in tasks:
             if hook is not None:
@@ -768,6 +776,8 @@ class Executor:
                 self._fold_autograd_grads(params)
         if pending_sends:
             PC.p2p_exchange(pending_sends, [])
+        for view, before, n in same_grad:
+            view.copy_(before + (view - before) / n)
 
         # gradient handles: this rank's accumulator as it stands after backward (before any reduction / update)
         grad_fetch = {}

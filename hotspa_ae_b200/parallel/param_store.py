@@ -383,6 +383,45 @@ class ParamStore:
             view = self.grad_arena(sid)[e.offset:e.offset + e.numel].view(e.local_shape)
             view.copy_(PC.split_all_reduce(view, groups, dim))
 
+    def _replicated_grad_params(self, sid: int) -> list:
+        """Parameters whose replicas all compute the SAME gradient: every tensor they are combined with is a pure
+        duplicate over their devices (e.g. a bias added to an all-reduced activation).  The reduction over the
+        duplicate group is a sum of partial contributions for every other parameter; for these it would count the
+        gradient once per replica, so the executor divides what a run added to their accumulators by the replica
+        count (`Executor.run`).
+        (The reference gets the same effect from the DS of the gradient: duplicate, not partial, hence no reduce.)"""
+        key = ("replicated_grads", sid)
+        if key in self.plans:
+            return self.plans[key]
+        consumers: dict = {}
+        for op in self.graph.ops:
+            for t in op.inputs:
+                if t.is_parameter:
+                    consumers.setdefault(t.id, []).append(op)
+        out = []
+        for p in self.graph.parameters:
+            if not p.requires_grad:
+                continue
+            ds = p.ds(sid)
+            n = ds.get_dim(-1)
+            if n <= 1 or p.id not in consumers:
+                continue
+            same = True
+            for op in consumers[p.id]:
+                for t in op.inputs:
+                    if t is p or t.is_parameter:
+                        continue
+                    tds = t.ds(sid)
+                    if not tds.is_pure_duplicate:
+                        same = False
+                for t in op.outputs:
+                    if t.ds(sid).get_dim(-2) > 1:
+                        same = False
+            if same:
+                out.append((p, n))
+        self.plans[key] = out
+        return out
+
     def reduce_and_step(self, opt, grad_scale: float = 1.0) -> None:
         sid = self.home
         lay, arena, garena = self.layout(sid), self.arena(sid), self.grad_arena(sid)

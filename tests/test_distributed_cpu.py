@@ -69,3 +69,9 @@ def test_hot_switch_between_heterogeneous_home_and_homogeneous_strategy():
 
 def test_trainer_under_a_heterogeneous_strategy_matches_the_homogeneous_run():
     _torchrun("hetero_trainer_worker.py", 4, marker="HETERO_TRAINER_OK", timeout=900)
+
+
+def test_device_group_parallel_layers_on_two_ranks():
+    # column-parallel -> row-parallel linear and a vocab-parallel embedding; the row-parallel bias is replicated and
+    # sees replicated activations, so its replicas' identical gradients must count once
+    _torchrun("nn_parallel_worker.py", 2, marker="NN_PARALLEL_OK", timeout=600)

@@ -1,1 +1,1 @@
-from .optimizer import AdamOptimizer, Optimizer, SGDOptimizer  # noqa: F401
+from .optimizer import AdamOptimizer, Optimizer, SGD, SGDOptimizer  # noqa: F401

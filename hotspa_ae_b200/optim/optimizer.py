@@ -111,3 +111,52 @@ class AdamOptimizer(Optimizer):
         master.add_(upd, alpha=-self.lr)
         out_compute.copy_(master)
         grad.zero_()
+
+
+class SGD(SGDOptimizer):
+    """The thin wrapper of the reference's Python optimizer package (python_refactor/hetu/optim/sgd.py): `params` given
+    selects the define-by-run use (`zero_grad` / `step` on tensors that carry `.grad`), `params=None` the
+    define-and-run use through `minimize`."""
+
+    def __init__(self, params=None, lr: float = 0.1, momentum: float = 0.0, nesterov: bool = False):
+        if lr < 0.0:
+            raise ValueError(f"Invalid learning rate: {lr}")
+        if momentum < 0.0 or momentum > 1:
+            raise ValueError(f"Invalid momentum: {momentum}")
+        if nesterov and momentum == 0:
+            raise ValueError("Nesterov requires non-zero momentum")
+        super().__init__(lr=lr, momentum=momentum, nesterov=nesterov)
+        self.params = None if params is None else list(params)
+        self.defaults = dict(lr=lr, momentum=momentum, nesterov=nesterov)
+        if self.params is not None:
+            if not self.params:
+                raise ValueError("No variables are provided")
+            for p in self.params:
+                if not p.requires_grad:
+                    raise ValueError(f"Parameter {p} is not requires_grad")
+
+    def _need_params(self, fn):
+        if self.params is None:
+            raise ValueError(f"Function '{fn}' should only be used in define-by-run mode")
+
+    def apply_dense(self, param, grad):
+        return O.sgd_update(param, grad, self.defaults["lr"])
+
+    def zero_grad(self):
+        self._need_params("zero_grad")
+        for p in self.params:
+            p.grad = None
+
+    def step(self):
+        """Applies `param -= lr * param.grad` for every parameter whose `.grad` is set (a graph tensor or an array
+        of the parameter's shape); returns the update ops."""
+        self._need_params("step")
+        ops = []
+        for p in self.params:
+            g = getattr(p, "grad", None)
+            if g is None:
+                continue
+            if not hasattr(g, "graph"):
+                g = p.graph.from_numpy(g, requires_grad=False) if hasattr(p.graph, "from_numpy") else g
+            ops.append(self.apply_dense(p, g))
+        return ops

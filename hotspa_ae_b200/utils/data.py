@@ -169,3 +169,7 @@ def token_budget_micro_batches(seqs, members, dp: int, dp_rank: int, tokens_per_
         out["cu_seqlens"].append(d[None]); out["row_len"].append(row_len)
         out["valid_tokens"] += int((b != IGNORE).sum())
     return out
+
+
+# torch-like dataset skeleton under its reference name (python_refactor/hetu/utils/data/__init__.py)
+from .dataset import DataLoader, Dataset, IterableDataset  # noqa: E402,F401

@@ -166,3 +166,21 @@ def test_roofline_helpers(tmp_path):
     assert abs(R.fused_roofline_s(1e11, 7.7e8, pk=pk) - 1e-3) < 1e-9     # link bound
     assert abs(R.switch_link_fraction(7.7e9, 20.0, pk=pk) - 0.5) < 1e-9
     assert R.fraction(2e-3, 1e-3) == 0.5
+
+
+def test_reference_package_names_resolve():
+    assert callable(ht.utils.checkpoint.save_checkpoint) and callable(ht.utils.checkpoint.load_checkpoint)
+    assert ht.utils.data.DataLoader is not None and issubclass(ht.utils.data.IterableDataset, ht.utils.data.Dataset)
+    with pytest.raises(ValueError):
+        ht.optim.SGD(lr=-1.0)
+    with pytest.raises(ValueError):
+        ht.optim.SGD(lr=0.1, nesterov=True)
+    with ht.graph("define_and_run") as g:
+        x = ht.placeholder(ht.float32, [2, 3], name="x")
+        w = ht.nn.functional.ones_([3], requires_grad=True, name="w")
+        loss = ht.reduce_sum((x * w) * (x * w))
+        op = ht.optim.SGD(lr=0.1).minimize(loss)
+    g.run(loss, [loss, op], {x: np.ones((2, 3), np.float32)}, 1, 0, ht.run_level("update"))
+    np.testing.assert_allclose(np.array(w.get_data()), 0.6, rtol=1e-6)
+    with pytest.raises(ValueError):
+        ht.optim.SGD(lr=0.1).step()

@@ -13,6 +13,8 @@ from hotspa_ae_b200.graph.graph import (delete_graph, get_default_define_and_run
                                         get_default_define_by_run_graph, get_default_eager_graph, get_graph,
                                         make_new_define_and_run_graph, make_new_eager_graph)
 from hotspa_ae_b200.graph.gradscaler import GradScaler  # noqa: F401
+from hotspa_ae_b200.graph.ctors import (empty, empty_like, full, full_like, ones, rand, rand_like, randn,  # noqa: F401
+                                        randn_like, trunc_randn, trunc_randn_like, zeros)
 from hotspa_ae_b200.utils.dataset import Dataloader  # noqa: F401
 from hotspa_ae_b200.core.stream import Event, Stream, get_stream  # noqa: F401
 from hotspa_ae_b200.core.ndarray import NDArray, numpy_to_NDArray  # noqa: F401

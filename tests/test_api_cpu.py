@@ -184,3 +184,29 @@ def test_reference_package_names_resolve():
     np.testing.assert_allclose(np.array(w.get_data()), 0.6, rtol=1e-6)
     with pytest.raises(ValueError):
         ht.optim.SGD(lr=0.1).step()
+
+
+def test_tensor_constructors():
+    from hotspa_ae_b200.parallel import mesh as M
+    M.reset_mesh()
+    ht.init_comm_group(8)
+    with ht.graph("define_and_run") as g:
+        z = ht.zeros([2, 3], name="z")
+        o = ht.ones([4], dtype=ht.float32, requires_grad=True)
+        f = ht.full([2], 7.5)
+        r = ht.rand([2000], -1.0, 3.0)
+        n = ht.randn([4000], 1.0, 0.5)
+        t = ht.trunc_randn([2000], 0.0, 1.0, -0.5, 0.5)
+        fl = ht.full_like(z, 2.0)
+        rl = ht.randn_like(o)
+        e = ht.empty_like(n)
+        x = ht.placeholder(ht.float32, [1], name="x")
+    assert z.is_parameter and not z.requires_grad and o.requires_grad and fl.global_shape == [2, 3]
+    g.run(None, [x], {x: np.zeros(1, np.float32)}, 1, 0, ht.run_level("alloc"))
+    get = lambda p: np.array(p.get_data())       # noqa: E731
+    assert get(z).sum() == 0 and get(o).sum() == 4 and np.allclose(get(f), 7.5) and np.allclose(get(fl), 2.0)
+    rv, nv, tv = get(r), get(n), get(t)
+    assert rv.min() >= -1.0 and rv.max() <= 3.0 and abs(rv.mean() - 1.0) < 0.15
+    assert abs(nv.mean() - 1.0) < 0.05 and abs(nv.std() - 0.5) < 0.05
+    assert tv.min() >= -0.5 and tv.max() <= 0.5
+    assert get(rl).shape == (4,) and get(e).shape == (4000,)

@@ -199,6 +199,62 @@ class Tensor:
             return v.detach().float().cpu().numpy() if v.is_floating_point() else v.cpu().numpy()
         raise ValueError(f"{self} has no value outside a run; fetch it through graph.run")
 
+    def get_or_compute(self):
+        """The tensor's value as an NDArray, computed now when the graph kind allows it (reference:
+        Tensor::get_or_compute)."""
+        from ..core.ndarray import NDArray
+        return NDArray(self.numpy())
+
+    def dim(self) -> int:
+        return self.ndim
+
+    def size(self, dim: int | None = None):
+        """Local shape (one device's shard), or one entry of it."""
+        shp = self.local_shape()
+        return shp if dim is None else shp[dim]
+
+    def stride(self, dim: int | None = None):
+        """Strides of the contiguous local shard, in elements."""
+        shp, st, acc = self.local_shape(), [], 1
+        for n in reversed(shp):
+            st.append(acc)
+            acc *= n
+        st.reverse()
+        return st if dim is None else st[dim]
+
+    def to(self, dtype=None, device=None, name=None):
+        """A cast of this tensor (reference: DataTransferOp); placement follows the strategy, so a device argument
+        is accepted and ignored."""
+        if dtype is None or dtype == self.dtype:
+            return self
+        from . import ops
+        return ops.cast(self, dtype, name=name)
+
+    def symbolic(self):
+        """The symbolic shape: entries are IntSymbols that follow later `set_data` calls."""
+        return list(self.symbolic_shape)
+
+    @property
+    def is_variable(self) -> bool:
+        return bool(self.is_parameter)
+
+    @property
+    def data(self):
+        return self.get_or_compute()
+
+    @property
+    def device(self):
+        from ..parallel import mesh as M
+        return M.mesh().local_device()
+
+    @property
+    def placement_group_union(self):
+        return self.get_device_group_union()
+
+    @property
+    def has_placement_group(self) -> bool:
+        return bool(self.get_device_group_union())
+
     def reset_data(self, array: np.ndarray) -> None:
         """Overwrite a parameter from a *global* numpy array (sliced by the current strategy-0 DS)."""
         self.graph.reset_param_data(self, array)

@@ -210,3 +210,20 @@ def test_tensor_constructors():
     assert abs(nv.mean() - 1.0) < 0.05 and abs(nv.std() - 0.5) < 0.05
     assert tv.min() >= -0.5 and tv.max() <= 0.5
     assert get(rl).shape == (4,) and get(e).shape == (4000,)
+
+
+def test_tensor_accessors():
+    from hotspa_ae_b200.parallel import mesh as M
+    M.reset_mesh()
+    ht.init_comm_group(8)
+    with ht.graph("define_and_run") as g:
+        x = ht.placeholder(ht.float32, [4, 6], name="x")
+        w = ht.ones([6, 3], name="w")
+        y = ht.matmul(x, w)
+        h = y.to(ht.bfloat16)
+    assert x.dim() == 2 and x.size() == [4, 6] and x.size(1) == 6 and x.stride() == [6, 1] and x.stride(0) == 6
+    assert w.is_variable and not x.is_variable and h.dtype == ht.bfloat16 and y.to(ht.float32) is y
+    assert len(x.symbolic()) == 2 and x.has_placement_group and x.placement_group_union[0].ranks() == [0]
+    assert str(x.device).startswith("localhost")
+    g.run(None, [y], {x: np.ones((4, 6), np.float32)}, 1, 0, ht.run_level("grad"))
+    assert w.get_or_compute().numpy().sum() == 18 and w.data.shape == [6, 3]

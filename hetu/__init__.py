@@ -9,6 +9,7 @@ from hotspa_ae_b200.core import (DistributedStates, DistributedStatesUnion, IntS
 from hotspa_ae_b200.graph.graph import (Graph, autocast, from_numpy, from_numpy_parallel, graph,  # noqa: F401
                                         merge_strategy, parallel_parameter, parallel_placeholder, placeholder,
                                         recompute, run_level)
+from hotspa_ae_b200.graph.graph import get_autocast, get_default_autocast  # noqa: F401
 from hotspa_ae_b200.graph.graph import (delete_graph, get_default_define_and_run_graph,  # noqa: F401
                                         get_default_define_by_run_graph, get_default_eager_graph, get_graph,
                                         make_new_define_and_run_graph, make_new_eager_graph)
@@ -26,6 +27,7 @@ from hotspa_ae_b200.graph.ops_extra import *  # noqa: F401,F403
 from hotspa_ae_b200.graph.ops_extra import sum  # noqa: F401,A004
 from hotspa_ae_b200.graph.tensor import Tensor, bfloat16, bool_, float16, float32, int32, int64  # noqa: F401
 from hotspa_ae_b200.optim import AdamOptimizer, Optimizer, SGDOptimizer  # noqa: F401
+from hotspa_ae_b200.parallel.mesh import get_local_hostname  # noqa: F401
 from hotspa_ae_b200.parallel.mesh import (Device, DeviceGroup, global_comm_barrier, global_device_group,  # noqa: F401
                                           init_comm_group, local_device)
 from hotspa_ae_b200 import nn  # noqa: F401

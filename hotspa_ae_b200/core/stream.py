@@ -33,6 +33,23 @@ class Stream:
     def cuda_stream(self):
         return self._cuda
 
+    # spellings of the reference's Stream (hetu/core/stream.h:8-60)
+    @property
+    def stream_index(self) -> int:
+        return self.index
+
+    @property
+    def device_type(self) -> str:
+        return self.device.type
+
+    @property
+    def device_index(self) -> int:
+        return self.device.index or 0
+
+    @property
+    def is_define(self) -> bool:
+        return True
+
     def __enter__(self):
         if self._cuda is not None:
             self._ctx = torch.cuda.stream(self._cuda)

@@ -33,6 +33,7 @@ PYBIND11_MODULE(_hsb_core, m) {
       .def("check_equal", &DistributedStates::check_equal)
       .def("check_max_dim", &DistributedStates::check_max_dim)
       .def("map_device_to_state_index", &DistributedStates::map_device_to_state_index)
+      .def("map_to_local_data", &DistributedStates::map_device_to_state_index)
       .def("get_dup_group_index", &DistributedStates::get_dup_group_index)
       .def("get_devices_by_dim", &DistributedStates::get_devices_by_dim)
       .def("get_loop_sizes", &DistributedStates::get_loop_sizes)
@@ -212,6 +213,7 @@ PYBIND11_MODULE(_hsb_core, m) {
       .def(py::init<>())
       .def(py::init<int64_t>())
       .def("set_data", &IntSymbol::set)
+      .def("reset_data", &IntSymbol::set)
       .def_property("data", &IntSymbol::get, &IntSymbol::set)
       .def("get_data", &IntSymbol::get)
       .def("is_leaf", &IntSymbol::is_leaf)

@@ -141,6 +141,16 @@ def autocast(dtype=torch.bfloat16):
         g.autocast_dtype = prev if _autocast_stack else g.autocast_dtype
 
 
+def get_autocast():
+    """dtype of the innermost active `ht.autocast(...)` context, or None (reference: AutoCast::cur_autocast_ctx)."""
+    return _autocast_stack[-1] if _autocast_stack else None
+
+
+def get_default_autocast():
+    """The autocast state outside every context: casting disabled."""
+    return None
+
+
 @contextlib.contextmanager
 def recompute():
     """Ops created inside are re-executed during backward instead of keeping their activations."""
@@ -191,6 +201,20 @@ class Graph:
         self._by_name: dict[str, Tensor] = {}
 
     # ---- definition -------------------------------------------------------------------------
+    @property
+    def cur_hetero_id(self) -> int:
+        """Index of the union member (pipeline) this process works in under the current strategy."""
+        return getattr(self, "pipeline_of", {}).get((self.cur_strategy_id, M.mesh().rank), 0)
+
+    @property
+    def use_hetero_id(self) -> bool:
+        return any(len(t.dg_hierarchy[self.cur_strategy_id]) > 1 for t in self.parameters
+                   if self.cur_strategy_id < len(t.dg_hierarchy))
+
+    def merge_strategy(self, num_strategy: int = 1):
+        """Context manager form of `ht.merge_strategy(self, num_strategy)`."""
+        return merge_strategy(self, num_strategy)
+
     def set_num_strategy(self, n: int) -> None:
         """Only before the first op: afterwards strategies are appended with `merge_strategy`."""
         if self.ops or self.parameters or self.placeholders:

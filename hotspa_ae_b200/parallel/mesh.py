@@ -26,6 +26,28 @@ class Device:
     def __repr__(self) -> str:
         return f"{self.hostname}:{self.type}:{self.local_index}(rank {self.index})"
 
+    # spellings of the reference's Device (hetu/core/device.h:58-135)
+    @property
+    def is_cpu(self) -> bool:
+        return self.type == "cpu"
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.type == "cuda"
+
+    @property
+    def is_undetermined(self) -> bool:
+        return self.type not in ("cpu", "cuda")
+
+    @property
+    def local(self) -> bool:
+        """Whether the device sits on this process's node."""
+        return self.hostname == os.environ.get("HETU_LOCAL_HOSTNAME", "localhost")
+
+    @property
+    def multiplex(self) -> int:
+        return 0
+
 
 class DeviceGroup:
     """Ordered list of devices (reference: hetu/core/device.h DeviceGroup)."""
@@ -42,6 +64,10 @@ class DeviceGroup:
 
     def __len__(self) -> int:
         return len(self._devices)
+
+    @property
+    def empty(self) -> bool:
+        return self.num_devices == 0
 
     def contains(self, dev) -> bool:
         idx = dev.index if isinstance(dev, Device) else int(dev)
@@ -167,6 +193,10 @@ def mesh() -> Mesh:
 def reset_mesh() -> None:
     global _MESH
     _MESH = None
+
+
+def get_local_hostname() -> str:
+    return os.environ.get("HETU_LOCAL_HOSTNAME", "localhost")
 
 
 def local_device() -> Device:

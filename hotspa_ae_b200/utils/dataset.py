@@ -164,6 +164,21 @@ class Dataloader:
         for _ in range(self.batch_num):
             yield self.get_next_arr()
 
+    # spellings of the reference's bound Dataloader (python_refactor/hetu/_binding/graph/dataloader.cc)
+    @property
+    def sample_num(self) -> int:
+        return self.samples_num
+
+    @property
+    def num_workers(self) -> int:
+        return 0
+
+    def get_data(self):
+        return self.get_arr()
+
+    def get_next_data(self):
+        return self.get_next_arr()
+
 
 class LlamaJsonDataset(Dataset):
     def __init__(self, json_file: str, key: str, max_seq_len: int, vocab_file: str, merge_file: str,

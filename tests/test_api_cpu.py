@@ -227,3 +227,33 @@ def test_tensor_accessors():
     assert str(x.device).startswith("localhost")
     g.run(None, [y], {x: np.ones((4, 6), np.float32)}, 1, 0, ht.run_level("grad"))
     assert w.get_or_compute().numpy().sum() == 18 and w.data.shape == [6, 3]
+
+
+def test_reference_spellings_on_core_classes():
+    import torch
+    from hotspa_ae_b200.parallel import mesh as M
+    M.reset_mesh()
+    ht.init_comm_group(8)
+    d = ht.local_device()
+    assert d.is_cpu and not d.is_cuda and not d.is_undetermined and d.local and d.multiplex == 0
+    assert ht.get_local_hostname() == "localhost"
+    grp = ht.DeviceGroup([0])
+    assert not grp.empty and ht.DeviceGroup([]).empty
+    st = ht.get_stream(1) if ht.get_stream.__code__.co_argcount == 1 else ht.get_stream(torch.device("cpu"), 1)
+    assert st.stream_index == 1 and st.device_type == "cpu" and st.is_define and st.device_index == 0
+    s = ht.IntSymbol(3)
+    s.reset_data(5)
+    assert s.data == 5 and s.is_leaf()
+    ds = ht.DistributedStates(4, {0: 2, -1: 2}, [0, -1])
+    assert dict(ds.map_to_local_data(3)) == dict(ds.map_device_to_state_index(3))
+    dl = ht.Dataloader(np.arange(20).reshape(10, 2), 4)
+    assert dl.batch_size == 4 and dl.batch_num == 2 and dl.sample_num == 10 and dl.num_workers == 0
+    first = dl.get_data()
+    assert np.array_equal(dl.get_next_data(), first) and not np.array_equal(dl.get_data(), first)
+    assert ht.get_autocast() is None and ht.get_default_autocast() is None
+    with ht.graph("define_and_run") as g:
+        with ht.autocast(ht.bfloat16):
+            assert ht.get_autocast() == ht.bfloat16
+        assert g.cur_hetero_id == 0 and not g.use_hetero_id
+        with g.merge_strategy(1):
+            pass

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 from ..parallel import mesh as M
@@ -65,7 +66,35 @@ def parse_args(argv=None):
     ap.add_argument("--save_checkpoint", default="", help="directory to write a checkpoint into after training")
     ap.add_argument("--load_checkpoint", default="", help="directory (or .bin file) to load weights from")
     ap.add_argument("--use_flash_attn", action="store_true", help="accepted for compatibility (always on)")
+    ap.add_argument("--run_memory_experiment", action="store_true",
+                    help="run the first step only and write this rank's memory figures to --memory_file")
+    ap.add_argument("--memory_file", default="", help="result file of --run_memory_experiment (JSON)")
+    ap.add_argument("--test_func", action="store_true", help="accepted for compatibility (unused by the reference too)")
+    ap.add_argument("--micro_batch_size", type=int, default=1,
+                    help="accepted for compatibility: micro-batches are packed rows / token budgets here")
+    ap.add_argument("--dataset", default="", help="dataset name, for log lines only")
+    ap.add_argument("--hidden_act", default="silu", help="accepted for compatibility: the Llama MLP is SwiGLU")
+    ap.add_argument("--dropout_prob", type=float, default=0.0, help="accepted for compatibility: Llama has no dropout")
     return ap.parse_args(argv)
+
+
+def memory_experiment(trainer, first_batch, path: str) -> dict:
+    """One step, then this rank's memory: allocator peaks, device usage as the driver library reports it (reference:
+    --run_memory_experiment with HETU_MEMORY_LOG_FILE, hotspa/llama_hot_switch.py:403-419)."""
+    import torch
+    from ..utils.profiler import CUDAProfiler
+    res = trainer.step(first_batch)
+    rec = {"rank": M.mesh().rank, "loss": res.loss, "tokens": res.tokens, "buckets": res.buckets}
+    rec.update(CUDAProfiler().memory_info())
+    if torch.cuda.is_available():
+        st = torch.cuda.memory_stats()
+        rec["allocated_peak_mb"] = st["allocated_bytes.all.peak"] / 2**20
+        rec["reserved_peak_mb"] = st["reserved_bytes.all.peak"] / 2**20
+    if path:
+        root, ext = os.path.splitext(path)
+        with open(f"{root}_rank{M.mesh().rank}{ext or '.json'}", "w") as f:
+            json.dump(rec, f)
+    return rec
 
 
 def batches(args, trainer):
@@ -95,6 +124,11 @@ def main(argv=None):
     if args.load_checkpoint:
         from ..utils.checkpoint import load_checkpoint
         load_checkpoint(trainer.model, args.load_checkpoint, graph=trainer.graph)
+    if args.run_memory_experiment:
+        rec = memory_experiment(trainer, next(iter(batches(args, trainer))), args.memory_file)
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+        return 0
     logf = open(args.log_file, "a") if (args.log_file and rank == 0) else None
 
     def log(msg):

@@ -51,3 +51,20 @@ def test_without_a_gpu_the_benchmark_refuses_instead_of_falling_back():
                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
                           env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     assert proc.returncode != 0 and "needs a GPU" in proc.stdout
+
+
+def test_run_script_strategy_tables():
+    import re
+    script = os.path.join(ROOT, "hotspa_ae_b200", "train", "scripts", "llama_hot_switch.sh")
+    for model, seq, gpus, data in [("7b", 32768, 8, "synthetic"), ("7b", 16384, 8, "synthetic"), ("7b", 4096, 8, "x"),
+                                   ("13b", 32768, 8, "commoncrawl"), ("7b", 32768, 8, "github"), ("3b", 8192, 8, "x"),
+                                   ("7b", 32768, 4, "x"), ("7b", 32768, 2, "x"), ("7b", 32768, 1, "x")]:
+        proc = subprocess.run(["bash", script, model, str(seq), str(gpus), "3", data], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, timeout=60, env=dict(os.environ, DRY_RUN="1"))
+        assert proc.returncode == 0, proc.stdout
+        m = re.search(r"buckets \(([^)]*)\), strategies \(([^)]*)\)", proc.stdout)
+        buckets = [int(b) for b in m.group(1).split()]
+        strategies = [tuple(int(v) for v in s.split(",")) for s in m.group(2).split()]
+        assert buckets[0] == seq and buckets[-1] == 0 and buckets == sorted(buckets, reverse=True)
+        assert len(strategies) == len(buckets) - 1, proc.stdout
+        assert all(dp * tp * pp == gpus for dp, tp, pp in strategies), proc.stdout

@@ -30,9 +30,10 @@ N_BUCKETS=$(( $(echo ${BUCKET_SIZES} | wc -w) - 1 ))
 
 # strategies for the 32K bucket set (three buckets); shorter contexts take a suffix of the list
 KEY="${MODEL_SIZE}-${NUM_GPUS}-${DATASET}"
+if [ "${SEQ_LEN}" != "32768" ] && [ "${DATASET}" = "github" ]; then KEY="${MODEL_SIZE}-${NUM_GPUS}-commoncrawl"; fi   # the 4-strategy sets are 32K ones
 case "${KEY}" in
-  3b-8-*|7b-8-synthetic|7b-8-commoncrawl) STRATEGIES="1,4,2 8,1,1 2,2,2" ;;
   7b-8-github)        STRATEGIES="1,4,2 8,1,1 4,2,1 2,2,2"; BUCKET_SIZES="32768 16384 8192 4096 0"; N_BUCKETS=4 ;;
+  3b-8-*|7b-8-*)      STRATEGIES="1,4,2 8,1,1 2,2,2" ;;
   13b-8-github)       STRATEGIES="1,8,1 4,2,1 2,2,2 1,4,2"; BUCKET_SIZES="32768 16384 8192 4096 0"; N_BUCKETS=4 ;;
   13b-8-*)            STRATEGIES="1,8,1 4,2,1 1,4,2" ;;
   *-4-*)              STRATEGIES="1,4,1 4,1,1 2,2,1" ;;

@@ -242,3 +242,51 @@ def build_normal_data_loader(dataset, consumed_samples: int, global_batch_size: 
 def build_dist_data_loader(dataset, consumed_samples: int, micro_batch_size: int, dp_rank: int, dp_size: int):
     return DataLoader(dataset, batch_sampler=DistBatchSampler(len(dataset), consumed_samples, micro_batch_size,
                                                               dp_rank, dp_size))
+
+
+def parquet_to_jsonl(parquet_file: str, json_file: str, columns=None, limit: int | None = None) -> int:
+    """Dataset preparation: one JSON object per row of a parquet shard (the form `LlamaJsonDataset` reads;
+    reference: hotspa/data_utils/create_web_dataset.py).  Streams row groups instead of materialising the table.
+    Returns the number of rows written."""
+    import pyarrow.parquet as pq
+    pf = pq.ParquetFile(parquet_file)
+    n = 0
+    os.makedirs(os.path.dirname(os.path.abspath(json_file)), exist_ok=True)
+    with open(json_file, "w") as f:
+        for batch in pf.iter_batches(batch_size=4096, columns=columns):
+            for row in batch.to_pylist():
+                f.write(json.dumps(row, ensure_ascii=False, default=str) + "\n")
+                n += 1
+                if limit is not None and n >= limit:
+                    return n
+    return n
+
+
+def _main(argv=None) -> int:
+    """`python -m hotspa_ae_b200.utils.dataset`: convert a parquet shard and / or build the token cache of a json
+    dataset and print a few batches (reference: the __main__ of hotspa/data_utils/llama_dataset.py)."""
+    import argparse
+    ap = argparse.ArgumentParser(description=_main.__doc__)
+    ap.add_argument("--parquet", default="", help="parquet shard to convert into --json_file first")
+    ap.add_argument("--json_file", required=True)
+    ap.add_argument("--json_key", default="content")
+    ap.add_argument("--vocab_file", default="")
+    ap.add_argument("--merge_file", default="")
+    ap.add_argument("--max_seq_len", type=int, default=4096)
+    ap.add_argument("--limit", type=int, default=0)
+    ap.add_argument("--show", type=int, default=5, help="batches to print")
+    a = ap.parse_args(argv)
+    if a.parquet:
+        rows = parquet_to_jsonl(a.parquet, a.json_file, limit=a.limit or None)
+        print(f"wrote {rows} rows to {a.json_file}")
+    if not (a.vocab_file and a.merge_file):
+        return 0
+    ds = LlamaJsonDataset(a.json_file, a.json_key, a.max_seq_len, a.vocab_file, a.merge_file)
+    print(f"{len(ds)} documents, token cache next to {a.json_file}")
+    for i, batch in enumerate(global_batches(ds, 4, a.show)):
+        print(i, [len(s) for s in batch])
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

@@ -87,3 +87,19 @@ def test_token_budget_micro_batches_follow_replica_shares():
     import pytest
     with pytest.raises(ValueError):
         D.token_budget_micro_batches(seqs, members, 2, 0, 4096, 0, 8, shares=[1.0])
+
+
+def test_parquet_to_jsonl(tmp_path):
+    import json
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from hotspa_ae_b200.utils import dataset as DSM
+    rows = [{"content": f"document {i} " * (i + 1), "url": f"http://x/{i}"} for i in range(10)]
+    pq.write_table(pa.Table.from_pylist(rows), tmp_path / "shard.parquet")
+    n = DSM.parquet_to_jsonl(str(tmp_path / "shard.parquet"), str(tmp_path / "out" / "web.json"))
+    lines = (tmp_path / "out" / "web.json").read_text().splitlines()
+    assert n == 10 == len(lines) and json.loads(lines[3]) == rows[3]
+    assert DSM.parquet_to_jsonl(str(tmp_path / "shard.parquet"), str(tmp_path / "few.json"), columns=["content"],
+                                limit=4) == 4
+    assert set(json.loads((tmp_path / "few.json").read_text().splitlines()[0])) == {"content"}
+    assert DSM._main(["--parquet", str(tmp_path / "shard.parquet"), "--json_file", str(tmp_path / "cli.json")]) == 0

@@ -79,3 +79,28 @@ def test_replan_and_switch_keeps_training_state():
 def test_replan_into_a_heterogeneous_strategy_keeps_training_state():
     # the slow device's replica splits its layers 3 | 1, the healthy replica 2 | 2: one pipeline per replica
     _run_elastic_worker("--hetero")
+
+
+def test_engine_argument_records():
+    import hetu as ht
+    from hotspa_ae_b200.elastic import utils as U
+    from hotspa_ae_b200.models.llama import LlamaLMHeadModel, llama_config
+    ctx = U.TrainerCtxs()
+    assert abs(ctx.tp_efficiency()[2] - 0.95) < 1e-9 and ctx.layer_memory_gb(4, 2, True) == 4 * 0.5 + 1.0 + 4.0
+    with pytest.raises(ValueError):
+        U.TrainerCtxs(straggler_threshold=1.0)
+    assert "TrainerEnvs(run_straggler_experiment = False" in str(U.TrainerEnvs())
+    # two pipelines of two stages, tp 2; rank 5 is dropped from its group; pipeline 1 splits its layers 3 | 1
+    st = U.TrainerStrategyArgs(dp=2, tp=2, pp=2, hetero_layers=[[2, 2], [3, 1]], unused_rank_list=[5])
+    pipes = st.pipelines()
+    assert pipes == [[{"ranks": [0, 1], "layers": 2}, {"ranks": [2, 3], "layers": 2}],
+                     [{"ranks": [4], "layers": 3}, {"ranks": [6, 7], "layers": 1}]]
+    cfg = st.to_config(4)
+    assert cfg["devices"] == [0, 1, 2, 3, 4, 6, 7]
+    u, groups = ht.nn.config2ds(dict(cfg["llama"]["blocks"]["blocks0"]["attn"]["qkv"], zero=False))
+    assert [g.ranks() for g in groups] == [[0, 1], [4]] and u.get_local(1).device_num == 1
+    assert U.TrainerStrategyArgs(dp=2, tp=2, pp=2, zero=True).to_config(4)["zero"] is True      # plain 3-D form
+    with pytest.raises(ValueError):
+        U.TrainerStrategyArgs(dp=2, tp=1, pp=2, hetero_layers=[[2, 2]])
+    mw = U.ModelWrapper(LlamaLMHeadModel, llama_config("tiny", num_layers=4))
+    assert mw.model_class is LlamaLMHeadModel and U.OptimizerWrapper(ht.AdamOptimizer).create_optimizer(lr=1e-3).lr == 1e-3

@@ -110,3 +110,41 @@ def test_descriptor_tables_of_a_real_plan_are_valid(monkeypatch):
         moved = int((descs[:, 2] * descs[:, 3]).sum())
         mine = [c for c in plan["all"] if c.dst_rank == rank]
         assert moved == sum(c.rows * c.row_elems for c in mine) * esz
+
+
+def _graph_for(model, strategies, rank=0):
+    M.reset_mesh()
+    ht.init_comm_group(8, world_size=8, rank=rank, virtual=True)
+    cfg = llama_config(model, num_layers=2 if model != "13b" else 4, vocab_size=32000)
+    cfgs = [propagate_zero(generate_llama_3d_config(cfg.num_layers, 8, dp, tp, pp, z)) for dp, tp, pp, z in strategies]
+    with ht.graph("define_and_run", num_strategy=len(cfgs)) as g:
+        with ht.autocast(torch.bfloat16):
+            LlamaLMHeadModel(cfg, cfgs)
+    return g
+
+
+def test_golden_traffic_of_the_benchmark_strategy_sets():
+    """Closed forms: into dp8 every rank must end with the whole model and holds 1/8 of it under tp4pp2, so
+    7 x (model size) elements cross links; out of dp8 nothing moves; gradients into the tp4pp2 home: every rank sends
+    its copy of everything it does not keep."""
+    for model, strategies in (("7b", STRATEGIES), ("13b", [(1, 8, 1, False), (4, 2, 1, True), (1, 4, 2, False)])):
+        g = _graph_for(model, strategies)
+        store = ParamStore(g)
+        total = sum(int(np.prod(p.global_shape)) for p in g.parameters)
+        split = sum(int(np.prod(p.global_shape)) for p in g.parameters if p.ds(0).get_dim(-1) < 8)   # not replicated
+        for src in range(3):
+            for dst in range(3):
+                if src == dst:
+                    continue
+                plan = store._plan(src, dst, "param")
+                need = sum(sum(e.numel for e in store.layout(dst, r).entries.values()) for r in range(8))
+                assert plan["remote_elems"] + plan["local_elems"] == need
+        if model == "7b":
+            to_dp8 = store._plan(0, 2, "param")
+            held = sum(sum(e.numel for e in store.layout(0, r).entries.values()) for r in range(8))
+            # every rank needs `total`; what it already holds under tp4pp2 stays local
+            assert to_dp8["remote_elems"] == 8 * total - to_dp8["local_elems"]
+            assert to_dp8["local_elems"] <= held and split > 0
+            assert store._plan(2, 0, "param")["remote_elems"] == 0 and store._plan(2, 1, "param")["remote_elems"] == 0
+            back = store._plan(2, 0, "grad")
+            assert back["remote_elems"] + back["local_elems"] == 8 * total

@@ -75,3 +75,8 @@ def test_device_group_parallel_layers_on_two_ranks():
     # column-parallel -> row-parallel linear and a vocab-parallel embedding; the row-parallel bias is replicated and
     # sees replicated activations, so its replicas' identical gradients must count once
     _torchrun("nn_parallel_worker.py", 2, marker="NN_PARALLEL_OK", timeout=600)
+
+
+def test_tensor_parallel_without_sequence_parallel():
+    # all-reduce after the row-parallel linear; norm weight and biases are replicated next to replicated activations
+    _torchrun("nonsp_tp_worker.py", 2, marker="NONSP_TP_OK", timeout=600)

@@ -28,6 +28,8 @@ class LlamaConfig:
     reference_parity: bool = False     # LayerNorm with bias, no RoPE (the reference's "LLaMA")
     recompute: bool = False            # re-run each block in backward instead of keeping activations
     init_std: float = 0.02
+    sequence_parallel: bool = True     # Megatron sequence parallelism between the tensor-parallel regions; False:
+                                       # activations stay replicated over tp and row-parallel outputs are all-reduced
     uniform_trace: bool = False        # issue the same op sequence whatever the pipeline split (needed when strategies
                                        # with other stage boundaries are merged into the graph later)
 
@@ -53,8 +55,9 @@ def llama_config(size: str, **overrides) -> LlamaConfig:
 
 def _norm(config, cfgs, name):
     if config.reference_parity:
-        return ht.nn.HtMultiParallelLayerNorm(config.hidden_size, cfgs, sp=True, name=name)
-    return ht.nn.HtMultiParallelRMSNorm(config.hidden_size, cfgs, sp=True, eps=config.rms_eps, name=name)
+        return ht.nn.HtMultiParallelLayerNorm(config.hidden_size, cfgs, sp=config.sequence_parallel, name=name)
+    return ht.nn.HtMultiParallelRMSNorm(config.hidden_size, cfgs, sp=config.sequence_parallel, eps=config.rms_eps,
+                                        name=name)
 
 
 class LlamaAttention(ht.nn.Module):
@@ -67,7 +70,8 @@ class LlamaAttention(ht.nn.Module):
             h, 3 * h, get_multi_ds_parallel_config(ds_parallel_configs, "qkv", layer_idx), bias=False,
             gather_output=False, init_method=init, name=f"colp_{name}")
         self.dense = ht.nn.HtMultiRowParallelLinear(
-            h, h, get_multi_ds_parallel_config(ds_parallel_configs, "dense", layer_idx), sp=True, bias=False,
+            h, h, get_multi_ds_parallel_config(ds_parallel_configs, "dense", layer_idx), sp=config.sequence_parallel,
+            bias=False,
             init_method=init, name=f"rowp_{name}")
 
     def forward(self, x, position_ids, cu_seqlens):
@@ -87,7 +91,8 @@ class LlamaMLP(ht.nn.Module):
             h, 2 * f, get_multi_ds_parallel_config(ds_parallel_configs, "dense_h_to_4h", layer_idx), bias=False,
             gather_output=False, init_method="normal_", name=f"colp_{name}")
         self.dense_4h_to_h = ht.nn.HtMultiRowParallelLinear(
-            f, h, get_multi_ds_parallel_config(ds_parallel_configs, "dense_4h_to_h", layer_idx), sp=True, bias=False,
+            f, h, get_multi_ds_parallel_config(ds_parallel_configs, "dense_4h_to_h", layer_idx),
+            sp=config.sequence_parallel, bias=False,
             init_method="normal_", name=f"rowp_{name}")
 
     def forward(self, x):
@@ -131,6 +136,13 @@ class LlamaModel(ht.nn.Module):
         self.rmsnorm_f = _norm(config, get_multi_ds_parallel_config(ds_parallel_configs, "layernorm_final"),
                                "rmsnorm_final")
 
+    def _act_layout(self, block):
+        """Layout of the hidden states between blocks: rows split over dp x tp with sequence parallelism, rows split
+        over dp and replicated over tp without it."""
+        if self.config.sequence_parallel:
+            return (block.rmsnorm_1 if block is not None else self.rmsnorm_f).ds_union_map["split0"]
+        return (block if block is not None else self.h[-1]).mlp.dense_h_to_4h.ds_union_map["split0_dup"]
+
     def forward(self, input_ids, position_ids, cu_seqlens):
         c = self.config
         x = self.wte(input_ids)                                   # [b, s, h] (partial over tp when vocab-parallel)
@@ -143,7 +155,7 @@ class LlamaModel(ht.nn.Module):
                 [g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, groups))
             if (crosses or c.uniform_trace) and residual is not None:
                 x, residual = x + residual, None                  # one tensor crosses the stage boundary
-            x = ht.comm(x, block.rmsnorm_1.ds_union_map["split0"], groups, name=f"pipeline_layer_{block.layer_idx}_comm")
+            x = ht.comm(x, self._act_layout(block), groups, name=f"pipeline_layer_{block.layer_idx}_comm")
             if c.recompute:
                 with ht.recompute():
                     x, residual = block(x, residual, position_ids, cu_seqlens)
@@ -153,7 +165,7 @@ class LlamaModel(ht.nn.Module):
         fin_groups = self.rmsnorm_f.device_group_unions
         if c.uniform_trace or any([g.ranks() for g in a] != [g.ranks() for g in b] for a, b in zip(prev_groups, fin_groups)):
             x, residual = x + residual, None
-            x = ht.comm(x, self.rmsnorm_f.ds_union_map["split0"], fin_groups, name="pipeline_final_comm")
+            x = ht.comm(x, self._act_layout(None), fin_groups, name="pipeline_final_comm")
         return self.rmsnorm_f(x, residual)[0] if residual is not None else self.rmsnorm_f(x)
 
 

@@ -384,11 +384,11 @@ class ParamStore:
             view.copy_(PC.split_all_reduce(view, groups, dim))
 
     def _replicated_grad_params(self, sid: int) -> list:
-        """Parameters whose replicas all compute the SAME gradient: every tensor they are combined with is a pure
-        duplicate over their devices (e.g. a bias added to an all-reduced activation).  The reduction over the
-        duplicate group is a sum of partial contributions for every other parameter; for these it would count the
-        gradient once per replica, so the executor divides what a run added to their accumulators by the replica
-        count (`Executor.run`).
+        """(parameter, k) for the parameters of which k replicas (this rank included) compute the SAME gradient: they
+        hold the same shard of every activation the parameter meets (e.g. a bias added to an all-reduced activation,
+        a norm weight under tensor parallelism without sequence parallelism).  The reduction over a parameter's
+        duplicate group sums partial contributions; identical ones would be counted k times, so the executor divides
+        what a run added to these accumulators by k (`Executor.run`).
         (The reference gets the same effect from the DS of the gradient: duplicate, not partial, hence no reduce.)"""
         key = ("replicated_grads", sid)
         if key in self.plans:
@@ -399,26 +399,33 @@ class ParamStore:
                 if t.is_parameter:
                     consumers.setdefault(t.id, []).append(op)
         out = []
+        me = self.rank
         for p in self.graph.parameters:
-            if not p.requires_grad:
+            if not p.requires_grad or p.id not in consumers:
                 continue
-            ds = p.ds(sid)
-            n = ds.get_dim(-1)
-            if n <= 1 or p.id not in consumers:
+            pg = p.group(sid)
+            if not pg.contains(me):
                 continue
-            same = True
+            mine = set(p.ds(sid).get_devices_by_dim(-1, pg.get_index(me), pg.ranks()))     # my replicas of p
+            if len(mine) <= 1:
+                continue
+            # replicas of p that hold the same shard of every activation p meets compute the same gradient
+            same = set(mine)
             for op in consumers[p.id]:
                 for t in op.inputs:
-                    if t is p or t.is_parameter:
+                    if t is p or t.is_parameter or t.id in self.graph.constants:
+                        continue
+                    tg = t.group(sid)
+                    if not tg.contains(me):
+                        same = {me}
                         continue
                     tds = t.ds(sid)
-                    if not tds.is_pure_duplicate:
-                        same = False
-                for t in op.outputs:
-                    if t.ds(sid).get_dim(-2) > 1:
-                        same = False
-            if same:
-                out.append((p, n))
+                    if tds.get_dim(-2) > 1:
+                        same = {me}
+                        continue
+                    same &= set(tds.get_devices_by_dim(-1, tg.get_index(me), tg.ranks()))
+            if len(same) > 1:
+                out.append((p, len(same)))
         self.plans[key] = out
         return out
 

@@ -28,13 +28,14 @@ def main():
     ap.add_argument("--switch_mode", type=str, default="nccl")
     ap.add_argument("--device", type=str, default="cpu")
     ap.add_argument("--tol", type=float, default=2e-4)
+    ap.add_argument("--no_sp", action="store_true", help="tensor parallelism without sequence parallelism")
     args = ap.parse_args()
     strategies = [tuple(s) for s in json.loads(args.strategies)]
     plan = json.loads(args.plan)
     ht.init_comm_group(8)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    cfg = llama_config("tiny", max_seq_len=256, num_layers=4)
+    cfg = llama_config("tiny", max_seq_len=256, num_layers=4, sequence_parallel=not args.no_sp)
     b = build_llama_graph(cfg, strategies, world, lr=1e-3)
     g = b["graph"]
     g.executor.configure_switch(args.switch_mode)

@@ -17,8 +17,10 @@ from hotspa_ae_b200.utils import checkpoint as CK  # noqa: E402
 def main():
     ht.init_comm_group(8)
     rank = int(os.environ["RANK"])
-    cfg = propagate_zero(generate_llama_3d_config(1, 2, 1, 2, 1, False))
-    h, f, rows = 8, 12, 6
+    world = int(os.environ["WORLD_SIZE"])
+    dp = world // 2                                   # 2 ranks: tp2; 4 ranks: dp2 x tp2 (ranks (0, 1) and (2, 3))
+    cfg = propagate_zero(generate_llama_3d_config(1, world, dp, 2, 1, False))
+    h, f, rows = 8, 12, 6 * dp
     x_u, x_g = ht.nn.config2ds(cfg["input"])
     with ht.graph("define_and_run", num_strategy=1) as g:
         x = ht.parallel_placeholder(ht.float32, [rows, h], [x_u], [x_g], name="x")
@@ -31,6 +33,8 @@ def main():
         loss = ht.reduce_sum(y * y)
         train_op = ht.SGDOptimizer(lr=0.01).minimize(loss)
     xs = np.random.default_rng(0).standard_normal((rows, h)).astype(np.float32)
+    full_xs = xs
+    xs = np.split(xs, dp)[rank // 2]                  # this replica's rows
     g.run(loss, [loss, train_op], {x: xs}, 1, 0, ht.run_level("alloc"))
     params = {"g": norm.weight, "w1": col.weight, "b1": col.bias, "w2": row.weight, "b2": row.bias}
     # give the biases and the norm weight non-trivial values
@@ -41,13 +45,15 @@ def main():
     out = g.run(loss, [loss, train_op], {x: xs}, 1, 0, ht.run_level("update"))
     after = {k: CK.gather_global(g, p) for k, p in params.items()}
     ref = {k: v.clone().requires_grad_(True) for k, v in before.items()}
-    X = torch.tensor(xs)
+    X = torch.tensor(full_xs)
     n = X * torch.rsqrt(X.pow(2).mean(-1, keepdim=True) + 1e-6) * ref["g"]
     hmid = torch.relu(n @ ref["w1"].T + ref["b1"])
     yr = hmid @ ref["w2"] + ref["b2"]                # the row-parallel weight is stored [in, out]
     lr_ = (yr * yr).sum()
     lr_.backward()
-    got = float(np.asarray(out[0]).reshape(-1)[0])
+    mine = torch.tensor(float(np.asarray(out[0]).reshape(-1)[0]) if rank % 2 == 0 else 0.0)   # one rank per replica
+    torch.distributed.all_reduce(mine)
+    got = float(mine)
     ok = abs(got - float(lr_)) < 1e-3 * max(1.0, abs(float(lr_)))
     worst, where = 0.0, ""
     for k in params:

@@ -77,6 +77,13 @@ def test_device_group_parallel_layers_on_two_ranks():
     _torchrun("nn_parallel_worker.py", 2, marker="NN_PARALLEL_OK", timeout=600)
 
 
-def test_tensor_parallel_without_sequence_parallel():
-    # all-reduce after the row-parallel linear; norm weight and biases are replicated next to replicated activations
-    _torchrun("nonsp_tp_worker.py", 2, marker="NONSP_TP_OK", timeout=600)
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_without_sequence_parallel(world):
+    # all-reduce after the row-parallel linear; norm weight and biases are replicated next to activations that are
+    # replicated over tp (and, with 4 ranks, split over dp): SGD makes a miscounted replica visible
+    _torchrun("nonsp_tp_worker.py", world, marker="NONSP_TP_OK", timeout=600)
+
+
+@pytest.mark.parametrize("world,strategy", [(2, [1, 2, 1, False]), (4, [2, 2, 1, True]), (4, [1, 2, 2, False])])
+def test_llama_without_sequence_parallel_matches_single_process(world, strategy):
+    run_workers(world, [strategy], [[0, "update", 128, 4]], extra=["--no_sp"])

@@ -66,6 +66,8 @@ def parse_args(argv=None):
     ap.add_argument("--save_checkpoint", default="", help="directory to write a checkpoint into after training")
     ap.add_argument("--load_checkpoint", default="", help="directory (or .bin file) to load weights from")
     ap.add_argument("--use_flash_attn", action="store_true", help="accepted for compatibility (always on)")
+    ap.add_argument("--no_sequence_parallel", action="store_true",
+                    help="tensor parallelism with all-reduce instead of Megatron sequence parallelism")
     ap.add_argument("--run_memory_experiment", action="store_true",
                     help="run the first step only and write this rank's memory figures to --memory_file")
     ap.add_argument("--memory_file", default="", help="result file of --run_memory_experiment (JSON)")

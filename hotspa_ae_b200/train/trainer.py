@@ -336,6 +336,8 @@ def build_trainer_from_args(args) -> HotSwitchTrainer:
         v = getattr(args, attr, None)
         if v is not None and v > 0:
             overrides[key] = v
+    if getattr(args, "no_sequence_parallel", False):
+        overrides["sequence_parallel"] = False
     if cfgs is not None:
         # the reference convention lists strategies as: longest bucket first, then shortest ... second longest
         cfgs = [cfgs[0]] + list(reversed(cfgs[1:]))

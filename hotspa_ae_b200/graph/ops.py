@@ -15,7 +15,6 @@ from __future__ import annotations
 import math
 from typing import Any, Callable
 
-import numpy as np
 import torch
 
 from ..core import DistributedStates, IntSymbol, deduce_linear, sym_value

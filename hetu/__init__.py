@@ -27,6 +27,7 @@ from hotspa_ae_b200.graph.ops_extra import *  # noqa: F401,F403
 from hotspa_ae_b200.graph.ops_extra import sum  # noqa: F401,A004
 from hotspa_ae_b200.graph.tensor import Tensor, bfloat16, bool_, float16, float32, int32, int64  # noqa: F401
 from hotspa_ae_b200.optim import AdamOptimizer, Optimizer, SGDOptimizer  # noqa: F401
+from hotspa_ae_b200.optim import gradients, requires_grad_variables  # noqa: F401
 from hotspa_ae_b200.parallel.mesh import get_local_hostname  # noqa: F401
 from hotspa_ae_b200.parallel.mesh import (Device, DeviceGroup, global_comm_barrier, global_device_group,  # noqa: F401
                                           init_comm_group, local_device)

@@ -1,1 +1,2 @@
-from .optimizer import AdamOptimizer, Optimizer, SGD, SGDOptimizer  # noqa: F401
+from .optimizer import (AdamOptimizer, GradHandle, Optimizer, SGD, SGDOptimizer, gradients,  # noqa: F401
+                        requires_grad_variables)

@@ -160,3 +160,30 @@ class SGD(SGDOptimizer):
                 g = p.graph.from_numpy(g, requires_grad=False) if hasattr(p.graph, "from_numpy") else g
             ops.append(self.apply_dense(p, g))
         return ops
+
+
+def requires_grad_variables(loss) -> list:
+    """Trainable parameters `loss` depends on (reference: hetu.requires_grad_variables of the legacy binding)."""
+    seen, out, stack = set(), [], [loss]
+    while stack:
+        t = stack.pop()
+        if t.id in seen:
+            continue
+        seen.add(t.id)
+        if t.is_parameter:
+            if t.requires_grad:
+                out.append(t)
+            continue
+        if t.producer is not None:
+            stack += list(t.producer.inputs)
+    order = {p.id: i for i, p in enumerate(loss.graph.parameters)}
+    return sorted(out, key=lambda p: order.get(p.id, 0))
+
+
+def gradients(loss, var_list=None, grad_loss=None) -> list:
+    """Fetchable gradient handles of `loss` with respect to `var_list` (default: every trainable parameter behind
+    it), in order.  Fetch them together with a train op, or at run level "grad" with the loss."""
+    if grad_loss is not None:
+        raise NotImplementedError("a custom seed gradient is given through graph.run(grad_scale=...)")
+    vars_ = list(var_list) if var_list is not None else requires_grad_variables(loss)
+    return [GradHandle(v) for v in vars_]

@@ -257,3 +257,30 @@ def test_reference_spellings_on_core_classes():
         assert g.cur_hetero_id == 0 and not g.use_hetero_id
         with g.merge_strategy(1):
             pass
+
+
+def test_gradients_and_requires_grad_variables():
+    from hotspa_ae_b200.parallel import mesh as M
+    M.reset_mesh()
+    ht.init_comm_group(8)
+    rng = np.random.default_rng(5)
+    xs = rng.standard_normal((3, 4)).astype(np.float32)
+    with ht.graph("define_and_run") as g:
+        x = ht.placeholder(ht.float32, [3, 4], name="x")
+        a = ht.randn([4, 2], 0.0, 0.5, requires_grad=True, name="a")
+        b = ht.ones([2], requires_grad=True, name="b")
+        frozen = ht.ones([2], requires_grad=False, name="frozen")
+        unused = ht.ones([2], requires_grad=True, name="unused")
+        loss = ht.reduce_sum(ht.tanh(ht.matmul(x, a) + b) * frozen)
+        vars_ = ht.requires_grad_variables(loss)
+        ga, gb = ht.gradients(loss)
+    assert [v.name for v in vars_] == ["a", "b"] and unused not in vars_
+    g.run(loss, [loss], {x: xs}, 1, 0, ht.run_level("alloc"))
+    av, bv = torch.tensor(np.array(a.get_data()), requires_grad=True), torch.tensor(np.array(b.get_data()), requires_grad=True)
+    out = g.run(loss, [loss, ga, gb], {x: xs}, 1, 0, ht.run_level("grad"))
+    ref = torch.tanh(torch.tensor(xs) @ av + bv).sum()
+    ref.backward()
+    np.testing.assert_allclose(out[1].numpy(), av.grad.numpy(), rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(out[2].numpy(), bv.grad.numpy(), rtol=1e-5, atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        ht.gradients(loss, grad_loss=loss)

@@ -210,11 +210,38 @@ class Executor:
         my_stage = next((i for i, r in enumerate(stages) if rank in r), -1)
 
         my_ops, recv_ops, send_ops, comm, needed = [], [], [], {}, []
+        n_consumers: dict = {}
+        for op in g.ops:
+            for t in op.inputs:
+                n_consumers[t.id] = n_consumers.get(t.id, 0) + 1
+        read_from: dict = {}
+        real = (C._C.COMM_ALL_REDUCE, C._C.COMM_ALL_GATHER, C._C.COMM_REDUCE_SCATTER, C._C.COMM_SPLIT, C._C.COMM_SCATTER)
         for op in g.ops:
             if getattr(op.outputs[0], "is_train_op", False):
                 continue
             if op.type == "comm":
                 x, y = op.inputs[0], op.outputs[0]
+                # two collectives back to back inside one group become the single collective that realises the
+                # composite reshard (reference: ExecutableGraph::Instantiate fuses back-to-back comm ops); only when
+                # both are real collectives, so that comm + linear pairs keep their shape
+                prev = x.producer
+                if (prev is not None and prev.type == "comm" and n_consumers.get(x.id, 0) == 1
+                        and x.group(sid).ranks() == y.group(sid).ranks()
+                        == read_from.get(prev.id, prev.inputs[0]).group(sid).ranks()
+                        and x.ds_hierarchy[sid].hetero_dim == y.ds_hierarchy[sid].hetero_dim
+                        == read_from.get(prev.id, prev.inputs[0]).ds_hierarchy[sid].hetero_dim):
+                    x0 = read_from.get(prev.id, prev.inputs[0])     # what `prev` really reads (it may be fused already)
+                    ranks0 = x0.group(sid).ranks()
+                    one = C.DistributedStatesUnion
+                    # (decided from the layouts alone, so every rank decides alike and creates the same groups)
+                    k_prev = C.classify_comm(one([x0.ds(sid)]), ranks0, one([x.ds(sid)]), ranks0, 0)
+                    k_this = C.classify_comm(one([x.ds(sid)]), ranks0, one([y.ds(sid)]), ranks0, 0)
+                    k_both = C.classify_comm(one([x0.ds(sid)]), ranks0, one([y.ds(sid)]), ranks0, 0)
+                    if k_prev in real and k_this in real and (k_both in real or k_both == C._C.COMM_UNUSED):
+                        if prev.id in comm:
+                            comm[prev.id] = CommInfo(C._C.COMM_UNUSED, "fused_into_next")
+                        x = x0
+                        read_from[op.id] = x0
                 s_ranks, d_ranks = x.group(sid).ranks(), y.group(sid).ranks()
                 su, du = x.ds_hierarchy[sid], y.ds_hierarchy[sid]
                 if su.hetero_dim != du.hetero_dim:

@@ -87,3 +87,7 @@ def test_tensor_parallel_without_sequence_parallel(world):
 @pytest.mark.parametrize("world,strategy", [(2, [1, 2, 1, False]), (4, [2, 2, 1, True]), (4, [1, 2, 2, False])])
 def test_llama_without_sequence_parallel_matches_single_process(world, strategy):
     run_workers(world, [strategy], [[0, "update", 128, 4]], extra=["--no_sp"])
+
+
+def test_back_to_back_collectives_are_planned_as_one():
+    _torchrun("comm_fusion_worker.py", 2, marker="COMM_FUSION_OK", timeout=600)

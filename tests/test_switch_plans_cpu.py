@@ -148,3 +148,21 @@ def test_golden_traffic_of_the_benchmark_strategy_sets():
             assert store._plan(2, 0, "param")["remote_elems"] == 0 and store._plan(2, 1, "param")["remote_elems"] == 0
             back = store._plan(2, 0, "grad")
             assert back["remote_elems"] + back["local_elems"] == 8 * total
+
+
+def test_llama_plans_contain_no_chained_collectives():
+    """The model issues no two real collectives back to back, so the chain fusion leaves its plans (and with them the
+    comm + GEMM pairs the fused kernels take over) as they are."""
+    from hotspa_ae_b200 import core as C
+    from helpers import build_llama_graph
+    for rank in (0, 5):
+        M.reset_mesh()
+        ht.init_comm_group(8, world_size=8, rank=rank, virtual=True)
+        g = build_llama_graph(llama_config("tiny", num_layers=4), STRATEGIES, 8)["graph"]
+        for sid in range(3):
+            plan = g.executor.plan(sid)
+            names = [info.name for info in plan.comm.values()]
+            assert "fused_into_next" not in names, (rank, sid)
+            kinds = {C.comm_type_name(i.kind) for i in plan.comm.values()}
+            if STRATEGIES[sid][1] > 1:
+                assert {"ALL_GATHER", "REDUCE_SCATTER"} <= kinds, (rank, sid, kinds)

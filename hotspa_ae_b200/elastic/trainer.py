@@ -29,7 +29,7 @@ from .strategy import Plan, StrategyModel, to_config_args, to_hetero_pipelines
 
 class ElasticTrainer(HotSwitchTrainer):
     def __init__(self, model="7b", strategy=(1, 1, 1, False), max_len: int = 4096, window: int = SLIDING_WINDOW,
-                 threshold: float = 1.15, allowed=None, **kw):
+                 threshold: float = 1.15, allowed=None, envs=None, **kw):
         from ..models.llama import LlamaConfig, llama_config
         if not isinstance(model, LlamaConfig):
             keys = {"num_layers", "hidden_size", "ffn_hidden_size", "num_heads", "vocab_size", "max_seq_len"}
@@ -45,6 +45,8 @@ class ElasticTrainer(HotSwitchTrainer):
         self.injected_slowdown: dict = {}                 # rank -> factor (host-side fault injection for tests)
         self.straggler = Straggler(self.device, None, WorkloadInfo(1, 1024, self.config.hidden_size))
         self.replans = 0
+        self.envs = envs                                   # TrainerEnvs: straggler / memory experiment switches
+        self._all_times: list = []
 
     # ---- strategies ------------------------------------------------------------------------------------
     def add_strategy(self, cfg: dict) -> int:
@@ -96,8 +98,33 @@ class ElasticTrainer(HotSwitchTrainer):
         else:
             mine = time.perf_counter() - t0
         mine *= self.injected_slowdown.get(self.mesh.rank, 1.0)
-        self.window.add(gather_times(mine))
+        times = gather_times(mine)
+        self.window.add(times)
+        self._record_experiments(times, res)
         return res
+
+    def _record_experiments(self, times, res) -> None:
+        """Straggler experiment: one JSON line per step with every rank's step time (rank 0 writes).  Memory
+        experiment: this rank's memory figures after the first step (reference: TrainerEnvs, run_straggler_experiment /
+        run_memory_experiment of python_refactor/elastic/engine/trainer.py)."""
+        envs = self.envs
+        if envs is None:
+            return
+        import json
+        step = len(self._all_times)
+        self._all_times.append(list(times))
+        if envs.run_straggler_experiment and envs.straggler_file and self.mesh.rank == 0:
+            with open(envs.straggler_file, "a") as f:
+                f.write(json.dumps({"step": step, "strategy": self.current, "times_s": [float(t) for t in times],
+                                    "loss": res.loss}) + "\n")
+        if envs.run_memory_experiment and envs.memory_file and step == 0:
+            from ..utils.profiler import CUDAProfiler
+            import os
+            rec = {"rank": self.mesh.rank, "strategy": self.current}
+            rec.update(CUDAProfiler().memory_info())
+            root, ext = os.path.splitext(envs.memory_file)
+            with open(f"{root}_rank{self.mesh.rank}{ext or '.json'}", "w") as f:
+                json.dump(rec, f)
 
     def _step_under(self, sid: int, sequences):
         """The parent's step with bucket 0 mapped to strategy `sid`."""

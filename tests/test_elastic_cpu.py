@@ -104,3 +104,24 @@ def test_engine_argument_records():
         U.TrainerStrategyArgs(dp=2, tp=1, pp=2, hetero_layers=[[2, 2]])
     mw = U.ModelWrapper(LlamaLMHeadModel, llama_config("tiny", num_layers=4))
     assert mw.model_class is LlamaLMHeadModel and U.OptimizerWrapper(ht.AdamOptimizer).create_optimizer(lr=1e-3).lr == 1e-3
+
+
+def test_straggler_and_memory_experiment_files(tmp_path):
+    import json
+    import torch
+    from hotspa_ae_b200.elastic.trainer import ElasticTrainer
+    from hotspa_ae_b200.elastic.utils import TrainerEnvs
+    from hotspa_ae_b200.parallel import mesh as M
+    from hotspa_ae_b200.utils import data as D
+    M.reset_mesh()
+    envs = TrainerEnvs(run_straggler_experiment=True, run_memory_experiment=True,
+                       straggler_file=str(tmp_path / "straggler.jsonl"), memory_file=str(tmp_path / "mem.json"))
+    tr = ElasticTrainer("tiny", (1, 1, 1, False), max_len=256, window=4, lr=1e-3, dtype=torch.float32, recompute=False,
+                        micro_batch_tokens=512, num_layers=2, max_seq_len=256, envs=envs)
+    for i in range(3):
+        lens = D.lognormal_lengths(512, seed=i, median=60, max_len=256)
+        tr.step(D.synthetic_sequences(lens, 1000, seed=i))
+    lines = [json.loads(l) for l in (tmp_path / "straggler.jsonl").read_text().splitlines()]
+    assert [l["step"] for l in lines] == [0, 1, 2] and len(lines[0]["times_s"]) == 1 and lines[0]["times_s"][0] > 0
+    mem = json.loads((tmp_path / "mem_rank0.json").read_text())
+    assert mem["rank"] == 0 and "mempool_allocated" in mem

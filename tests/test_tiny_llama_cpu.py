@@ -30,7 +30,7 @@ def test_tiny_llama_one_step_matches_pytorch():
         ref_losses.append(l)
     total = sum(ref_losses) / nmb
     total.backward()
-    np.testing.assert_allclose(losses, np.array([float(l) for l in ref_losses]), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(losses, np.array([float(l.detach()) for l in ref_losses]), rtol=1e-5, atol=1e-5)
     # one Adam step with lr 1e-3 from zero moments: p -= lr * sign-like update
     for k, p in b["model"].named_parameters():
         g_ref = w0[k].grad

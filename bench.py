@@ -68,7 +68,7 @@ TOKENS_PER_GPU_BY_MODEL = {"7b": 32768, "13b": 32768, "32b": 16384}
 # one value per strategy); only entries whose peak memory was measured
 KEEP_ACTIVATIONS: dict = {
     # 7B: one kept block costs 4.0-4.3 GB per 32K-token micro-batch divided by the tensor-parallel degree
-    "7b": {1: 6, 2: [20, 10], 4: [32, 20, 10], 8: [16, 16, 18]},
+    "7b": {1: 5, 2: [20, 10], 4: [32, 20, 10], 8: [16, 16, 18]},
 }
 
 REFERENCE_UNAVAILABLE = (

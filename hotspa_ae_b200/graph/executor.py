@@ -43,6 +43,7 @@ class CommInfo:
     fused: bool = False     # the neighbouring linear op performs this collective inside its GEMM kernel
     repartition: bool = False   # boundary op whose pieces come from the reshard planner (layouts differ)
     split_groups: list = field(default_factory=list)    # hetero collectives: rank groups per micro-block
+    pre: "CommInfo | None" = None   # collective inside the union member that runs before a split collective
 
 
 @dataclass
@@ -123,6 +124,11 @@ class Runtime:
 
     def comm(self, op, x):
         info: CommInfo = self.plan.comm[op.id]
+        if info.pre is not None:
+            x = self._apply_comm(info.pre, x)
+        return self._apply_comm(info, x)
+
+    def _apply_comm(self, info: CommInfo, x):
         k = info.kind
         if k == C._C.COMM_UNUSED or info.fused:
             return x
@@ -365,8 +371,31 @@ class Executor:
         su, du = x.ds_hierarchy[sid], y.ds_hierarchy[sid]
         kind = C.classify_comm(su, x.group(sid).ranks(), du, y.group(sid).ranks(), x.member_index(sid))
         base = kind & (C._C.COMM_SPLIT_ALL_REDUCE | C._C.COMM_SPLIT_REDUCE_SCATTER | C._C.COMM_SPLIT_ALL_GATHER)
-        if kind == C._C.COMM_UNSUPPORTED or base == 0 or kind != base:
-            raise NotImplementedError(f"{op}: {su} -> {du} needs a local collective next to the split one")
+        if kind == C._C.COMM_UNSUPPORTED or base == 0:
+            raise NotImplementedError(f"{op}: no collective realises {su} -> {du}")
+        # a member whose own layout changes too (e.g. it is partial over its tensor-parallel ranks as well) first runs
+        # that collective inside the member; its holders then carry equal data into the split collective.  The groups
+        # of every member are collected so that all ranks create the same process groups.
+        one = C.DistributedStatesUnion
+        real = (C._C.COMM_ALL_REDUCE, C._C.COMM_ALL_GATHER, C._C.COMM_REDUCE_SCATTER, C._C.COMM_SPLIT, C._C.COMM_SCATTER)
+        pre = None
+        for m, grp_m in enumerate(x.dg_hierarchy[sid]):
+            ranks_m = grp_m.ranks()
+            ls, ld = su.get_local(m), du.get_local(m)
+            if ls.check_equal(ld):
+                continue
+            k_m = C.classify_comm(one([ls]), ranks_m, one([ld]), ranks_m, 0)
+            if k_m == C._C.COMM_UNUSED:
+                continue
+            if k_m not in real:
+                raise NotImplementedError(f"{op}: member {m} needs {C.comm_type_name(k_m)} next to the split collective")
+            if base == C._C.COMM_SPLIT_REDUCE_SCATTER:
+                raise NotImplementedError(f"{op}: a split reduce-scatter with a collective inside member {m}")
+            for idx in range(len(ranks_m)):
+                ranks_i, dim, index, count = self._collective_group(k_m, ls, ld, idx, ranks_m)
+                needed.append(ranks_i)
+                if ranks_m[idx] == self.mesh.rank:
+                    pre = CommInfo(k_m, C.comm_type_name(k_m), ranks_i, dim, index, count)
         # groups follow the layout that is split finest: the destination for gather / all-reduce, the source's data
         # layout otherwise; the hetero dimension itself is taken out (that is what the collective resolves)
         ref_u, ref_t = (du, y) if base != C._C.COMM_SPLIT_REDUCE_SCATTER else (su, x)
@@ -378,6 +407,7 @@ class Executor:
                 every.update(g for gs in PC.split_collective_groups(locals_, rank_groups, r)[2] for g in gs)
         needed += sorted(every)
         info = CommInfo(base, C.comm_type_name(base))
+        info.pre = pre
         if self.mesh.rank in {r for grp in rank_groups for r in grp}:
             dim, _, groups = PC.split_collective_groups(locals_, rank_groups, self.mesh.rank)
             info.dim, info.split_groups = dim, groups

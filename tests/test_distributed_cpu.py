@@ -91,3 +91,8 @@ def test_llama_without_sequence_parallel_matches_single_process(world, strategy)
 
 def test_back_to_back_collectives_are_planned_as_one():
     _torchrun("comm_fusion_worker.py", 2, marker="COMM_FUSION_OK", timeout=600)
+
+
+def test_comm_ops_that_change_the_hetero_dimension():
+    # all-reduce inside a member followed by a split all-reduce across the members; split all-gather of rows
+    _torchrun("split_comm_graph_worker.py", 3, marker="SPLIT_COMM_GRAPH_OK", timeout=600)

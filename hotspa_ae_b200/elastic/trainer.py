@@ -191,9 +191,12 @@ class ElasticTrainer(HotSwitchTrainer):
             sid = self.pool[key]
         else:
             a = to_config_args(plan)
-            if plan.unused:
-                raise NotImplementedError("plans that drop devices need a new process group; restart from a checkpoint")
-            if a["hetero"] and plan.dp > 1:
+            if plan.unused and self.switch_mode == "fused":
+                raise NotImplementedError("a plan that leaves devices out is not supported with the fused peer-memory "
+                                          "switch (its barriers span every rank); use switch_mode='nccl'")
+            if plan.unused or (a["hetero"] and plan.dp > 1):
+                if plan.dp < 2:
+                    raise NotImplementedError("leaving devices out needs at least two replicas in the new plan")
                 # replicas with different layer splits: one pipeline per replica (a heterogeneous union; no ZeRO)
                 cfg = generate_llama_hetero_3d_config(self.config.num_layers, to_hetero_pipelines(plan), zero=False)
             else:

@@ -1,0 +1,66 @@
+"""Worker (4 gloo ranks): a device is taken out of training between two steps (it stays alive and only sits out: the
+"suspended" device of the elastic engine).  The trainer re-plans over the three remaining ranks, hot-switches the
+training state into the new layout and continues; the weights equal those of an uninterrupted run."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import hetu as ht  # noqa: E402
+from hotspa_ae_b200.elastic.strategy import StrategyModel  # noqa: E402
+from hotspa_ae_b200.elastic.trainer import ElasticTrainer  # noqa: E402
+from hotspa_ae_b200.parallel import mesh  # noqa: E402
+from hotspa_ae_b200.utils import checkpoint as CK  # noqa: E402
+from hotspa_ae_b200.utils import data as D  # noqa: E402
+
+OUT = 1          # the rank that is taken out (a middle one: the survivors are not a prefix of the ranks)
+
+
+def batches(n):
+    out = []
+    for i in range(n):
+        lens = D.lognormal_lengths(1024, seed=i, median=60, max_len=256)
+        out.append(D.synthetic_sequences(lens, 1000, seed=i))
+    return out
+
+
+def run(drop: bool):
+    mesh.reset_mesh()
+    tr = ElasticTrainer("tiny", (4, 1, 1, False), max_len=256, window=100, lr=1e-3, dtype=torch.float32,
+                        recompute=False, micro_batch_tokens=512, num_layers=2, max_seq_len=256, switch_mode="nccl")
+    data = batches(4)
+    res = [tr.step(b) for b in data[:2]]
+    if drop:
+        model = StrategyModel(tr.config.num_layers, list(range(4)), {}, unused=[OUT], allowed=[(3, 1, 1)])
+        plan = model.best()
+        assert plan.unused == [OUT] and plan.dp == 3 and sorted(plan.rank_order) == [0, 2, 3], plan
+        sid = tr.apply_plan(plan)
+        assert tr.current == sid and tr.input_ids.ds_hierarchy[sid].is_hetero()
+    res += [tr.step(b) for b in data[2:]]
+    full = {k: CK.gather_global(tr.graph, p).cpu() for k, p in tr.model.named_parameters()}
+    return tr, [r.loss for r in res], full
+
+
+def main():
+    ht.init_comm_group(8)
+    rank = int(os.environ["RANK"])
+    _, l0, w0 = run(False)
+    tr1, l1, w1 = run(True)
+    worst = max(float((w0[k] - w1[k]).abs().max()) for k in w0)
+    ok = worst < 3e-4 and np.allclose(l0, l1, rtol=1e-4, atol=1e-5)
+    if rank == OUT:
+        ok = ok and tr1.graph.executor.plan(tr1.current).my_stage < 0        # it really sat out
+    print(f"rank {rank}: losses {np.round(l0, 5).tolist()} vs {np.round(l1, 5).tolist()}; worst weight diff {worst:.2e} "
+          f"ok={ok}", flush=True)
+    t = torch.tensor([0 if ok else 1])
+    torch.distributed.all_reduce(t)
+    if rank == 0 and int(t.item()) == 0:
+        print("ELASTIC_DROP_OK")
+    sys.exit(0 if int(t.item()) == 0 else 3)
+
+
+if __name__ == "__main__":
+    main()

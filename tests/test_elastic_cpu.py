@@ -125,3 +125,8 @@ def test_straggler_and_memory_experiment_files(tmp_path):
     assert [l["step"] for l in lines] == [0, 1, 2] and len(lines[0]["times_s"]) == 1 and lines[0]["times_s"][0] > 0
     mem = json.loads((tmp_path / "mem_rank0.json").read_text())
     assert mem["rank"] == 0 and "mempool_allocated" in mem
+
+
+def test_a_device_is_taken_out_and_training_continues_on_the_rest():
+    # the survivors (ranks 0, 2, 3) become three single-device pipelines of a heterogeneous strategy
+    torchrun_cpu("elastic_drop_worker.py", 4, marker="ELASTIC_DROP_OK")
